@@ -1,0 +1,478 @@
+#!/usr/bin/env python
+"""Benchmark of the direct 2-D cross-correlation path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of synthetic input: the five
+benchmark configurations (one-to-one 16x16 and 256x256, one-to-many 64x64 x512, n-to-m
+32x32 32x64, n-to-mn 48x48 16x128), each as ONE library call.  Inputs are seeded
+uniform[0,1) float32 -- the value distribution of the reference's own generator
+(benchmark/input_generator.py:20-32) -- and are resident in HBM before the timed region.
+
+With N > 1 (one process per GPU, launched by torch.distributed.run) every rank runs the
+same pass on its own GPU: the independent result matrices of the many-matrix modes are the
+sharding unit, so N ranks holding one configuration's worth each is the N-times larger
+problem (N*512 right matrices, N*32 left matrices, N*16 left groups) sharded with the
+other operand replicated -- weak scaling, no collective on the data path.  The fixed-size
+split of each configuration over N GPUs ("strong") is reported per configuration as well.
+
+Output: ONE JSON line on rank 0.  `value` is the whole-job GFLOP/s (algorithmic FLOP =
+2 * pairs * rows^2 * cols^2) over all ranks; per-configuration GFLOP/s, output shifts/s and
+fraction of FP32-FFMA peak are under `per_config`.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# name -> (mode, rows, cols, n_left, n_right)
+CONFIGS = {
+    "C1": ("one_to_one", 16, 16, 1, 1),
+    "C2": ("one_to_one", 256, 256, 1, 1),
+    "C3": ("one_to_many", 64, 64, 1, 512),
+    "C4": ("n_to_m", 32, 32, 32, 64),
+    "C5": ("n_to_mn", 48, 48, 16, 2048),
+}
+L2_BYTES = 126 * 1024 * 1024
+NOMINAL_SM, NOMINAL_LANES = 148, 128
+
+
+def pairs_of(mode, nl, nr):
+    return {"one_to_one": 1, "one_to_many": nr, "n_to_mn": nr, "n_to_m": nl * nr}[mode]
+
+
+def flop_of(k):
+    mode, r, c, nl, nr = CONFIGS[k]
+    return 2.0 * pairs_of(mode, nl, nr) * r * r * c * c
+
+
+def shifts_of(k):
+    mode, r, c, nl, nr = CONFIGS[k]
+    return pairs_of(mode, nl, nr) * (2 * r - 1) * (2 * c - 1)
+
+
+def bytes_of(k):
+    """Compulsory bytes of one launch: every input matrix read once, every output written once."""
+    mode, r, c, nl, nr = CONFIGS[k]
+    return 4 * ((nl + nr) * r * c + shifts_of(k))
+
+
+def config_inputs(k, rank=0):
+    """Seeds 1000+k (left) and 2000+k (right); other ranks offset the seed (they hold other
+    matrices of the N-times larger problem)."""
+    mode, r, c, nl, nr = CONFIGS[k]
+    idx = int(k[1])
+    left = np.random.default_rng(1000 + idx).random((nl, r, c), dtype=np.float32)
+    right = np.random.default_rng(2000 + idx + 100 * rank).random((nr, r, c), dtype=np.float32)
+    return left, right
+
+
+def load_package():
+    name = "jpdc23_artifact_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "jpdc23-artifact_b200", "__init__.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+# ---- clocks -------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi samples of one GPU every 100 ms while the timed region runs (read-only)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); pw.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s, p in zip(sm, pw) if p >= 0.5 * max(pw)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "power_w_max": max(pw),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---- CPU baseline (the reference's own CPU path) ------------------------------------------------
+def cpu_baseline(target_seconds: float, threads: int):
+    """Time the reference's CPU implementation (oracle/_ref, validate.hpp:94-298, compiled
+    unmodified) -- or the C restatement when that library is absent -- on a bounded sample of
+    each configuration: as many whole result matrices as fit the time budget, split over
+    `threads` host threads.  Returns (GFLOP/s over the sample, description)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import pyoracle
+    if pyoracle.Reference.available():
+        ref = pyoracle.Reference()
+        kind = "reference"
+
+        def run(mode, left, right):
+            return ref.run_threaded(mode, left, right, threads)
+    else:
+        orc = pyoracle.Oracle()
+        kind = "port"
+
+        def run(mode, left, right):
+            return orc.run(mode, left, right, threads=threads)
+
+    est_rate = 2.2e9 * threads              # FLOP/s guess to size the sample; measured below
+    budget = target_seconds / len(CONFIGS)
+    total_flop, total_s, parts = 0.0, 0.0, []
+    for k, (mode, r, c, nl, nr) in CONFIGS.items():
+        left, right = config_inputs(k)
+        per_pair = 2.0 * r * r * c * c
+        want_pairs = max(1, int(budget * est_rate / per_pair))
+        if mode == "one_to_one":
+            l, rt, npairs = left, right, 1
+        elif mode == "one_to_many":
+            n = min(nr, max(threads, want_pairs))
+            l, rt, npairs = left, right[:n], n
+        elif mode == "n_to_m":
+            nls = min(nl, max(1, want_pairs // nr)) if want_pairs >= nr else 1
+            nrs = nr if want_pairs >= nr else min(nr, max(threads, want_pairs))
+            l, rt, npairs = left[:nls], right[:nrs], nls * nrs
+        else:  # n_to_mn, file order t*n + l: keep every left, cut the number of groups t
+            m = nr // nl
+            ms = min(m, max(1, want_pairs // nl))
+            l, rt, npairs = left, right[:ms * nl], ms * nl
+        t0 = time.perf_counter()
+        run(mode, l, rt)
+        dt = time.perf_counter() - t0
+        total_flop += per_pair * npairs
+        total_s += dt
+        parts.append(f"{k}:{npairs}/{pairs_of(mode, nl, nr)} pairs {dt:.2f}s")
+    return total_flop / total_s / 1e9, kind, "; ".join(parts)
+
+
+# ---- the reference arm -----------------------------------------------------------------------------
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    threads = os.cpu_count() or 1
+    vals = []
+    desc = kind = ""
+    for _ in range(args.warmup if args.warmup < 1 else 1):
+        cpu_baseline(2.0, threads)
+    per_step = max(3.0, min(30.0, 120.0 / max(1, args.steps)))
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        v, kind, desc = cpu_baseline(per_step, threads)
+        vals.append(v)
+    wall = time.perf_counter() - t0
+    value = statistics.mean(vals)
+    line = {
+        "impl": "reference", "metric": "xcorr_gflops", "value": value, "unit": "GFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * wall / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "GFLOP/s", "cores": threads, "kind": kind,
+                         "sample": desc + " (each step; result matrices split over host threads, "
+                                          "each thread running the single-threaded reference loop)"},
+        "e2e": {"value": value, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def workload_config(n_gpus):
+    ws = sum(bytes_of(k) for k in CONFIGS)
+    return {
+        "workload": "one pass over the five BASELINE configurations per GPU: "
+                    "C1 one_to_one 16x16; C2 one_to_one 256x256; C3 one_to_many 64x64 1x512; "
+                    "C4 n_to_m 32x32 32x64; C5 n_to_mn 48x48 16x(128 each)",
+        "sharding": "weak: every rank holds one configuration's worth of independent result matrices "
+                    "(N*512 rights, N*32 lefts, N*16 left groups in total); no collective on the data path",
+        "flop_per_step_per_gpu": sum(flop_of(k) for k in CONFIGS),
+        "l2": f"no explicit flush: one pass reads and writes {ws / 1e6:.0f} MB, more than the 126 MB L2",
+        "n_gpus": n_gpus,
+    }
+
+
+# ---- our arm -------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    xc = load_package()
+    xc.lib()                                   # raises if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    warmup = max(3, args.warmup)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    # ---- resident inputs, outputs, workspaces
+    dev = {}
+    for k, (mode, r, c, nl, nr) in CONFIGS.items():
+        left, right = config_inputs(k, rank)
+        wsb = xc.workspace_bytes(mode, r, c, nl, nr)
+        dev[k] = dict(
+            left=torch.from_numpy(left).cuda(), right=torch.from_numpy(right).cuda(),
+            out=torch.empty(xc.out_shape(mode, r, c, nl, nr), dtype=torch.float32, device="cuda"),
+            ws=torch.empty(max(wsb, 16), dtype=torch.uint8, device="cuda"), wsb=wsb)
+
+    def launch(k):
+        mode, r, c, nl, nr = CONFIGS[k]
+        d = dev[k]
+        xc.run_device(mode, d["left"].data_ptr(), d["right"].data_ptr(), d["out"].data_ptr(), r, c, nl, nr,
+                      None, d["ws"].data_ptr() if d["wsb"] else 0, d["wsb"], stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        for k in CONFIGS:
+            launch(k)
+    plans = {}
+    for k in CONFIGS:
+        launch(k)
+        plans[k] = xc.last_launch()
+    torch.cuda.synchronize()
+
+    # ---- timed region: K steps, one event pair around the region, one per launch
+    ev = {k: [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+              for _ in range(args.steps)] for k in CONFIGS}
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    xc.reset_launch_count()
+    e_start.record()
+    for s in range(args.steps):
+        for k in CONFIGS:
+            a, b = ev[k][s]
+            a.record()
+            launch(k)
+            b.record()
+    e_stop.record()
+    barrier()
+    launches = xc.launch_count()
+    region_ms = e_start.elapsed_time(e_stop)
+    clocks = sampler.stop() if rank == 0 else None
+    per_ms = {k: statistics.mean(a.elapsed_time(b) for a, b in ev[k]) for k in CONFIGS}
+    per_min = {k: min(a.elapsed_time(b) for a, b in ev[k]) for k in CONFIGS}
+
+    # ---- strong scaling of each shardable configuration: its own units split over the ranks
+    strong_ms = {}
+    if world > 1:
+        for k, (mode, r, c, nl, nr) in CONFIGS.items():
+            if mode == "one_to_one":
+                continue
+            units = nr if mode == "one_to_many" else nl
+            first, count = xc.shard_range(units, world, rank)
+            if count == 0:
+                strong_ms[k] = 0.0
+                continue
+            d = dev[k]
+            m = nr // nl if mode == "n_to_mn" else nr
+            if mode == "one_to_many":
+                a_nl, a_nr = 1, count
+            elif mode == "n_to_m":
+                a_nl, a_nr = count, nr
+            else:
+                a_nl, a_nr = count, count * m
+
+            def shard_launch():
+                xc.run_device(mode, d["left"].data_ptr(), d["right"].data_ptr(), d["out"].data_ptr(),
+                              r, c, a_nl, a_nr, None, 0, 0, stream)
+            for _ in range(3):
+                shard_launch()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(args.steps):
+                shard_launch()
+            b.record()
+            barrier()
+            strong_ms[k] = a.elapsed_time(b) / args.steps
+
+    # ---- end to end through the host-buffer entry point (pinned host memory both ways)
+    host = {}
+    for k, (mode, r, c, nl, nr) in CONFIGS.items():
+        left, right = config_inputs(k, rank)
+        hl = torch.from_numpy(left).pin_memory()
+        hr = torch.from_numpy(right).pin_memory()
+        ho = torch.empty(xc.out_shape(mode, r, c, nl, nr), dtype=torch.float32).pin_memory()
+        host[k] = (hl, hr, ho)
+    lib = xc.lib()
+
+    def e2e_pass():
+        for k, (mode, r, c, nl, nr) in CONFIGS.items():
+            hl, hr, ho = host[k]
+            xc.check(lib.xcorr_run_host_f32(xc.MODES[mode], hl.data_ptr(), hr.data_ptr(), ho.data_ptr(),
+                                            r, c, nl, nr, None, local_rank))
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_pass()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    checksum = float(host["C5"][2][0, 47, 47])   # a device result read on the host
+    barrier()
+
+    # ---- FFMA peak of this GPU, measured now
+    ffma_flops, _ = xc.ffma_peak_probe(stream)
+
+    # ---- max over ranks
+    vec = torch.tensor([region_ms, e2e_ms] + [per_ms[k] for k in CONFIGS] +
+                       [strong_ms.get(k, 0.0) for k in CONFIGS], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(vec, op=dist.ReduceOp.MAX)
+    vec = vec.cpu().tolist()
+    region_ms, e2e_ms = vec[0], vec[1]
+    per_ms_max = dict(zip(CONFIGS, vec[2:2 + len(CONFIGS)]))
+    strong_max = dict(zip(CONFIGS, vec[2 + len(CONFIGS):]))
+
+    if rank == 0:
+        ms_per_step = region_ms / args.steps
+        flop_step = sum(flop_of(k) for k in CONFIGS)
+        value = world * flop_step / (ms_per_step * 1e-3) / 1e9
+        peaks = {}
+        mp = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(mp):
+            peaks = json.load(open(mp))
+        hbm_peak = peaks.get("hbm_gbs", 6650.0)
+        sm_max = (clocks or {}).get("sm_max_mhz") or peaks.get("sm_max_mhz", 1965.0)
+        nominal_peak = NOMINAL_SM * NOMINAL_LANES * 2 * sm_max * 1e6
+        per_config = {}
+        for k, (mode, r, c, nl, nr) in CONFIGS.items():
+            t = per_ms_max[k] * 1e-3
+            entry = {
+                "mode": mode, "shape": f"{r}x{c} {nl}x{nr}", "ms": per_ms_max[k], "ms_min_rank0": per_min[k],
+                "gflops": world * flop_of(k) / t / 1e9, "shifts_per_s": world * shifts_of(k) / t,
+                "frac_ffma_measured": flop_of(k) / t / ffma_flops,
+                "frac_ffma_nominal": flop_of(k) / t / nominal_peak,
+                "hbm_gbs": bytes_of(k) / t / 1e9, "plan": plans[k],
+            }
+            if k in strong_ms:
+                ts = strong_max[k] * 1e-3
+                entry["strong"] = {"ms": strong_max[k], "gflops": flop_of(k) / ts / 1e9 if ts > 0 else None,
+                                   "shifts_per_s": shifts_of(k) / ts if ts > 0 else None}
+            per_config[k] = entry
+        dom = max(CONFIGS, key=lambda k: per_ms_max[k])
+        traffic = None
+        tp = os.path.join(ROOT, "profiles", "dram_traffic.json")
+        if os.path.exists(tp):
+            traffic = json.load(open(tp)).get(dom)
+        achieved = flop_of(dom) / (per_ms_max[dom] * 1e-3) / 1e12
+        roofline = {
+            "bound": "fp32_ffma", "kernel": plans[dom].split(" ")[0].replace("kernel=", "") + f" ({dom})",
+            "achieved": achieved, "peak": ffma_flops / 1e12, "unit": "TFLOP/s",
+            "frac": achieved / (ffma_flops / 1e12),
+            "peak_source": "of measured: register-only FFMA probe on this GPU in this run "
+                           f"(nominal 148 SM x 128 lanes x 2 x {sm_max:.0f} MHz = {nominal_peak / 1e12:.1f})",
+            "traffic": traffic,
+            "hbm": {"achieved": bytes_of(dom) / (per_ms_max[dom] * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": bytes_of(dom) / (per_ms_max[dom] * 1e-3) / 1e9 / hbm_peak,
+                    "note": "compulsory bytes / time: far below the HBM roofline, the kernel is FFMA-bound"},
+        }
+        line = {
+            "metric": "xcorr_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(world),
+            "shifts_per_s": world * sum(shifts_of(k) for k in CONFIGS) / (ms_per_step * 1e-3),
+            "frac_ffma_measured": flop_step / (ms_per_step * 1e-3) / ffma_flops,
+            "ffma_peak_measured_tflops": ffma_flops / 1e12, "ffma_peak_nominal_tflops": nominal_peak / 1e12,
+            "per_config": per_config, "roofline": roofline, "clocks": clocks,
+            "e2e": {"value": world * flop_step / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
+                    "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "h2d_bytes_per_step": sum(4 * (CONFIGS[k][3] + CONFIGS[k][4]) * CONFIGS[k][1] * CONFIGS[k][2]
+                                              for k in CONFIGS),
+                    "d2h_bytes_per_step": sum(4 * shifts_of(k) for k in CONFIGS),
+                    "api": "xcorr_run_host_f32 per configuration: pinned host in, H2D, kernel, D2H, pinned host out",
+                    "result_probe": checksum},
+            "gpu_launches": int(launches),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            v, kind, desc = cpu_baseline(args.cpu_seconds, threads)
+            line["cpu_baseline"] = {"value": v, "unit": "GFLOP/s", "cores": threads, "kind": kind, "sample": desc}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

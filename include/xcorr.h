@@ -1,0 +1,226 @@
+/*
+ * xcorr.h -- C ABI of the B200 (sm_100a) direct 2-D cross-correlation library.
+ *
+ * The reference project has no FFI layer; its seam is the C++ launcher API declared in
+ * repo/cross-corr/src/kernels.cuh:41-283 (free function templates `run_*<float,float>`
+ * taking caller-owned device pointers, a matrix size, a search size, matrix counts,
+ * tuning integers and sometimes a stream) and, one level up, the per-mode algorithm
+ * classes of one_to_one.hpp / one_to_many.hpp / n_to_mn.hpp / n_to_m.hpp.  Every entry
+ * point below names the reference interface it stands in for.
+ *
+ * Conventions shared by all entry points
+ *   - float32, row-major, matrices of one array stacked contiguously
+ *     (repo/cross-corr/src/matrix.hpp:410-619, data_array).
+ *   - `left` is the reference's "ref", `right` its "target"/"deformed".
+ *   - out[(sy + rows-1) * (2*cols-1) + (sx + cols-1)] =
+ *         sum over the overlap of left[y+sy][x+sx] * right[y][x]
+ *     for sx in [-(cols-1), cols-1], sy in [-(rows-1), rows-1]
+ *     (repo/cross-corr/src/validate.hpp:95-132); one (2*rows-1) x (2*cols-1) result per pair.
+ *   - Device entry points: pointers are device pointers owned by the caller; nothing is
+ *     allocated, freed or retained; the launch is asynchronous on `stream` (a
+ *     cudaStream_t passed as void*, NULL = legacy default stream) and does not
+ *     synchronise.  Unlike the reference launchers, which throw std::runtime_error
+ *     (e.g. naive_shuffle_multirow_both.cu:645-665), errors come back as a status
+ *     code; nothing is thrown across this boundary.
+ *   - Result order (validate.hpp:230-291):
+ *       one_to_many  out[t]                left 0 with right t
+ *       n_to_m       out[l * n_right + t]  left l with right t
+ *       n_to_mn      GROUPED order: right and out matrix l*m + t belong to left l,
+ *                    m = n_right / n_left.  This is the in-memory order the reference's
+ *                    GPU algorithms use after load_interleaved_from_csv
+ *                    (matrix.hpp:484-503); files hold the order t*n_left + l, and
+ *                    xcorr_n_to_mn_reorder_f32 converts between the two.
+ */
+#ifndef XCORR_H
+#define XCORR_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define XCORR_API
+#else
+#define XCORR_API __attribute__((visibility("default")))
+#endif
+
+typedef enum xcorr_status {
+    XCORR_OK = 0,
+    XCORR_ERR_NULL_POINTER = 1,      /* a required pointer is NULL */
+    XCORR_ERR_INVALID_SIZE = 2,      /* zero rows/cols/counts, n_right % n_left != 0, overflow of uint32 indexing */
+    XCORR_ERR_INVALID_HINT = 3,      /* a tuning value outside the supported range */
+    XCORR_ERR_WORKSPACE = 4,         /* workspace missing or smaller than xcorr_workspace_bytes() */
+    XCORR_ERR_CUDA = 5,              /* a CUDA runtime call failed; see xcorr_last_error_string() */
+    XCORR_ERR_UNSUPPORTED = 6,       /* shape needs more shared memory than one SM has */
+    XCORR_ERR_DEVICE = 7,            /* bad device index / no usable device for the sharded runner */
+    XCORR_ERR_TIMEOUT = 8            /* a bounded device-side wait gave up */
+} xcorr_status;
+
+typedef enum xcorr_mode {
+    XCORR_ONE_TO_ONE = 0,
+    XCORR_ONE_TO_MANY = 1,
+    XCORR_N_TO_MN = 2,
+    XCORR_N_TO_M = 3
+} xcorr_mode;
+
+/* Kernel families.  The first three mirror the reference's algorithm families; which
+ * registry names map to which family is the host program's business. */
+typedef enum xcorr_kernel {
+    XCORR_KERNEL_AUTO = 0,          /* per-shape selection */
+    XCORR_KERNEL_TILE = 1,          /* register-tiled circular-class kernel (the fast path) */
+    XCORR_KERNEL_OVERLAP_WISE = 2,  /* one thread per overlap -- run_cross_corr_naive_original, naive_original.cu:131-161 */
+    XCORR_KERNEL_WARP_PER_OVERLAP = 3 /* one warp per overlap -- run_ccn_warp_per_shift, naive_warp_per_shift.cu:308-335 */
+} xcorr_kernel;
+
+/* How partial sums of a row-split launch are combined (the reference's "work
+ * distribution" kernels always use atomicAdd on a caller-zeroed buffer,
+ * naive_shuffle.cu:307-413, one_to_one.hpp:277). */
+typedef enum xcorr_combine {
+    XCORR_COMBINE_AUTO = 0,
+    XCORR_COMBINE_STORE = 1,     /* no row split; each output written once */
+    XCORR_COMBINE_ATOMIC = 2,    /* the library zeroes `out`, then red.global.add.f32 */
+    XCORR_COMBINE_WORKSPACE = 3  /* partial images in the workspace + fixed-order reduction: bit-reproducible */
+} xcorr_combine;
+
+/* Tuning hints; all zero (or a NULL pointer) = automatic.  These replace the reference's
+ * per-algorithm JSON keys (warps_per_thread_block, shifts_per_thread,
+ * left_rows_per_iteration, right_matrices_per_thread, rows_per_thread, ...), which the
+ * reference bakes into template instantiations. */
+typedef struct xcorr_hints {
+    int32_t kernel;            /* xcorr_kernel */
+    int32_t combine;           /* xcorr_combine */
+    int32_t overlap_rows;      /* TILE: y-overlap classes per thread, 1..4 (cf. shifts_per_thread) */
+    int32_t class_lanes;       /* TILE: lanes of a warp spread over y-classes: 1,2,4,8,16,32; the
+                                  other 32/class_lanes lanes take different right matrices
+                                  (cf. right_matrices_per_thread) */
+    int32_t warps_x;           /* TILE: warps of a block along x-class tiles (cf. warps_per_thread_block) */
+    int32_t warps_y;           /* TILE: warps of a block along y-class groups */
+    int32_t row_slices;        /* TILE: number of slices the right rows are split into (cf. rows_per_thread) */
+    int32_t block_threads;     /* OVERLAP_WISE / WARP_PER_OVERLAP: threads per block */
+    int32_t reserved[8];
+} xcorr_hints;
+
+/* ---- device-pointer entry points ------------------------------------------------------
+ * One per input mode.  They stand in for the reference launchers the mode's algorithm
+ * classes call:
+ *   one_to_one   run_ccn_shuffle_multirow_both            kernels.cuh:191-201 (one_to_one.hpp:755)
+ *   one_to_many  run_ccn_shuffle_one_to_many_multirow_both_multimat_right
+ *                                                          kernels.cuh:227-240 (one_to_many.hpp:379)
+ *   n_to_mn      the same launcher once per left matrix on round-robin streams
+ *                                                          (n_to_mn.hpp:553-571)
+ *   n_to_m       run_ccn_n_to_m_shuffle_multirow_both_multimat_both
+ *                                                          kernels.cuh:242-256 (n_to_m.hpp:495)
+ * and, through hints->kernel, for run_cross_corr_naive_original (kernels.cuh:41-51) and
+ * run_ccn_warp_per_shift (kernels.cuh:98-106).  The search size is always the full
+ * (2*cols-1, 2*rows-1), which is what every reference caller passes.
+ * `workspace` may be NULL unless the chosen plan combines through the workspace
+ * (see xcorr_workspace_bytes); it must be 256-byte aligned. */
+XCORR_API xcorr_status xcorr_one_to_one_f32(const float* d_left, const float* d_right, float* d_out,
+                                            uint32_t rows, uint32_t cols,
+                                            const xcorr_hints* hints,
+                                            void* d_workspace, size_t workspace_bytes, void* stream);
+
+XCORR_API xcorr_status xcorr_one_to_many_f32(const float* d_left, const float* d_right, float* d_out,
+                                             uint32_t rows, uint32_t cols, uint32_t n_right,
+                                             const xcorr_hints* hints,
+                                             void* d_workspace, size_t workspace_bytes, void* stream);
+
+XCORR_API xcorr_status xcorr_n_to_mn_f32(const float* d_left, const float* d_right, float* d_out,
+                                         uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                         const xcorr_hints* hints,
+                                         void* d_workspace, size_t workspace_bytes, void* stream);
+
+XCORR_API xcorr_status xcorr_n_to_m_f32(const float* d_left, const float* d_right, float* d_out,
+                                        uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                        const xcorr_hints* hints,
+                                        void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* Mode-generic form of the four above (same contract). */
+XCORR_API xcorr_status xcorr_run_f32(int32_t mode, const float* d_left, const float* d_right, float* d_out,
+                                     uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                     const xcorr_hints* hints,
+                                     void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of workspace the plan chosen for this shape and these hints needs (0 when it
+ * needs none).  Replaces the reference's convention that callers of the atomic variants
+ * zero the output themselves (one_to_one.hpp:277, :503). */
+XCORR_API size_t xcorr_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols,
+                                       uint32_t n_left, uint32_t n_right, const xcorr_hints* hints);
+
+/* Text form of the launch plan this shape and these hints would get (the same text
+ * xcorr_last_launch_string reports after a launch); needs no device -- without one a B200
+ * (148 SMs, 227 KB shared memory per block) is assumed.  Returns an xcorr_status. */
+XCORR_API int32_t xcorr_describe_plan(int32_t mode, uint32_t rows, uint32_t cols,
+                                      uint32_t n_left, uint32_t n_right, const xcorr_hints* hints,
+                                      char* buffer, size_t buffer_bytes);
+
+/* Number of result matrices of a mode (validate.hpp:214-291 check_num_result_matrices). */
+XCORR_API uint64_t xcorr_num_results(int32_t mode, uint32_t n_left, uint32_t n_right);
+
+/* `cross input` shape rules: one_to_one.hpp:20-22, one_to_many.hpp:15-17,
+ * n_to_mn.hpp:23-25, n_to_m.hpp:19-21.  Returns 1 for valid, 0 for invalid. */
+XCORR_API int32_t xcorr_validate_input_size(int32_t mode, uint32_t rows, uint32_t cols,
+                                            uint32_t n_left, uint32_t n_right);
+
+/* ---- host-buffer entry points -----------------------------------------------------------
+ * The reference's whole computation step for one algorithm object: prepare (cudaMalloc),
+ * transfer (H2D), run, finalize (D2H), free -- main.cpp:123-174, one_to_one.hpp:112-135 and
+ * the other modes' naive_gpu_* classes.  Host pointers in, host result out; synchronous.
+ * Device buffers are cached per device and reused across calls.  n_to_mn takes and
+ * returns GROUPED order like the device entry point. */
+XCORR_API xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, const float* h_right, float* h_out,
+                                          uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                          const xcorr_hints* hints, int32_t device);
+
+/* Same, with the independent result matrices sharded over `n_devices` GPUs of this
+ * process (devices[i] are CUDA device indices; NULL = 0..n_devices-1): right matrices for
+ * one_to_many, left matrices for n_to_m and n_to_mn (each with all / its own rights), the
+ * other operand replicated; one host thread and stream per GPU, no collective.  one_to_one
+ * runs on devices[0].  The reference has no multi-GPU path; this extends the stream
+ * fan-out of n_to_mn.hpp:329-348 / n_to_m.hpp:293-312 across devices. */
+XCORR_API xcorr_status xcorr_run_host_sharded_f32(int32_t mode, const float* h_left, const float* h_right,
+                                                  float* h_out, uint32_t rows, uint32_t cols,
+                                                  uint32_t n_left, uint32_t n_right,
+                                                  const xcorr_hints* hints,
+                                                  const int32_t* devices, int32_t n_devices);
+
+/* The shard of units (right matrices or left matrices, see above) that part `index` of
+ * `parts` owns: [*first, *first + *count).  Contiguous, sizes differ by at most one. */
+XCORR_API void xcorr_shard_range(uint32_t units, int32_t parts, int32_t index,
+                                 uint32_t* first, uint32_t* count);
+
+/* Release the cached device buffers of xcorr_run_host*_f32 (all devices). */
+XCORR_API void xcorr_release_host_cache(void);
+
+/* ---- n_to_mn order helpers (host memory) -------------------------------------------------
+ * matrix.hpp:614-618 get_interleaved_index and :484-552 load/store interleaved.
+ * to_grouped != 0: file order (t*n_left + l) -> grouped order (l*m + t); 0: the inverse.
+ * `elems` = floats per matrix.  src and dst must not overlap. */
+XCORR_API xcorr_status xcorr_n_to_mn_reorder_f32(const float* src, float* dst, uint32_t n_left,
+                                                 uint32_t n_total, size_t elems, int32_t to_grouped);
+
+/* ---- diagnostics ---------------------------------------------------------------------------
+ * xcorr_last_launch_string: kernel name, grid, block, dynamic shared memory and plan of
+ * the calling thread's last launch -- replaces kernel_args.hpp/.cpp (last_kernel_launch_args
+ * string echoed by main.cpp:131-133).  Thread-local; valid until the thread's next call. */
+XCORR_API const char* xcorr_last_launch_string(void);
+XCORR_API const char* xcorr_last_error_string(void);
+XCORR_API const char* xcorr_status_string(int32_t status);
+
+/* Number of kernels (library kernels only, not memsets or copies) launched by the calling
+ * thread since the counter was last reset. */
+XCORR_API uint64_t xcorr_launch_count(void);
+XCORR_API void xcorr_reset_launch_count(void);
+
+/* Measured FP32 FFMA throughput of the current device in FLOP/s: a dependency-free
+ * register-only FFMA kernel on every SM, timed with CUDA events on `stream`
+ * (synchronises).  The denominator for "fraction of FFMA peak". */
+XCORR_API xcorr_status xcorr_ffma_peak_probe(double* flops_per_second, double* kernel_ms, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XCORR_H */

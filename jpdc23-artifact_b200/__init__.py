@@ -1,0 +1,211 @@
+"""Python binding (ctypes) of the B200 direct cross-correlation library.
+
+The product is ``lib/libxcorr.so`` (C ABI in ``include/xcorr.h``) and the ``bin/cross``
+host program; this module only loads the library for tests, the benchmark and scripts.
+There is no CPU fallback: every call goes to the CUDA library and raises if it is missing.
+
+The directory name contains a hyphen, so import it by path::
+
+    import importlib.util, sys
+    spec = importlib.util.spec_from_file_location(
+        "jpdc23_artifact_b200", "<repo>/jpdc23-artifact_b200/__init__.py")
+    xc = importlib.util.module_from_spec(spec); sys.modules[spec.name] = xc
+    spec.loader.exec_module(xc)
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "lib", "libxcorr.so")
+CROSS_PATH = os.path.join(PKG_DIR, "bin", "cross")
+HEADER_PATH = os.path.join(os.path.dirname(PKG_DIR), "include", "xcorr.h")
+
+MODES = {"one_to_one": 0, "one_to_many": 1, "n_to_mn": 2, "n_to_m": 3}
+KERNELS = {"auto": 0, "tile": 1, "overlap_wise": 2, "warp_per_overlap": 3}
+COMBINE = {"auto": 0, "store": 1, "atomic": 2, "workspace": 3}
+
+
+class XcorrError(RuntimeError):
+    def __init__(self, status: int, what: str, detail: str):
+        super().__init__(f"xcorr status {status} ({what}): {detail}")
+        self.status = status
+
+
+class Hints(C.Structure):
+    """Mirror of ``xcorr_hints`` (include/xcorr.h)."""
+    _fields_ = [
+        ("kernel", C.c_int32), ("combine", C.c_int32), ("overlap_rows", C.c_int32),
+        ("class_lanes", C.c_int32), ("warps_x", C.c_int32), ("warps_y", C.c_int32),
+        ("row_slices", C.c_int32), ("block_threads", C.c_int32), ("reserved", C.c_int32 * 8),
+    ]
+
+
+def make_hints(kernel="auto", combine="auto", overlap_rows=0, class_lanes=0, warps_x=0, warps_y=0,
+               row_slices=0, block_threads=0) -> Hints:
+    h = Hints()
+    h.kernel = KERNELS[kernel] if isinstance(kernel, str) else int(kernel)
+    h.combine = COMBINE[combine] if isinstance(combine, str) else int(combine)
+    h.overlap_rows, h.class_lanes = overlap_rows, class_lanes
+    h.warps_x, h.warps_y, h.row_slices, h.block_threads = warps_x, warps_y, row_slices, block_threads
+    return h
+
+
+def build(verbose: bool = False) -> None:
+    """Compile lib/libxcorr.so and bin/cross for sm_100a (nvcc cross-compiles without a GPU)."""
+    subprocess.run(["make", "-C", PKG_DIR, "all"], check=True,
+                   stdout=None if verbose else subprocess.DEVNULL)
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(
+            f"{LIB_PATH} is missing: build it with `make -C {PKG_DIR}` (there is no CPU fallback)")
+    L = C.CDLL(LIB_PATH)
+    u32, i32, vp, sz = C.c_uint32, C.c_int32, C.c_void_p, C.c_size_t
+    hp = C.POINTER(Hints)
+    L.xcorr_run_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, hp, vp, sz, vp]
+    L.xcorr_one_to_one_f32.argtypes = [vp, vp, vp, u32, u32, hp, vp, sz, vp]
+    L.xcorr_one_to_many_f32.argtypes = [vp, vp, vp, u32, u32, u32, hp, vp, sz, vp]
+    L.xcorr_n_to_mn_f32.argtypes = [vp, vp, vp, u32, u32, u32, u32, hp, vp, sz, vp]
+    L.xcorr_n_to_m_f32.argtypes = [vp, vp, vp, u32, u32, u32, u32, hp, vp, sz, vp]
+    L.xcorr_workspace_bytes.argtypes = [i32, u32, u32, u32, u32, hp]
+    L.xcorr_workspace_bytes.restype = sz
+    L.xcorr_describe_plan.argtypes = [i32, u32, u32, u32, u32, hp, C.c_char_p, sz]
+    L.xcorr_describe_plan.restype = i32
+    L.xcorr_num_results.argtypes = [i32, u32, u32]
+    L.xcorr_num_results.restype = C.c_uint64
+    L.xcorr_validate_input_size.argtypes = [i32, u32, u32, u32, u32]
+    L.xcorr_validate_input_size.restype = i32
+    L.xcorr_run_host_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, hp, i32]
+    L.xcorr_run_host_sharded_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, hp,
+                                             C.POINTER(i32), i32]
+    L.xcorr_shard_range.argtypes = [u32, i32, i32, C.POINTER(u32), C.POINTER(u32)]
+    L.xcorr_shard_range.restype = None
+    L.xcorr_release_host_cache.argtypes = []
+    L.xcorr_release_host_cache.restype = None
+    L.xcorr_n_to_mn_reorder_f32.argtypes = [vp, vp, u32, u32, sz, i32]
+    for name in ("xcorr_last_launch_string", "xcorr_last_error_string"):
+        getattr(L, name).argtypes = []
+        getattr(L, name).restype = C.c_char_p
+    L.xcorr_status_string.argtypes = [i32]
+    L.xcorr_status_string.restype = C.c_char_p
+    L.xcorr_launch_count.argtypes = []
+    L.xcorr_launch_count.restype = C.c_uint64
+    L.xcorr_reset_launch_count.argtypes = []
+    L.xcorr_reset_launch_count.restype = None
+    L.xcorr_ffma_peak_probe.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_double), vp]
+    _lib = L
+    return L
+
+
+def check(status: int) -> None:
+    if status != 0:
+        L = lib()
+        raise XcorrError(status, L.xcorr_status_string(status).decode(),
+                         L.xcorr_last_error_string().decode())
+
+
+def _mode(mode) -> int:
+    return MODES[mode] if isinstance(mode, str) else int(mode)
+
+
+def out_shape(mode, rows: int, cols: int, n_left: int, n_right: int):
+    n = int(lib().xcorr_num_results(_mode(mode), n_left, n_right))
+    return (n, 2 * rows - 1, 2 * cols - 1)
+
+
+def shard_range(units: int, parts: int, index: int):
+    first, count = C.c_uint32(0), C.c_uint32(0)
+    lib().xcorr_shard_range(units, parts, index, C.byref(first), C.byref(count))
+    return first.value, count.value
+
+
+def workspace_bytes(mode, rows, cols, n_left, n_right, hints: Hints | None = None) -> int:
+    return int(lib().xcorr_workspace_bytes(_mode(mode), rows, cols, n_left, n_right,
+                                           C.byref(hints) if hints is not None else None))
+
+
+def describe_plan(mode, rows, cols, n_left, n_right, hints: Hints | None = None) -> str:
+    buf = C.create_string_buffer(1024)
+    check(lib().xcorr_describe_plan(_mode(mode), rows, cols, n_left, n_right,
+                                    C.byref(hints) if hints is not None else None, buf, len(buf)))
+    return buf.value.decode()
+
+
+def run_device(mode, d_left: int, d_right: int, d_out: int, rows: int, cols: int, n_left: int,
+               n_right: int, hints: Hints | None = None, d_workspace: int = 0,
+               workspace_bytes_: int = 0, stream: int = 0) -> None:
+    """Asynchronous launch on raw device addresses (ints), e.g. torch ``tensor.data_ptr()``."""
+    check(lib().xcorr_run_f32(_mode(mode), d_left, d_right, d_out, rows, cols, n_left, n_right,
+                              C.byref(hints) if hints is not None else None,
+                              d_workspace or None, workspace_bytes_, stream or None))
+
+
+def run_host(mode, left: np.ndarray, right: np.ndarray, hints: Hints | None = None, device: int = 0,
+             devices: list[int] | None = None, out: np.ndarray | None = None) -> np.ndarray:
+    """Host arrays in, host result out (H2D, kernel, D2H).  ``devices`` shards over GPUs.
+    n_to_mn uses GROUPED order (right / result l*m + t belongs to left l)."""
+    left = np.ascontiguousarray(left, np.float32)
+    right = np.ascontiguousarray(right, np.float32)
+    if left.ndim == 2:
+        left = left[None]
+    if right.ndim == 2:
+        right = right[None]
+    nl, rows, cols = left.shape
+    nr = right.shape[0]
+    if right.shape[1:] != (rows, cols):
+        raise ValueError("left and right matrices must have the same size")
+    shape = out_shape(mode, rows, cols, nl, nr)
+    if shape[0] == 0:
+        check(2)
+    if out is None:
+        out = np.empty(shape, np.float32)
+    hp = C.byref(hints) if hints is not None else None
+    if devices is None:
+        check(lib().xcorr_run_host_f32(_mode(mode), left.ctypes.data, right.ctypes.data,
+                                       out.ctypes.data, rows, cols, nl, nr, hp, device))
+    else:
+        arr = (C.c_int32 * len(devices))(*devices)
+        check(lib().xcorr_run_host_sharded_f32(_mode(mode), left.ctypes.data, right.ctypes.data,
+                                               out.ctypes.data, rows, cols, nl, nr, hp, arr,
+                                               len(devices)))
+    return out
+
+
+def n_to_mn_reorder(a: np.ndarray, n_left: int, to_grouped: bool) -> np.ndarray:
+    a = np.ascontiguousarray(a, np.float32)
+    dst = np.empty_like(a)
+    elems = int(np.prod(a.shape[1:]))
+    check(lib().xcorr_n_to_mn_reorder_f32(a.ctypes.data, dst.ctypes.data, n_left, a.shape[0], elems,
+                                          1 if to_grouped else 0))
+    return dst
+
+
+def last_launch() -> str:
+    return lib().xcorr_last_launch_string().decode()
+
+
+def launch_count() -> int:
+    return int(lib().xcorr_launch_count())
+
+
+def reset_launch_count() -> None:
+    lib().xcorr_reset_launch_count()
+
+
+def ffma_peak_probe(stream: int = 0):
+    flops, ms = C.c_double(0), C.c_double(0)
+    check(lib().xcorr_ffma_peak_probe(C.byref(flops), C.byref(ms), stream or None))
+    return flops.value, ms.value

@@ -1,0 +1,646 @@
+// C ABI of the cross-correlation library: argument checks, per-shape planning, launches,
+// the host-buffer and multi-GPU front ends, diagnostics.  See include/xcorr.h for the
+// contract of every entry point and the reference interface it stands in for.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "xcorr.h"
+#include "xcorr_launch.h"
+#include "xcorr_plan.h"
+
+namespace {
+
+using namespace xcorr;
+
+thread_local std::string t_last_launch = "no kernel launched yet";
+thread_local std::string t_last_error;
+thread_local uint64_t t_launch_count = 0;
+
+xcorr_status fail(xcorr_status st, const std::string& msg) {
+    t_last_error = msg;
+    return st;
+}
+
+xcorr_status cuda_fail(cudaError_t e, const char* what) {
+    t_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return XCORR_ERR_CUDA;
+}
+
+#define XC_CUDA(call)                                           \
+    do {                                                        \
+        cudaError_t e__ = (call);                               \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call);   \
+    } while (0)
+
+struct DeviceInfo {
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    bool valid = false;
+};
+
+constexpr int kMaxDevices = 64;
+DeviceInfo g_dev_info[kMaxDevices];
+std::mutex g_dev_info_mutex;
+
+xcorr_status current_device_info(DeviceInfo* out, int* dev_out = nullptr) {
+    int dev = 0;
+    XC_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(XCORR_ERR_DEVICE, "device index out of range");
+    std::lock_guard<std::mutex> lock(g_dev_info_mutex);
+    DeviceInfo& d = g_dev_info[dev];
+    if (!d.valid) {
+        int v = 0;
+        XC_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+        d.sm_count = v;
+        XC_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        d.smem_optin = (size_t)v;
+        d.valid = true;
+    }
+    *out = d;
+    if (dev_out) *dev_out = dev;
+    return XCORR_OK;
+}
+
+// Planning never needs a device: without one it assumes a B200 (148 SMs, 227 KB).
+DeviceInfo assumed_device() {
+    DeviceInfo d;
+    d.sm_count = 148;
+    d.smem_optin = kSmemLimit;
+    d.valid = true;
+    return d;
+}
+
+bool pair_map(int32_t mode, uint32_t n_left, uint32_t n_right, PairMap* pm) {
+    switch (mode) {
+    case XCORR_ONE_TO_ONE:
+        if (n_left != 1 || n_right != 1) return false;
+        *pm = PairMap{1, 1, 0};
+        return true;
+    case XCORR_ONE_TO_MANY:
+        if (n_left != 1 || n_right == 0) return false;
+        *pm = PairMap{1, n_right, 0};
+        return true;
+    case XCORR_N_TO_MN:
+        if (n_left == 0 || n_right == 0 || n_right % n_left != 0) return false;
+        *pm = PairMap{n_left, n_right / n_left, n_right / n_left};
+        return true;
+    case XCORR_N_TO_M:
+        if (n_left == 0 || n_right == 0) return false;
+        *pm = PairMap{n_left, n_right, 0};
+        return true;
+    default:
+        return false;
+    }
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
+bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+int largest_divisor_at_most(int n, int cap) {
+    for (int d = std::min(n, cap); d >= 1; --d)
+        if (n % d == 0) return d;
+    return 1;
+}
+
+// Fill the fields that follow from (TY, SL, WX, WY, S).
+void finish_plan(TilePlan& p, const PairMap& pm) {
+    p.ML = 32 / p.SL;
+    p.logSL = ilog2(p.SL);
+    p.Wp = round_up(p.W, kTX);
+    p.Hp = round_up(p.H, p.SL * p.TY);
+    p.NTX = p.Wp / kTX;
+    p.NGY = p.Hp / (p.SL * p.TY);
+    p.CX = (p.NTX + p.WX - 1) / p.WX;
+    p.CY = (p.NGY + p.WY - 1) / p.WY;
+    p.RSmax = (p.H + p.S - 1) / p.S;
+    p.RG = (int)((pm.m + p.ML - 1) / p.ML);
+    const int cls_per_block = p.WY * p.SL * p.TY;
+    p.nstage = std::min(p.RSmax + cls_per_block - 1, p.Hp);
+    p.LS = p.Wp + 4;
+    p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
+    p.threads = 32 * p.WX * p.WY;
+    p.smem_bytes = ((size_t)p.nstage * p.LS + (size_t)p.ML * p.RMS) * sizeof(float);
+}
+
+// Per-shape plan of the tile kernel.
+xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, const DeviceInfo& dev,
+                       TilePlan* out) {
+    TilePlan best{};
+    double best_score = -1.0;
+    const int want_ty = h ? h->overlap_rows : 0;
+    const int want_sl = h ? h->class_lanes : 0;
+    if (want_ty < 0 || want_ty > kMaxTY) return fail(XCORR_ERR_INVALID_HINT, "overlap_rows must be 0..4");
+    if (want_sl != 0 && (!is_pow2(want_sl) || want_sl > 32))
+        return fail(XCORR_ERR_INVALID_HINT, "class_lanes must be 0 or a power of two <= 32");
+    const int want_wx = h ? h->warps_x : 0, want_wy = h ? h->warps_y : 0;
+    if (want_wx < 0 || want_wy < 0 || (want_wx ? want_wx : 1) * (want_wy ? want_wy : 1) > kMaxWarps)
+        return fail(XCORR_ERR_INVALID_HINT, "warps_x * warps_y must be 1..16");
+    const int want_s = h ? h->row_slices : 0;
+    if (want_s < 0 || want_s > H) return fail(XCORR_ERR_INVALID_HINT, "row_slices must be 0..rows");
+    const int want_combine = h ? h->combine : 0;
+    if (want_combine < 0 || want_combine > 3) return fail(XCORR_ERR_INVALID_HINT, "unknown combine mode");
+
+    static const double ty_eff[5] = {0.0, 0.55, 0.80, 0.93, 1.0};
+    for (int TY = 1; TY <= kMaxTY; ++TY) {
+        if (want_ty && TY != want_ty) continue;
+        for (int SL = 1; SL <= 32; SL *= 2) {
+            if (want_sl && SL != want_sl) continue;
+            TilePlan p{};
+            p.H = H; p.W = W; p.TY = TY; p.SL = SL; p.WX = 1; p.WY = 1; p.S = 1;
+            finish_plan(p, pm);
+            // warps of a block: all x tiles if they fit, y groups after that
+            const int cap = 8;
+            int WX = want_wx ? want_wx : largest_divisor_at_most(p.NTX, p.NTX > cap ? kMaxWarps : cap);
+            if (!want_wx && p.NTX > kMaxWarps) WX = largest_divisor_at_most(p.NTX, kMaxWarps);
+            int WY = want_wy ? want_wy : largest_divisor_at_most(p.NGY, std::max(1, cap / WX));
+            if (WX * WY > kMaxWarps) continue;
+            p.WX = WX; p.WY = WY;
+
+            // Estimated time = executed multiply-adds of the busiest SM / SM rate, bounded
+            // below by one warp's serial issue time, + cost of combining row slices.
+            // Automatic plans only use combinations that are bit-reproducible: one slice
+            // (plain stores), two slices (two commuting atomic adds onto zero) or any
+            // number through the workspace (fixed-order reduction).
+            const double npairs = (double)pm.n_left * pm.m;
+            const double out_bytes = npairs * (2.0 * H - 1) * (2.0 * W - 1) * 4.0;
+            const double sm_rate = 128.0 * 1.8e9 * 0.8 * ty_eff[TY];
+            const int s_lo = want_s ? want_s : 1;
+            const int s_hi = want_s ? want_s : std::min(H, 64);
+            for (int S = s_lo; S <= s_hi; ++S) {
+                p.S = S;
+                finish_plan(p, pm);
+                if (p.smem_bytes > dev.smem_optin) continue;
+                const double tasks = (double)pm.n_left * p.RG * p.CX * p.CY * S;
+                if (tasks > 2147483647.0) continue;
+                const double rs = (double)H / S;
+                const double macs_per_block = (double)p.threads * rs * p.Wp * TY * kTX;
+                const double busiest = std::ceil(tasks / dev.sm_count);
+                // resident warps per SM (128 registers per thread, 1 KB of shared memory
+                // reserved per block): below ~12 the FFMA pipe idles on shared-memory latency
+                const int by_smem = (int)((dev.smem_optin + 1024) / (p.smem_bytes + 1024));
+                const int by_regs = 65536 / (128 * p.threads);
+                const int resident = std::max(1, std::min(by_smem, by_regs)) * (p.threads / 32);
+                const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident);
+                // shared-memory wavefronts per 8-step chunk against its FFMA issue slots
+                const double wavefronts = 2.0 * TY * std::max(1, p.SL / 8) + 2.0 * std::max(1, p.ML / 8);
+                const double smem_util = 4.0 * wavefronts / (64.0 * TY);
+                const double smem_eff = 1.0 / (1.0 + std::max(0.0, smem_util - 0.4));
+                const double t_rate = busiest * macs_per_block / (sm_rate * occ_eff * smem_eff) * (rs + 0.25) / rs;
+                // one warp issues at most one FFMA per clock: a lower bound for tiny inputs
+                const double t_serial = rs * p.NTX * (64.0 * TY) / 1.8e9;
+                int comb = want_combine;
+                if (comb == XCORR_COMBINE_AUTO) comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
+                // a memset or a second kernel in front of / behind the main one costs a few us
+                double t_combine = 0.0;
+                if (comb == kAtomic) t_combine = 2e-6 + out_bytes / 3e12 + S * out_bytes / 1.5e12;
+                else if (comb == kWorkspace) t_combine = 3e-6 + (2.0 * S + 1.0) * out_bytes / 3e12;
+                const double t = std::max(t_rate, t_serial) + t_combine;
+                const double score = 1.0 / t;
+                if (score > best_score * 1.0001) {
+                    best_score = score;
+                    best = p;
+                }
+            }
+        }
+    }
+    if (best_score < 0.0)
+        return fail(XCORR_ERR_UNSUPPORTED, "no tile plan fits in shared memory for this shape / these hints");
+
+    const unsigned long long total_out = (unsigned long long)pm.n_left * pm.m *
+                                         (2ull * H - 1) * (2ull * W - 1);
+    if (best.S == 1) {
+        if (want_combine == XCORR_COMBINE_ATOMIC) best.combine = kAtomic;
+        else if (want_combine == XCORR_COMBINE_WORKSPACE) best.combine = kWorkspace;
+        else best.combine = kStore;
+    } else {
+        if (want_combine == XCORR_COMBINE_STORE)
+            return fail(XCORR_ERR_INVALID_HINT, "combine=store needs row_slices=1");
+        if (want_combine == XCORR_COMBINE_ATOMIC) best.combine = kAtomic;
+        else if (want_combine == XCORR_COMBINE_WORKSPACE) best.combine = kWorkspace;
+        // two addends onto a zeroed word commute: atomics stay bit-reproducible
+        else best.combine = best.S == 2 ? kAtomic : kWorkspace;
+    }
+    best.workspace_bytes = best.combine == kWorkspace ? (size_t)best.S * total_out * sizeof(float) : 0;
+    best.grid = (unsigned)((unsigned long long)pm.n_left * best.RG * best.CX * best.CY * best.S);
+    *out = best;
+    return XCORR_OK;
+}
+
+int pick_kernel(const xcorr_hints* h) {
+    const int k = h ? h->kernel : XCORR_KERNEL_AUTO;
+    return k == XCORR_KERNEL_AUTO ? XCORR_KERNEL_TILE : k;
+}
+
+xcorr_status check_sizes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                         PairMap* pm) {
+    if (rows == 0 || cols == 0) return fail(XCORR_ERR_INVALID_SIZE, "rows and cols must be positive");
+    if (rows > 16384 || cols > 16384) return fail(XCORR_ERR_INVALID_SIZE, "rows and cols are limited to 16384");
+    if (!pair_map(mode, n_left, n_right, pm))
+        return fail(XCORR_ERR_INVALID_SIZE, "matrix counts do not fit the mode "
+                    "(one_to_one 1x1, one_to_many 1xN, n_to_mn N x k*N, n_to_m NxM)");
+    return XCORR_OK;
+}
+
+std::string describe_plan(const TilePlan& p) {
+    char buf[512];
+    std::snprintf(buf, sizeof buf,
+                  "kernel=tile<TY=%d> grid=(%u,1,1) block=(%d,1,1) smem=%zu plan{H=%d W=%d Hp=%d Wp=%d SL=%d ML=%d "
+                  "WX=%d WY=%d CX=%d CY=%d RG=%d S=%d nstage=%d combine=%s workspace=%zu}",
+                  p.TY, p.grid, p.threads, p.smem_bytes, p.H, p.W, p.Hp, p.Wp, p.SL, p.ML, p.WX, p.WY,
+                  p.CX, p.CY, p.RG, p.S, p.nstage,
+                  p.combine == kStore ? "store" : p.combine == kAtomic ? "atomic" : "workspace",
+                  p.workspace_bytes);
+    return buf;
+}
+
+xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right, float* d_out,
+                        uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                        const xcorr_hints* hints, void* d_ws, size_t ws_bytes, void* stream_v) {
+    if (!d_left || !d_right || !d_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+    PairMap pm{};
+    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+    if (st != XCORR_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int H = (int)rows, W = (int)cols;
+    const unsigned long long npairs = (unsigned long long)pm.n_left * pm.m;
+    const unsigned long long total_out = npairs * (2ull * H - 1) * (2ull * W - 1);
+    DeviceInfo dev;
+    st = current_device_info(&dev);
+    if (st != XCORR_OK) return st;
+
+    const int kernel = pick_kernel(hints);
+    const int bt = hints && hints->block_threads ? hints->block_threads : 256;
+    if (bt < 32 || bt > 1024 || bt % 32 != 0)
+        return fail(XCORR_ERR_INVALID_HINT, "block_threads must be a multiple of 32 in 32..1024");
+    char buf[256];
+    if (kernel == XCORR_KERNEL_OVERLAP_WISE) {
+        dim3 g, b;
+        XC_CUDA(launch_overlap_wise(d_left, d_right, d_out, H, W, pm, npairs, bt, &g, &b, stream));
+        std::snprintf(buf, sizeof buf, "kernel=overlap_wise grid=(%u,%u,%u) block=(%u,%u,1) smem=0", g.x, g.y, g.z, b.x, b.y);
+        t_last_launch = buf;
+        ++t_launch_count;
+        return XCORR_OK;
+    }
+    if (kernel == XCORR_KERNEL_WARP_PER_OVERLAP) {
+        dim3 g, b;
+        XC_CUDA(launch_warp_per_overlap(d_left, d_right, d_out, H, W, pm, npairs, bt, dev.sm_count, &g, &b, stream));
+        std::snprintf(buf, sizeof buf, "kernel=warp_per_overlap grid=(%u,1,1) block=(%u,1,1) smem=0", g.x, b.x);
+        t_last_launch = buf;
+        ++t_launch_count;
+        return XCORR_OK;
+    }
+    if (kernel != XCORR_KERNEL_TILE) return fail(XCORR_ERR_INVALID_HINT, "unknown kernel family");
+
+    TilePlan p{};
+    st = plan_tile(pm, H, W, hints, dev, &p);
+    if (st != XCORR_OK) return st;
+    if (p.combine == kWorkspace) {
+        const bool explicit_ws = hints && hints->combine == XCORR_COMBINE_WORKSPACE;
+        if (!d_ws || ws_bytes < p.workspace_bytes) {
+            if (explicit_ws)
+                return fail(XCORR_ERR_WORKSPACE, "combine=workspace needs xcorr_workspace_bytes() bytes of workspace");
+            // automatic plan without (enough) workspace: fall back to atomics
+            p.combine = kAtomic;
+            p.workspace_bytes = 0;
+        } else if (reinterpret_cast<uintptr_t>(d_ws) % 16 != 0) {
+            return fail(XCORR_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+        }
+    }
+    TileArgs a{};
+    a.left = d_left; a.right = d_right; a.out = d_out;
+    a.ws = p.combine == kWorkspace ? static_cast<float*>(d_ws) : nullptr;
+    a.p = p; a.pm = pm; a.total_out = total_out;
+    a.vec_ok = (W % 4 == 0) && reinterpret_cast<uintptr_t>(d_left) % 16 == 0 &&
+               reinterpret_cast<uintptr_t>(d_right) % 16 == 0;
+    t_last_launch = describe_plan(p);
+    if (p.combine == kAtomic) XC_CUDA(cudaMemsetAsync(d_out, 0, total_out * sizeof(float), stream));
+    XC_CUDA(launch_tile(a, stream));
+    ++t_launch_count;
+    if (p.combine == kWorkspace) {
+        XC_CUDA(launch_reduce_partials(a.ws, d_out, total_out, H, W, p.Hp, p.S, dev.sm_count, stream));
+        ++t_launch_count;
+    }
+    return XCORR_OK;
+}
+
+// ---- host-buffer front end -------------------------------------------------------------
+struct HostCache {
+    std::mutex mutex;
+    float* d_left = nullptr;  size_t left_bytes = 0;
+    float* d_right = nullptr; size_t right_bytes = 0;
+    float* d_out = nullptr;   size_t out_bytes = 0;
+    void* d_ws = nullptr;     size_t ws_bytes = 0;
+    cudaStream_t stream = nullptr;
+};
+HostCache g_host_cache[kMaxDevices];
+
+template<typename T>
+xcorr_status grow(T** ptr, size_t* have, size_t need) {
+    if (need <= *have) return XCORR_OK;
+    if (*ptr) XC_CUDA(cudaFree(*ptr));
+    *ptr = nullptr; *have = 0;
+    XC_CUDA(cudaMalloc(reinterpret_cast<void**>(ptr), need));
+    *have = need;
+    return XCORR_OK;
+}
+
+xcorr_status run_host(int32_t mode, const float* h_left, const float* h_right, float* h_out,
+                      uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                      const xcorr_hints* hints, int32_t device) {
+    if (!h_left || !h_right || !h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+    PairMap pm{};
+    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+    if (st != XCORR_OK) return st;
+    int ndev = 0;
+    XC_CUDA(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev || device >= kMaxDevices) return fail(XCORR_ERR_DEVICE, "no such CUDA device");
+    XC_CUDA(cudaSetDevice(device));
+    HostCache& c = g_host_cache[device];
+    std::lock_guard<std::mutex> lock(c.mutex);
+    if (!c.stream) XC_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    const size_t in_elems = (size_t)rows * cols;
+    const size_t out_elems = (size_t)(2 * rows - 1) * (2 * cols - 1);
+    const size_t lbytes = in_elems * n_left * sizeof(float);
+    const size_t rbytes = in_elems * n_right * sizeof(float);
+    const size_t obytes = out_elems * (size_t)pm.n_left * pm.m * sizeof(float);
+    if ((st = grow(&c.d_left, &c.left_bytes, lbytes)) != XCORR_OK) return st;
+    if ((st = grow(&c.d_right, &c.right_bytes, rbytes)) != XCORR_OK) return st;
+    if ((st = grow(&c.d_out, &c.out_bytes, obytes)) != XCORR_OK) return st;
+    const size_t wsb = xcorr_workspace_bytes(mode, rows, cols, n_left, n_right, hints);
+    if ((st = grow(&c.d_ws, &c.ws_bytes, wsb)) != XCORR_OK) return st;
+    XC_CUDA(cudaMemcpyAsync(c.d_left, h_left, lbytes, cudaMemcpyHostToDevice, c.stream));
+    XC_CUDA(cudaMemcpyAsync(c.d_right, h_right, rbytes, cudaMemcpyHostToDevice, c.stream));
+    st = run_device(mode, c.d_left, c.d_right, c.d_out, rows, cols, n_left, n_right, hints,
+                    c.d_ws, c.ws_bytes, c.stream);
+    if (st != XCORR_OK) return st;
+    XC_CUDA(cudaMemcpyAsync(h_out, c.d_out, obytes, cudaMemcpyDeviceToHost, c.stream));
+    XC_CUDA(cudaStreamSynchronize(c.stream));
+    return XCORR_OK;
+}
+
+}  // namespace
+
+// ============================================================================================
+extern "C" {
+
+xcorr_status xcorr_run_f32(int32_t mode, const float* d_left, const float* d_right, float* d_out,
+                           uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                           const xcorr_hints* hints, void* d_workspace, size_t workspace_bytes, void* stream) {
+    return run_device(mode, d_left, d_right, d_out, rows, cols, n_left, n_right, hints,
+                      d_workspace, workspace_bytes, stream);
+}
+
+xcorr_status xcorr_one_to_one_f32(const float* d_left, const float* d_right, float* d_out,
+                                  uint32_t rows, uint32_t cols, const xcorr_hints* hints,
+                                  void* d_workspace, size_t workspace_bytes, void* stream) {
+    return run_device(XCORR_ONE_TO_ONE, d_left, d_right, d_out, rows, cols, 1, 1, hints,
+                      d_workspace, workspace_bytes, stream);
+}
+
+xcorr_status xcorr_one_to_many_f32(const float* d_left, const float* d_right, float* d_out,
+                                   uint32_t rows, uint32_t cols, uint32_t n_right, const xcorr_hints* hints,
+                                   void* d_workspace, size_t workspace_bytes, void* stream) {
+    return run_device(XCORR_ONE_TO_MANY, d_left, d_right, d_out, rows, cols, 1, n_right, hints,
+                      d_workspace, workspace_bytes, stream);
+}
+
+xcorr_status xcorr_n_to_mn_f32(const float* d_left, const float* d_right, float* d_out,
+                               uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                               const xcorr_hints* hints, void* d_workspace, size_t workspace_bytes, void* stream) {
+    return run_device(XCORR_N_TO_MN, d_left, d_right, d_out, rows, cols, n_left, n_right, hints,
+                      d_workspace, workspace_bytes, stream);
+}
+
+xcorr_status xcorr_n_to_m_f32(const float* d_left, const float* d_right, float* d_out,
+                              uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                              const xcorr_hints* hints, void* d_workspace, size_t workspace_bytes, void* stream) {
+    return run_device(XCORR_N_TO_M, d_left, d_right, d_out, rows, cols, n_left, n_right, hints,
+                      d_workspace, workspace_bytes, stream);
+}
+
+size_t xcorr_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                             const xcorr_hints* hints) {
+    PairMap pm{};
+    if (check_sizes(mode, rows, cols, n_left, n_right, &pm) != XCORR_OK) return 0;
+    if (pick_kernel(hints) != XCORR_KERNEL_TILE) return 0;
+    DeviceInfo dev;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0 || current_device_info(&dev) != XCORR_OK) {
+        (void)cudaGetLastError();
+        dev = assumed_device();
+    }
+    TilePlan p{};
+    if (plan_tile(pm, (int)rows, (int)cols, hints, dev, &p) != XCORR_OK) return 0;
+    return p.workspace_bytes;
+}
+
+int32_t xcorr_describe_plan(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                            const xcorr_hints* hints, char* buffer, size_t buffer_bytes) {
+    if (!buffer || buffer_bytes == 0) return fail(XCORR_ERR_NULL_POINTER, "buffer must not be NULL");
+    PairMap pm{};
+    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+    if (st != XCORR_OK) return st;
+    std::string text;
+    const int kernel = pick_kernel(hints);
+    if (kernel == XCORR_KERNEL_OVERLAP_WISE) text = "kernel=overlap_wise";
+    else if (kernel == XCORR_KERNEL_WARP_PER_OVERLAP) text = "kernel=warp_per_overlap";
+    else if (kernel == XCORR_KERNEL_TILE) {
+        DeviceInfo dev;
+        int ndev = 0;
+        if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0 || current_device_info(&dev) != XCORR_OK) {
+            (void)cudaGetLastError();
+            dev = assumed_device();
+        }
+        TilePlan p{};
+        st = plan_tile(pm, (int)rows, (int)cols, hints, dev, &p);
+        if (st != XCORR_OK) return st;
+        text = describe_plan(p);
+    } else {
+        return fail(XCORR_ERR_INVALID_HINT, "unknown kernel family");
+    }
+    std::snprintf(buffer, buffer_bytes, "%s", text.c_str());
+    return XCORR_OK;
+}
+
+uint64_t xcorr_num_results(int32_t mode, uint32_t n_left, uint32_t n_right) {
+    PairMap pm{};
+    if (!pair_map(mode, n_left, n_right, &pm)) return 0;
+    return (uint64_t)pm.n_left * pm.m;
+}
+
+int32_t xcorr_validate_input_size(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right) {
+    PairMap pm{};
+    return rows > 0 && cols > 0 && pair_map(mode, n_left, n_right, &pm) ? 1 : 0;
+}
+
+xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, const float* h_right, float* h_out,
+                                uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                const xcorr_hints* hints, int32_t device) {
+    return run_host(mode, h_left, h_right, h_out, rows, cols, n_left, n_right, hints, device);
+}
+
+void xcorr_shard_range(uint32_t units, int32_t parts, int32_t index, uint32_t* first, uint32_t* count) {
+    if (parts <= 0 || index < 0 || index >= parts) {
+        if (first) *first = 0;
+        if (count) *count = 0;
+        return;
+    }
+    const uint64_t lo = (uint64_t)units * (uint64_t)index / (uint64_t)parts;
+    const uint64_t hi = (uint64_t)units * (uint64_t)(index + 1) / (uint64_t)parts;
+    if (first) *first = (uint32_t)lo;
+    if (count) *count = (uint32_t)(hi - lo);
+}
+
+xcorr_status xcorr_run_host_sharded_f32(int32_t mode, const float* h_left, const float* h_right, float* h_out,
+                                        uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                        const xcorr_hints* hints, const int32_t* devices, int32_t n_devices) {
+    if (!h_left || !h_right || !h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+    PairMap pm{};
+    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+    if (st != XCORR_OK) return st;
+    if (n_devices <= 0 || n_devices > kMaxDevices) return fail(XCORR_ERR_DEVICE, "n_devices must be 1..64");
+    std::vector<int32_t> devs(n_devices);
+    for (int i = 0; i < n_devices; ++i) devs[i] = devices ? devices[i] : i;
+    if (mode == XCORR_ONE_TO_ONE || n_devices == 1)
+        return run_host(mode, h_left, h_right, h_out, rows, cols, n_left, n_right, hints, devs[0]);
+
+    const size_t in_elems = (size_t)rows * cols;
+    const size_t out_elems = (size_t)(2 * rows - 1) * (2 * cols - 1);
+    const uint32_t units = mode == XCORR_ONE_TO_MANY ? n_right : n_left;
+    std::vector<xcorr_status> status(n_devices, XCORR_OK);
+    std::vector<std::string> errors(n_devices);
+    std::vector<std::thread> workers;
+    for (int i = 0; i < n_devices; ++i) {
+        uint32_t first = 0, count = 0;
+        xcorr_shard_range(units, n_devices, i, &first, &count);
+        if (count == 0) continue;
+        workers.emplace_back([&, i, first, count]() {
+            const float* l = h_left;
+            const float* r = h_right;
+            float* o = h_out;
+            uint32_t nl = n_left, nr = n_right;
+            if (mode == XCORR_ONE_TO_MANY) {           // a block of right matrices
+                r += (size_t)first * in_elems;
+                o += (size_t)first * out_elems;
+                nr = count;
+            } else if (mode == XCORR_N_TO_M) {          // a block of left matrices, all rights
+                l += (size_t)first * in_elems;
+                o += (size_t)first * pm.m * out_elems;
+                nl = count;
+            } else {                                    // n_to_mn: lefts with their own m rights
+                l += (size_t)first * in_elems;
+                r += (size_t)first * pm.m * in_elems;
+                o += (size_t)first * pm.m * out_elems;
+                nl = count;
+                nr = count * pm.m;
+            }
+            status[i] = run_host(mode, l, r, o, rows, cols, nl, nr, hints, devs[i]);
+            if (status[i] != XCORR_OK) errors[i] = t_last_error;
+        });
+    }
+    for (auto& w : workers) w.join();
+    for (int i = 0; i < n_devices; ++i)
+        if (status[i] != XCORR_OK) return fail(status[i], "shard " + std::to_string(i) + ": " + errors[i]);
+    return XCORR_OK;
+}
+
+void xcorr_release_host_cache(void) {
+    int prev = 0;
+    if (cudaGetDevice(&prev) != cudaSuccess) { (void)cudaGetLastError(); return; }
+    for (int d = 0; d < kMaxDevices; ++d) {
+        HostCache& c = g_host_cache[d];
+        std::lock_guard<std::mutex> lock(c.mutex);
+        if (!c.d_left && !c.d_right && !c.d_out && !c.d_ws && !c.stream) continue;
+        if (cudaSetDevice(d) != cudaSuccess) { (void)cudaGetLastError(); continue; }
+        if (c.d_left) cudaFree(c.d_left);
+        if (c.d_right) cudaFree(c.d_right);
+        if (c.d_out) cudaFree(c.d_out);
+        if (c.d_ws) cudaFree(c.d_ws);
+        if (c.stream) cudaStreamDestroy(c.stream);
+        c.d_left = c.d_right = c.d_out = nullptr;
+        c.d_ws = nullptr;
+        c.left_bytes = c.right_bytes = c.out_bytes = c.ws_bytes = 0;
+        c.stream = nullptr;
+    }
+    cudaSetDevice(prev);
+}
+
+xcorr_status xcorr_n_to_mn_reorder_f32(const float* src, float* dst, uint32_t n_left, uint32_t n_total,
+                                       size_t elems, int32_t to_grouped) {
+    if (!src || !dst) return fail(XCORR_ERR_NULL_POINTER, "src and dst must not be NULL");
+    if (n_left == 0 || n_total % n_left != 0) return fail(XCORR_ERR_INVALID_SIZE, "n_total must be a multiple of n_left");
+    const uint32_t m = n_total / n_left;
+    for (uint32_t i = 0; i < n_total; ++i) {
+        // file index i = t*n_left + l  <->  grouped index l*m + t
+        const uint32_t l = i % n_left, t = i / n_left;
+        const uint32_t g = l * m + t;
+        if (to_grouped) std::memcpy(dst + (size_t)g * elems, src + (size_t)i * elems, elems * sizeof(float));
+        else            std::memcpy(dst + (size_t)i * elems, src + (size_t)g * elems, elems * sizeof(float));
+    }
+    return XCORR_OK;
+}
+
+const char* xcorr_last_launch_string(void) { return t_last_launch.c_str(); }
+const char* xcorr_last_error_string(void) { return t_last_error.c_str(); }
+
+const char* xcorr_status_string(int32_t status) {
+    switch (status) {
+    case XCORR_OK: return "ok";
+    case XCORR_ERR_NULL_POINTER: return "null pointer";
+    case XCORR_ERR_INVALID_SIZE: return "invalid size";
+    case XCORR_ERR_INVALID_HINT: return "invalid hint";
+    case XCORR_ERR_WORKSPACE: return "workspace missing or too small";
+    case XCORR_ERR_CUDA: return "CUDA error";
+    case XCORR_ERR_UNSUPPORTED: return "unsupported shape";
+    case XCORR_ERR_DEVICE: return "bad device";
+    case XCORR_ERR_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+    }
+}
+
+uint64_t xcorr_launch_count(void) { return t_launch_count; }
+void xcorr_reset_launch_count(void) { t_launch_count = 0; }
+
+xcorr_status xcorr_ffma_peak_probe(double* flops_per_second, double* kernel_ms, void* stream_v) {
+    if (!flops_per_second) return fail(XCORR_ERR_NULL_POINTER, "flops_per_second must not be NULL");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    DeviceInfo dev;
+    xcorr_status st = current_device_info(&dev);
+    if (st != XCORR_OK) return st;
+    float* sink = nullptr;
+    XC_CUDA(cudaMalloc(&sink, sizeof(float)));
+    cudaEvent_t e0, e1;
+    XC_CUDA(cudaEventCreate(&e0));
+    XC_CUDA(cudaEventCreate(&e1));
+    const int blocks = dev.sm_count * 2, iters = 4096;
+    double best_ms = 1e30;
+    for (int rep = 0; rep < 4; ++rep) {            // first repetition is the warm-up
+        XC_CUDA(cudaEventRecord(e0, stream));
+        XC_CUDA(launch_ffma_probe(sink, iters, blocks, stream));
+        XC_CUDA(cudaEventRecord(e1, stream));
+        XC_CUDA(cudaEventSynchronize(e1));
+        float ms = 0.f;
+        XC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        if (rep > 0 && ms < best_ms) best_ms = ms;
+        ++t_launch_count;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(sink);
+    const double flop = 2.0 * 16.0 * 8.0 * (double)iters * 1024.0 * (double)blocks;
+    *flops_per_second = flop / (best_ms * 1e-3);
+    if (kernel_ms) *kernel_ms = best_ms;
+    return XCORR_OK;
+}
+
+}  // extern "C"

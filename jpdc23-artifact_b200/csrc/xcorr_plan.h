@@ -1,0 +1,74 @@
+// Launch plan of the register-tiled circular-class kernel, shared by the planner (host),
+// the launcher and the kernel itself.
+//
+// Circular classes.  Pad the matrices with zeros to Hp x Wp.  For a class
+// (cy, cx) in [0,Hp) x [0,Wp) accumulate, over every right element (ry, rx),
+//     left[(ry + cy) mod Hp][(rx + cx) mod Wp] * right[ry][rx].
+// Every product of the true cross-correlation appears in exactly one class, and within a
+// class the terms split by whether the row / column index wrapped:
+//     no x wrap -> shift sx = cx          x wrap -> shift sx = cx - Wp
+//     no y wrap -> shift sy = cy          y wrap -> shift sy = cy - Hp
+// so one class feeds (up to) four outputs and costs exactly Hp*Wp multiply-adds whatever
+// the shift: no overlap clamping in the inner loop, no idle lanes at the corners, and the
+// total is Hp^2*Wp^2 -- the algorithmic W^2*H^2 when no padding is needed.  This replaces
+// the reference's zero-filled out-of-range loads (bound_checked_loads.cuh:23-25) and its
+// startup / wind-down ladders (naive_shuffle_multirow_both.cu:244-292).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace xcorr {
+
+constexpr int kTX = 8;            // x classes per thread (one 8-wide tile, two float4)
+constexpr int kMaxTY = 4;         // y classes per thread
+constexpr int kMaxWarps = 16;     // warps per block
+constexpr int kSmemLimit = 227 * 1024;
+
+enum Combine : int { kStore = 1, kAtomic = 2, kWorkspace = 3 };
+
+// How the pairs of a mode are enumerated: left l in [0, n_left) meets rights
+// l*right_stride + j, j in [0, m); the result matrix is l*m + j.
+//   one_to_one   n_left=1 m=1        one_to_many  n_left=1 m=n_right
+//   n_to_m       m=n_right stride=0  n_to_mn      m=n_right/n_left stride=m
+struct PairMap {
+    uint32_t n_left;
+    uint32_t m;
+    uint32_t right_stride;
+};
+
+struct TilePlan {
+    int H, W;          // true size
+    int Hp, Wp;        // padded size: Wp multiple of 8, Hp multiple of SL*TY
+    int TY;            // y classes per thread (template parameter of the kernel)
+    int SL, ML;        // lanes over y classes / lanes over right matrices, SL*ML = 32
+    int logSL;
+    int NTX;           // x-class tiles = Wp / 8
+    int NGY;           // y-class groups = Hp / (SL*TY)
+    int WX, WY;        // warps of a block along x tiles / y groups
+    int CX, CY;        // blocks needed along x tiles / y groups
+    int S;             // row slices of the right matrices
+    int RSmax;         // rows of the longest slice
+    int RG;            // right-matrix groups per left = ceil(m / ML)
+    int nstage;        // left rows staged in shared memory
+    int LS;            // floats between staged left rows (Wp + 4: row*LS/4 odd -> conflict-free float4)
+    int RMS;           // floats between the staged right matrices of one block
+    int threads;
+    int combine;       // Combine
+    unsigned grid;
+    size_t smem_bytes;
+    size_t workspace_bytes;
+};
+
+// Kernel arguments (passed by value).
+struct TileArgs {
+    const float* left;
+    const float* right;
+    float* out;
+    float* ws;         // partial images, S * total_out floats (kWorkspace) or nullptr
+    TilePlan p;
+    PairMap pm;
+    int vec_ok;        // rows may be fetched with 16-byte loads
+    unsigned long long total_out;  // floats in the whole output array
+};
+
+}  // namespace xcorr

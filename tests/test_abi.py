@@ -1,0 +1,113 @@
+"""CPU tests of the C-ABI library: it loads, exports every symbol include/xcorr.h declares,
+and its host-only entry points (planning, shard ranges, order helpers, argument checks that
+fail before any CUDA call) behave.  No kernel runs here."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import file_to_grouped, grouped_to_file
+
+
+def declared_symbols(header_path):
+    text = open(header_path).read()
+    return sorted(set(re.findall(r"XCORR_API[^;(]*?\b(xcorr_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(xc):
+    names = declared_symbols(xc.HEADER_PATH)
+    assert len(names) >= 19
+    lib = C.CDLL(xc.LIB_PATH)
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_hints_struct_layout(xc):
+    assert C.sizeof(xc.Hints) == 16 * 4
+
+
+def test_status_strings(xc):
+    lib = xc.lib()
+    assert lib.xcorr_status_string(0) == b"ok"
+    assert lib.xcorr_status_string(2) == b"invalid size"
+    assert lib.xcorr_status_string(99) == b"unknown status"
+
+
+def test_num_results_and_input_rules(xc):
+    lib = xc.lib()
+    # one_to_one.hpp:20-22, one_to_many.hpp:15-17, n_to_mn.hpp:23-25, n_to_m.hpp:19-21
+    assert lib.xcorr_validate_input_size(0, 16, 16, 1, 1) == 1
+    assert lib.xcorr_validate_input_size(0, 16, 16, 1, 2) == 0
+    assert lib.xcorr_validate_input_size(0, 0, 16, 1, 1) == 0
+    assert lib.xcorr_validate_input_size(1, 4, 4, 1, 7) == 1
+    assert lib.xcorr_validate_input_size(1, 4, 4, 2, 7) == 0
+    assert lib.xcorr_validate_input_size(2, 4, 4, 3, 9) == 1
+    assert lib.xcorr_validate_input_size(2, 4, 4, 3, 10) == 0
+    assert lib.xcorr_validate_input_size(3, 4, 4, 3, 10) == 1
+    assert lib.xcorr_validate_input_size(7, 4, 4, 1, 1) == 0
+    assert lib.xcorr_num_results(0, 1, 1) == 1
+    assert lib.xcorr_num_results(1, 1, 512) == 512
+    assert lib.xcorr_num_results(2, 16, 2048) == 2048
+    assert lib.xcorr_num_results(3, 32, 64) == 2048
+    assert lib.xcorr_num_results(2, 16, 2047) == 0
+
+
+def test_shard_ranges_partition_the_units(xc):
+    for units, parts in [(512, 8), (16, 8), (32, 3), (5, 8), (1, 2), (2048, 7)]:
+        covered = []
+        sizes = []
+        for i in range(parts):
+            first, count = xc.shard_range(units, parts, i)
+            covered.extend(range(first, first + count))
+            sizes.append(count)
+        assert covered == list(range(units))
+        assert max(sizes) - min(sizes) <= 1
+    assert xc.shard_range(10, 0, 0) == (0, 0)
+    assert xc.shard_range(10, 4, 4) == (0, 0)
+
+
+def test_n_to_mn_reorder_matches_reference_index(xc, oracle):
+    n, m, elems = 3, 4, 6
+    a = np.arange(n * m * elems, dtype=np.float32).reshape(n * m, 2, 3)
+    g = xc.n_to_mn_reorder(a, n, True)
+    for i in range(n * m):
+        assert np.array_equal(g[oracle.interleaved_index(i, n, m)], a[i])   # matrix.hpp:614-618
+    assert np.array_equal(xc.n_to_mn_reorder(g, n, False), a)
+    assert np.array_equal(g, file_to_grouped(a, n))
+    assert np.array_equal(grouped_to_file(g, n), a)
+    with pytest.raises(xc.XcorrError):
+        xc.n_to_mn_reorder(a[:5], 3, True)
+
+
+def test_workspace_planning_without_a_device(xc):
+    # config 2 (one pair of 256x256) needs a row split over ~all SMs -> partial images
+    big = xc.workspace_bytes("one_to_one", 256, 256, 1, 1)
+    out_bytes = 511 * 511 * 4
+    assert big > 0 and big % out_bytes == 0 and 8 <= big // out_bytes <= 64
+    # many independent pairs fill the GPU without a row split or with two slices: no workspace
+    assert xc.workspace_bytes("one_to_many", 64, 64, 1, 512) == 0
+    assert xc.workspace_bytes("n_to_m", 32, 32, 32, 64) == 0
+    # explicit hints
+    h = xc.make_hints(kernel="tile", combine="workspace", row_slices=4)
+    assert xc.workspace_bytes("one_to_one", 16, 16, 1, 1, h) == 4 * 31 * 31 * 4
+    assert xc.workspace_bytes("one_to_one", 16, 16, 1, 1, xc.make_hints(kernel="overlap_wise")) == 0
+    # invalid shapes plan nothing
+    assert xc.workspace_bytes("n_to_mn", 16, 16, 3, 10) == 0
+
+
+def test_argument_errors_come_back_as_status_codes(xc):
+    lib = xc.lib()
+    # NULL pointers and bad counts are rejected before any CUDA call
+    assert lib.xcorr_one_to_one_f32(None, None, None, 4, 4, None, None, 0, None) == 1
+    buf = np.zeros(64, np.float32)
+    p = buf.ctypes.data
+    assert lib.xcorr_run_f32(2, p, p, p, 4, 4, 3, 10, None, None, 0, None) == 2
+    assert lib.xcorr_run_f32(0, p, p, p, 0, 4, 1, 1, None, None, 0, None) == 2
+    assert lib.xcorr_run_f32(9, p, p, p, 4, 4, 1, 1, None, None, 0, None) == 2
+    assert lib.xcorr_run_host_f32(0, None, p, p, 4, 4, 1, 1, None, 0) == 1
+    assert b"NULL" in lib.xcorr_last_error_string()
+    assert lib.xcorr_run_host_sharded_f32(1, p, p, p, 4, 4, 1, 2, None, None, 0) == 7
+    assert lib.xcorr_n_to_mn_reorder_f32(None, p, 1, 1, 1, 1) == 1
+    assert lib.xcorr_ffma_peak_probe(None, None, None) == 1
