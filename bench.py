@@ -254,7 +254,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--only", default="", help="comma-separated subset of C1..C5 (profiling runs; "
+                    "the default line always covers all five)")
     args = ap.parse_args()
+    if args.only:
+        keep = [k.strip() for k in args.only.split(",") if k.strip()]
+        for k in list(CONFIGS):
+            if k not in keep:
+                del CONFIGS[k]
+        if not CONFIGS:
+            raise SystemExit("--only selected no configuration")
     if args.impl == "reference":
         return run_reference_arm(args)
 
@@ -387,7 +396,8 @@ def main():
     for _ in range(e2e_steps):
         e2e_pass()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    checksum = float(host["C5"][2][0, 47, 47])   # a device result read on the host
+    last = list(CONFIGS)[-1]
+    checksum = float(host[last][2].reshape(-1)[0])   # a device result read on the host
     barrier()
 
     # ---- FFMA peak of this GPU, measured now
