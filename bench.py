@@ -256,6 +256,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--only", default="", help="comma-separated subset of C1..C5 (profiling runs; "
                     "the default line always covers all five)")
+    ap.add_argument("--hints", default="", help='JSON {"C3": {"overlap_rows": 4, ...}}: force plan hints of '
+                    "a configuration (profiling and tuning runs; the default line uses automatic plans)")
     args = ap.parse_args()
     if args.only:
         keep = [k.strip() for k in args.only.split(",") if k.strip()]
@@ -284,11 +286,13 @@ def main():
     warmup = max(3, args.warmup)
     stream = torch.cuda.current_stream().cuda_stream
 
+    forced = {k: xc.make_hints(kernel="tile", **v) for k, v in (json.loads(args.hints) if args.hints else {}).items()}
+
     # ---- resident inputs, outputs, workspaces
     dev = {}
     for k, (mode, r, c, nl, nr) in CONFIGS.items():
         left, right = config_inputs(k, rank)
-        wsb = xc.workspace_bytes(mode, r, c, nl, nr)
+        wsb = xc.workspace_bytes(mode, r, c, nl, nr, forced.get(k))
         dev[k] = dict(
             left=torch.from_numpy(left).cuda(), right=torch.from_numpy(right).cuda(),
             out=torch.empty(xc.out_shape(mode, r, c, nl, nr), dtype=torch.float32, device="cuda"),
@@ -298,7 +302,7 @@ def main():
         mode, r, c, nl, nr = CONFIGS[k]
         d = dev[k]
         xc.run_device(mode, d["left"].data_ptr(), d["right"].data_ptr(), d["out"].data_ptr(), r, c, nl, nr,
-                      None, d["ws"].data_ptr() if d["wsb"] else 0, d["wsb"], stream)
+                      forced.get(k), d["ws"].data_ptr() if d["wsb"] else 0, d["wsb"], stream)
 
     def barrier():
         if world > 1:

@@ -119,6 +119,7 @@ void finish_plan(TilePlan& p, const PairMap& pm) {
     p.Wp = round_up(p.W, kTX);
     p.Hp = round_up(p.H, p.SL * p.TY);
     p.NTX = p.Wp / kTX;
+    p.NCH = p.Wp / 8;
     p.NGY = p.Hp / (p.SL * p.TY);
     p.CX = (p.NTX + p.WX - 1) / p.WX;
     p.CY = (p.NGY + p.WY - 1) / p.WY;
@@ -193,11 +194,11 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
                 const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident);
                 // shared-memory wavefronts per 8-step chunk against its FFMA issue slots
                 const double wavefronts = 2.0 * TY * std::max(1, p.SL / 8) + 2.0 * std::max(1, p.ML / 8);
-                const double smem_util = 4.0 * wavefronts / (64.0 * TY);
+                const double smem_util = 4.0 * wavefronts / (8.0 * TY * kTX);
                 const double smem_eff = 1.0 / (1.0 + std::max(0.0, smem_util - 0.4));
                 const double t_rate = busiest * macs_per_block / (sm_rate * occ_eff * smem_eff) * (rs + 0.25) / rs;
                 // one warp issues at most one FFMA per clock: a lower bound for tiny inputs
-                const double t_serial = rs * p.NTX * (64.0 * TY) / 1.8e9;
+                const double t_serial = 2.0 * rs * p.Wp * TY * kTX / 1.8e9 / 2.0;
                 int comb = want_combine;
                 if (comb == XCORR_COMBINE_AUTO) comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
                 // a memset or a second kernel in front of / behind the main one costs a few us

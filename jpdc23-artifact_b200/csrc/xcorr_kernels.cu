@@ -20,26 +20,30 @@ namespace xcorr {
 // tile kernel
 // ------------------------------------------------------------------------------------------
 //
-// Work split.  A warp owns one 8-wide tile of x classes (the same for all its lanes) and
+// Work split.  A warp owns one 16-wide tile of x classes (the same for all its lanes) and
 // SL*TY y classes: lane (m, q), q in [0,SL), holds classes cyw + q + SL*t, t in [0,TY), for
 // right matrix m of the block's group (ML = 32/SL matrices per warp).  A block is WX x WY
 // such warps sharing one left matrix, ML right matrices and one slice [r0, r1) of right
 // rows, all staged in shared memory once.
 //
-// Per right row ry the thread walks the left row's columns u = 0..Wp-1 in chunks of 8:
-//     acc[t][j] += L[(ry + cy_t) mod Hp][u] * R[ry][(u - cx0 - j) mod Wp]
-// The eight R values a step needs are a window that slides by one per step: 16 registers,
-// refilled with two 16-byte loads per chunk; the left values are two 16-byte loads per
-// y class per chunk.  TY*8 FFMA per step against (TY + 1)/4 loads: no shuffles.
+// Per right row ry the thread walks the left row's columns u in chunks of 8:
+//     acc[t][j] += L[(ry + cy_t) mod Hp][u] * R[ry][(u - cx0 - j) mod Wp],  j in [0,16)
+// The R values a chunk needs are a 23-wide window that slides by one per step; each chunk
+// refills its 8 new entries with two 16-byte loads, the left values are two 16-byte loads
+// per y class.  TY*16 FFMA per step against (TY + 1)/4 loads, and no shuffles.
 //
-// x wrap: column j of the tile has wrapped while u < cx0 + j.  Chunks before the tile's own
-// chunk are all-wrapped (accB), chunks after it all-unwrapped (accA) and the one chunk in
-// between is unrolled with the target chosen per (step, column) at compile time.
-// y wrap: class cy wraps from row ry = Hp - cy on.  The row loop flushes a class's
-// accumulators to the unwrapped output row when it reaches that row, and to the wrapped (or
-// still unwrapped) one at the end of the slice.
+// x wrap: column j has wrapped while u < cx0 + j.  Instead of two accumulator sets the
+// slice is walked twice with one set: pass B (wrapped part, output shift cx - Wp) takes the
+// chunks u < cx0 in full and the two chunks of the tile's own columns in their lower
+// triangle (step < j); pass A (unwrapped part, output shift cx) takes the upper triangle
+// (step >= j) and the chunks behind it.  Together exactly Wp multiply-adds per class and
+// row; only the tile's own two chunks are loaded twice.
+// y wrap: class cy wraps from row ry = Hp - cy on.  The row loop writes a class's sums to
+// the unwrapped output row when it reaches that row, and to the wrapped (or still
+// unwrapped) one at the end of the slice.
 
-enum ChunkType : int { kAllWrapped = 0, kMixed = 1, kNoneWrapped = 2 };
+enum Pass : int { kPassWrapped = 0, kPassUnwrapped = 1 };
+constexpr int kWin = kTX + 7;     // window entries a chunk reads
 
 // 16-byte shared-memory load through a 32-bit shared-window address (one register per
 // address instead of the two a generic pointer takes).
@@ -50,10 +54,24 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
     return v;
 }
 
-template<int TY, int TYPE>
-__device__ __forceinline__ void tile_chunk(float (&accA)[TY][kTX], float (&accB)[TY][kTX],
-                                           const float (&w)[16], const uint32_t (&lp)[TY],
-                                           uint32_t col_bytes) {
+// The 8 new window entries of a chunk: R[...] at `addr` -> w[15..22].
+__device__ __forceinline__ void window_refill(float (&w)[kWin], uint32_t addr) {
+    const float4 a0 = lds128(addr), a1 = lds128(addr + 16);
+    w[15] = a0.x; w[16] = a0.y; w[17] = a0.z; w[18] = a0.w;
+    w[19] = a1.x; w[20] = a1.y; w[21] = a1.z; w[22] = a1.w;
+}
+
+__device__ __forceinline__ void window_shift(float (&w)[kWin]) {
+#pragma unroll
+    for (int i = 0; i < kWin - 8; ++i) w[i] = w[i + 8];
+}
+
+// One chunk of 8 steps.  TRI < 0: every (step, column) pair.  TRI = 0 / 1: first / second
+// chunk of the tile's own columns, where only the pairs on the pass's side of the diagonal
+// count: step >= j for the unwrapped pass, step < j for the wrapped one.
+template<int TY, int TRI, int PASS>
+__device__ __forceinline__ void tile_chunk(float (&acc)[TY][kTX], const float (&w)[kWin],
+                                           const uint32_t (&lp)[TY], uint32_t col_bytes) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
 #pragma unroll
@@ -65,31 +83,153 @@ __device__ __forceinline__ void tile_chunk(float (&accA)[TY][kTX], float (&accB)
                 const float l = k == 0 ? lv.x : k == 1 ? lv.y : k == 2 ? lv.z : lv.w;
 #pragma unroll
                 for (int j = 0; j < kTX; ++j) {
-                    const float r = w[8 + kk - j];
-                    if (TYPE == kNoneWrapped || (TYPE == kMixed && kk >= j))
-                        accA[t][j] = fmaf(l, r, accA[t][j]);
-                    else
-                        accB[t][j] = fmaf(l, r, accB[t][j]);
+                    const int step = 8 * (TRI < 0 ? 0 : TRI) + kk;
+                    const bool take = TRI < 0 || ((step >= j) == (PASS == kPassUnwrapped));
+                    if (take) acc[t][j] = fmaf(l, w[15 + kk - j], acc[t][j]);
                 }
             }
         }
     }
 }
 
-// Write one y class's 2*8 sums (vals[0..7] unwrapped in x, vals[8..15] wrapped in x) to
-// output row `orow`.  Deliberately a rolled loop over a local-memory copy of the sums: the
-// flush runs once per class per slice, and unrolled it costs the hot loop ~90 registers.
+// All chunks of one right row for one pass.
+template<int TY, int PASS>
+__device__ __forceinline__ void tile_row(float (&acc)[TY][kTX], const uint32_t (&lp)[TY], uint32_t rrow,
+                                         int cx0, int Wp, int nchunks) {
+    float w[kWin];
+    const int cb = cx0 >> 3;                 // first chunk of the tile's own columns
+    if (PASS == kPassWrapped) {
+        // window of the first chunk: R[Wp - cx0 - 15 .. Wp - cx0 - 1]
+        uint32_t rp = rrow + (uint32_t)(Wp - cx0 - 16) * 4;
+        {
+            const float4 a0 = lds128(rp), a1 = lds128(rp + 16), a2 = lds128(rp + 32), a3 = lds128(rp + 48);
+            w[0] = a0.y; w[1] = a0.z; w[2] = a0.w;
+            w[3] = a1.x; w[4] = a1.y; w[5] = a1.z; w[6] = a1.w;
+            w[7] = a2.x; w[8] = a2.y; w[9] = a2.z; w[10] = a2.w;
+            w[11] = a3.x; w[12] = a3.y; w[13] = a3.z; w[14] = a3.w;
+        }
+        rp += 64;
+#pragma unroll 1
+        for (int c = 0; c < cb; ++c, rp += 32) {
+            window_refill(w, rp);
+            tile_chunk<TY, -1, PASS>(acc, w, lp, (uint32_t)c * 32);
+            window_shift(w);
+        }
+        // the tile's own columns, lower triangle; no new window entries are needed
+#pragma unroll
+        for (int i = 15; i < kWin; ++i) w[i] = 0.f;
+        tile_chunk<TY, 0, PASS>(acc, w, lp, (uint32_t)cb * 32);
+        window_shift(w);
+        tile_chunk<TY, 1, PASS>(acc, w, lp, (uint32_t)(cb + 1) * 32);
+    } else {
+        uint32_t rp = rrow;
+#pragma unroll
+        for (int i = 0; i < 15; ++i) w[i] = 0.f;
+        window_refill(w, rp);
+        tile_chunk<TY, 0, PASS>(acc, w, lp, (uint32_t)cb * 32);
+        window_shift(w);
+        window_refill(w, rp + 32);
+        tile_chunk<TY, 1, PASS>(acc, w, lp, (uint32_t)(cb + 1) * 32);
+        window_shift(w);
+        rp += 64;
+#pragma unroll 1
+        for (int c = cb + 2; c < nchunks; ++c, rp += 32) {
+            window_refill(w, rp);
+            tile_chunk<TY, -1, PASS>(acc, w, lp, (uint32_t)c * 32);
+            window_shift(w);
+        }
+    }
+}
+
+// Write one y class's 16 sums of one pass to output row `orow`.  Deliberately a rolled loop
+// over a local-memory copy: the flush runs once per class, pass and slice, and unrolled it
+// costs the hot loop dozens of registers.
+template<int PASS>
 __device__ __forceinline__ void tile_emit_row(float* __restrict__ dst, int orow, int OW, int W, int Wp,
                                               int cx0, const float* vals, int combine) {
     float* o = dst + (size_t)orow * OW;
 #pragma unroll 1
-    for (int j = 0; j < 2 * kTX; ++j) {
-        // j < 8: shift sx = cx0 + j; else shift sx = cx0 + (j - 8) - Wp
-        const int col = j < kTX ? cx0 + j + W - 1 : cx0 + j - kTX - Wp + W - 1;
-        const bool ok = j < kTX ? cx0 + j < W : col >= 0;
+    for (int j = 0; j < kTX; ++j) {
+        const int cx = cx0 + j;
+        // unwrapped: shift sx = cx; wrapped: shift sx = cx - Wp
+        const int col = PASS == kPassUnwrapped ? cx + W - 1 : cx - Wp + W - 1;
+        const bool ok = PASS == kPassUnwrapped ? cx < W : col >= 0;
         if (ok) {
             if (combine == kAtomic) atomicAdd(o + col, vals[j]); else o[col] = vals[j];
         }
+    }
+}
+
+// One pass over the slice's rows for one thread.
+template<int TY, int PASS>
+__device__ __forceinline__ void tile_pass(const TilePlan& p, float* __restrict__ dst, uint32_t sL_addr,
+                                          uint32_t rmat_addr, int r0, int r1, int cy0, int cya, int cx0,
+                                          bool lane_live) {
+    const int H = p.H, W = p.W, Hp = p.Hp, Wp = p.Wp;
+    const int OW = 2 * W - 1;
+    const uint32_t stage_bytes = (uint32_t)(p.nstage * p.LS * 4);
+    uint32_t lofs[TY];                        // byte offset of class t's staged left row
+#pragma unroll
+    for (int t = 0; t < TY; ++t) {
+        int i = cy0 + p.SL * t - cya;        // staged row for ry = r0
+        if (i >= p.nstage) i -= p.nstage;
+        lofs[t] = (uint32_t)(i * p.LS * 4);
+    }
+    float acc[TY][kTX];
+#pragma unroll
+    for (int t = 0; t < TY; ++t)
+#pragma unroll
+        for (int j = 0; j < kTX; ++j) acc[t][j] = 0.f;
+
+    uint32_t rrow = rmat_addr;
+#pragma unroll 1
+    for (int ry = r0; ry < r1; ++ry, rrow += (uint32_t)Wp * 4) {
+        // a class that starts wrapping at this row: its unwrapped-in-y part is complete
+        // (the wrap rows of a lane's classes differ, so at most one matches)
+        int tsel = -1;
+#pragma unroll
+        for (int t = 0; t < TY; ++t)
+            if (ry == Hp - (cy0 + p.SL * t) && ry > r0) tsel = t;
+        if (tsel >= 0) {
+            float vals[kTX];
+#pragma unroll
+            for (int t = 0; t < TY; ++t) {
+                if (t == tsel) {
+#pragma unroll
+                    for (int j = 0; j < kTX; ++j) { vals[j] = acc[t][j]; acc[t][j] = 0.f; }
+                }
+            }
+            const int cyt = cy0 + p.SL * tsel;
+            if (lane_live && cyt < H)
+                tile_emit_row<PASS>(dst, cyt + H - 1, OW, W, Wp, cx0, vals, p.combine);
+        }
+
+        uint32_t lp[TY];
+#pragma unroll
+        for (int t = 0; t < TY; ++t) lp[t] = sL_addr + lofs[t];
+        tile_row<TY, PASS>(acc, lp, rrow, cx0, Wp, p.NCH);
+#pragma unroll
+        for (int t = 0; t < TY; ++t) {
+            lofs[t] += (uint32_t)p.LS * 4;
+            if (lofs[t] == stage_bytes) lofs[t] = 0;
+        }
+    }
+
+    // end of the slice: the sums belong to the wrapped output row if the class wrapped
+    // inside (or before) the slice, else to the unwrapped one
+    if (!lane_live) return;
+    float vals[TY][kTX];
+#pragma unroll
+    for (int t = 0; t < TY; ++t)
+#pragma unroll
+        for (int j = 0; j < kTX; ++j) vals[t][j] = acc[t][j];
+#pragma unroll 1
+    for (int t = 0; t < TY; ++t) {
+        const int cyt = cy0 + p.SL * t;
+        const bool wrapped = r1 > Hp - cyt;
+        const int sy = wrapped ? cyt - Hp : cyt;
+        if (sy > -H && sy < H)
+            tile_emit_row<PASS>(dst, sy + H - 1, OW, W, Wp, cx0, vals[t], p.combine);
     }
 }
 
@@ -187,109 +327,16 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) tile_kernel(const TileArgs 
     const unsigned jright = (unsigned)rg * p.ML + m;
     const bool lane_live = jright < a.pm.m;
     const int cx0 = tile_x * kTX;
-    const int cyw = grp_y * p.SL * TY;
+    const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
 
-    const int cy0 = cyw + q;                 // class t of this lane: cy0 + SL*t
-    const int stage_bytes = p.nstage * p.LS * 4;
-    const uint32_t sL_addr = (uint32_t)__cvta_generic_to_shared(sL);
-    // byte offset (within the staged left rows) of class t's row for the current ry
-    uint32_t lofs[TY];
-#pragma unroll
-    for (int t = 0; t < TY; ++t) {
-        int i = cy0 + p.SL * t - cya;        // staged row for ry = r0; < 2*nstage
-        if (i >= p.nstage) i -= p.nstage;
-        lofs[t] = (uint32_t)(i * p.LS * 4);
-    }
-
-    float accA[TY][kTX], accB[TY][kTX];
-#pragma unroll
-    for (int t = 0; t < TY; ++t)
-#pragma unroll
-        for (int j = 0; j < kTX; ++j) { accA[t][j] = 0.f; accB[t][j] = 0.f; }
-
-    const int OW = 2 * W - 1, OH = 2 * H - 1;
     const size_t out_mat = (size_t)l * a.pm.m + jright;
     float* dst = (p.combine == kWorkspace ? a.ws + (size_t)s * a.total_out : a.out)
-                 + out_mat * (size_t)OW * OH;
+                 + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
+    const uint32_t sL_addr = (uint32_t)__cvta_generic_to_shared(sL);
+    const uint32_t rmat_addr = (uint32_t)__cvta_generic_to_shared(sR + (size_t)m * p.RMS);
 
-    const int nchunks = p.NTX;
-    const int cb = tile_x;                   // chunk in which this tile's columns wrap
-    // start of the window of the first chunk, for the slice's first row
-    uint32_t rrow = (uint32_t)__cvta_generic_to_shared(sR + (size_t)m * p.RMS) + (uint32_t)(Wp - cx0 - 8) * 4;
-
-    for (int ry = r0; ry < r1; ++ry, rrow += Wp * 4) {
-        // a class that starts wrapping at this row: its unwrapped part is complete
-        // (the wrap rows of a lane's classes differ, so at most one matches)
-        int tsel = -1;
-#pragma unroll
-        for (int t = 0; t < TY; ++t)
-            if (ry == Hp - (cy0 + p.SL * t) && ry > r0) tsel = t;
-        if (tsel >= 0) {
-            float vals[2 * kTX];
-#pragma unroll
-            for (int t = 0; t < TY; ++t) {
-                if (t == tsel) {
-#pragma unroll
-                    for (int j = 0; j < kTX; ++j) {
-                        vals[j] = accA[t][j]; vals[kTX + j] = accB[t][j];
-                        accA[t][j] = 0.f; accB[t][j] = 0.f;
-                    }
-                }
-            }
-            const int cyt = cy0 + p.SL * tsel;
-            if (lane_live && cyt < H)
-                tile_emit_row(dst, cyt + H - 1, OW, W, Wp, cx0, vals, p.combine);
-        }
-
-        uint32_t lp[TY];
-#pragma unroll
-        for (int t = 0; t < TY; ++t) lp[t] = sL_addr + lofs[t];
-
-        uint32_t rp = rrow;
-        float w[16];
-        {
-            const float4 a0 = lds128(rp), a1 = lds128(rp + 16);
-            w[0] = a0.x; w[1] = a0.y; w[2] = a0.z; w[3] = a0.w;
-            w[4] = a1.x; w[5] = a1.y; w[6] = a1.z; w[7] = a1.w;
-        }
-        for (int c = 0; c < nchunks; ++c) {
-            rp += 32;
-            if (c == cb) rp -= Wp * 4;
-            {
-                const float4 a0 = lds128(rp), a1 = lds128(rp + 16);
-                w[8] = a0.x; w[9] = a0.y; w[10] = a0.z; w[11] = a0.w;
-                w[12] = a1.x; w[13] = a1.y; w[14] = a1.z; w[15] = a1.w;
-            }
-            if (c < cb)       tile_chunk<TY, kAllWrapped>(accA, accB, w, lp, c * 32);
-            else if (c == cb) tile_chunk<TY, kMixed>(accA, accB, w, lp, c * 32);
-            else              tile_chunk<TY, kNoneWrapped>(accA, accB, w, lp, c * 32);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) w[i] = w[i + 8];
-        }
-
-#pragma unroll
-        for (int t = 0; t < TY; ++t) {
-            lofs[t] += p.LS * 4;
-            if (lofs[t] == (uint32_t)stage_bytes) lofs[t] = 0;
-        }
-    }
-
-    // ---- end of the slice: whatever is in the accumulators belongs to the wrapped output
-    //      row if the class wrapped inside (or before) the slice, else to the unwrapped one.
-    if (!lane_live) return;
-    float vals[TY][2 * kTX];
-#pragma unroll
-    for (int t = 0; t < TY; ++t)
-#pragma unroll
-        for (int j = 0; j < kTX; ++j) { vals[t][j] = accA[t][j]; vals[t][kTX + j] = accB[t][j]; }
-#pragma unroll 1
-    for (int t = 0; t < TY; ++t) {
-        const int cyt = cy0 + p.SL * t;
-        const bool wrapped = r1 > Hp - cyt;
-        const int sy = wrapped ? cyt - Hp : cyt;
-        if (sy > -H && sy < H)
-            tile_emit_row(dst, sy + H - 1, OW, W, Wp, cx0, vals[t], p.combine);
-    }
+    tile_pass<TY, kPassWrapped>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live);
+    tile_pass<TY, kPassUnwrapped>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live);
 }
 
 // Sum the per-slice partial images in slice order.  Slice s wrote output row `orow`

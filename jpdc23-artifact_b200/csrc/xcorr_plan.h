@@ -19,7 +19,7 @@
 
 namespace xcorr {
 
-constexpr int kTX = 8;            // x classes per thread (one 8-wide tile, two float4)
+constexpr int kTX = 16;           // x classes per thread (one 16-wide tile)
 constexpr int kMaxTY = 4;         // y classes per thread
 constexpr int kMaxWarps = 16;     // warps per block
 constexpr int kSmemLimit = 227 * 1024;
@@ -38,11 +38,12 @@ struct PairMap {
 
 struct TilePlan {
     int H, W;          // true size
-    int Hp, Wp;        // padded size: Wp multiple of 8, Hp multiple of SL*TY
+    int Hp, Wp;        // padded size: Wp multiple of 16, Hp multiple of SL*TY
     int TY;            // y classes per thread (template parameter of the kernel)
     int SL, ML;        // lanes over y classes / lanes over right matrices, SL*ML = 32
     int logSL;
-    int NTX;           // x-class tiles = Wp / 8
+    int NTX;           // x-class tiles = Wp / 16
+    int NCH;           // 8-step chunks per row = Wp / 8
     int NGY;           // y-class groups = Hp / (SL*TY)
     int WX, WY;        // warps of a block along x tiles / y groups
     int CX, CY;        // blocks needed along x tiles / y groups

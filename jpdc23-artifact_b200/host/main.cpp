@@ -268,13 +268,6 @@ int command_run(const std::vector<std::string>& tokens, const std::string& prog)
     }
     if (n_devices < 1) throw option_error("--devices must be at least 1");
     std::vector<int> devices;
-    if (spec->fam != family::cpu) {
-        int have = 0;
-        if (cudaGetDeviceCount(&have) != cudaSuccess || have == 0)
-            throw std::runtime_error("no CUDA device is available; only the cpu_* algorithms run without one");
-        if (n_devices > have)
-            throw std::runtime_error("--devices " + std::to_string(n_devices) + " asked for, " + std::to_string(have) + " present");
-    }
     for (int i = 0; i < n_devices; ++i) devices.push_back(i);
 
     const bool compute_bench = bench == benchmark_type::Compute;
@@ -287,6 +280,13 @@ int command_run(const std::vector<std::string>& tokens, const std::string& prog)
         alg_args = json_object::parse(f);
     }
     algorithm alg(*spec, alg_args, min_time_s * 1e9, bench, devices);
+    if (spec->fam != family::cpu) {
+        int have = 0;
+        if (cudaGetDeviceCount(&have) != cudaSuccess || have == 0)
+            throw std::runtime_error("no CUDA device is available; only the cpu_* algorithms run without one");
+        if (n_devices > have)
+            throw std::runtime_error("--devices " + std::to_string(n_devices) + " asked for, " + std::to_string(have) + " present");
+    }
 
     try {
         log.log("Loading inputs");

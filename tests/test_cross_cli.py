@@ -1,0 +1,314 @@
+"""Tests of the `cross` host program: command line, algorithm registry, matrix file format,
+timing CSV, exit codes.  The CPU tests use the cpu_* algorithms (no GPU needed); the GPU
+tests run the CUDA-backed algorithms and compare the files they write with the oracle."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from conftest import grouped_to_file, seeded_inputs
+
+# the reference's registry (repo/cross-corr/src/main.cpp:368-402) without its FFT entries
+EXPECTED_NAMES = sorted("""
+cpu_one_to_one cpu_one_to_many cpu_n_to_mn cpu_n_to_m
+nai_orig_one_to_one nai_orig_one_to_many nai_orig_n_to_mn nai_orig_n_to_m
+nai_shuffle_one_to_one nai_shuffle_work_distribution_one_to_one
+nai_shuffle_multimat_right_one_to_one nai_shuffle_multimat_right_one_to_many
+nai_shuffle_multimat_right_work_distribution_one_to_one
+nai_shuffle_multimat_right_work_distribution_one_to_many
+nai_shuffle_multimat_right_work_distribution_n_to_mn
+nai_shuffle_multimat_right_work_distribution_n_to_m
+nai_shuffle_multimat_both_work_distribution_local_mem_n_to_m
+nai_shuffle_multimat_both_work_distribution_n_to_m
+nai_shuffle_multirow_both_multimat_both_n_to_m
+nai_shuffle_multirow_right_one_to_one nai_shuffle_multirow_both_one_to_one
+nai_shuffle_multirow_both_local_mem_one_to_one
+nai_shuffle_multirow_right_multimat_right_one_to_one
+nai_shuffle_multirow_right_multimat_right_one_to_many
+nai_shuffle_multirow_right_multimat_right_n_to_mn
+nai_shuffle_multirow_both_multimat_right_one_to_many
+nai_shuffle_multirow_both_multimat_right_n_to_mn
+nai_warp_per_shift_one_to_one nai_warp_per_shift_simple_indexing_one_to_one
+nai_warp_per_shift_work_distribution_one_to_one
+nai_warp_per_shift_shared_mem_one_to_one nai_warp_per_shift_shared_mem_one_to_many
+nai_warp_per_shift_shared_mem_n_to_mn nai_warp_per_shift_shared_mem_n_to_m
+nai_block_per_shift_one_to_one
+""".split())
+
+
+@pytest.fixture(scope="session")
+def cross(xc):
+    if not os.path.exists(xc.CROSS_PATH):
+        xc.build()
+    return xc.CROSS_PATH
+
+
+def run(cross, *args, cwd=None):
+    return subprocess.run([cross, *map(str, args)], capture_output=True, text=True, cwd=cwd, timeout=600)
+
+
+def write_matrices(path, arr):
+    """The reference's input format (benchmark/input_generator.py:20-32): header
+    '# rows,cols,count' then one comma-separated line per matrix row."""
+    arr = np.asarray(arr)
+    n, rows, cols = arr.shape
+    np.savetxt(path, arr.reshape(n * rows, cols), delimiter=",", header=f"{rows},{cols},{n}")
+
+
+def read_matrices(path):
+    with open(path) as f:
+        head = f.readline()
+    assert head.startswith("# ")
+    rows, cols, n = (int(v) for v in head[2:].split(","))
+    data = np.loadtxt(path, delimiter=",", skiprows=1, ndmin=2)
+    assert data.shape == (rows * n, cols)
+    return data.reshape(n, rows, cols)
+
+
+# ---- no GPU needed --------------------------------------------------------------------------------
+def test_list_prints_the_registry_sorted(cross):
+    r = run(cross, "list")
+    assert r.returncode == 0
+    assert r.stdout.split() == EXPECTED_NAMES
+
+
+def test_help_and_unknown_command(cross):
+    assert run(cross).returncode == 0 and "Usage:" in run(cross).stdout
+    assert run(cross, "--help").returncode == 0
+    r = run(cross, "frobnicate")
+    assert r.returncode == 1 and "Unknown command frobnicate" in r.stderr
+
+
+def test_input_command(cross):
+    assert run(cross, "input", "one_to_one", 16, 16, 1, 1).stdout == "Valid\n"
+    assert run(cross, "input", "one_to_one", 16, 16, 1, 2).stdout == "Invalid\n"
+    assert run(cross, "input", "one_to_many", 16, 16, 1, 200).stdout == "Valid\n"
+    assert run(cross, "input", "n_to_mn", 16, 16, 4, 10).stdout == "Invalid\n"
+    assert run(cross, "input", "n_to_mn", 16, 16, 4, 12).stdout == "Valid\n"
+    assert run(cross, "input", "n_to_m", 0, 16, 4, 12).stdout == "Invalid\n"
+    r = run(cross, "input", "many_to_many", 1, 1, 1, 1)
+    assert r.returncode == 1 and "Unknown algorithm type" in r.stderr
+    assert run(cross, "input", "n_to_m", 1, 1).returncode == 1
+
+
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [
+    ("one_to_one", 5, 7, 1, 1), ("one_to_many", 6, 6, 1, 3), ("n_to_mn", 4, 5, 2, 6), ("n_to_m", 3, 8, 2, 3)])
+def test_cpu_algorithms_write_the_reference_result(cross, oracle, tmp_path, mode, rows, cols, nl, nr):
+    left, right = seeded_inputs(rows, cols, nl, nr, 17)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    r = run(cross, "run", "-o", tmp_path / "out.csv", f"cpu_{mode}", tmp_path / "l.csv", tmp_path / "r.csv",
+            cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    assert "Loading inputs" in r.stdout and "No validation" in r.stdout
+    got = read_matrices(tmp_path / "out.csv")
+    want = oracle.run(mode, left, right)                     # n_to_mn: file order both sides
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() <= 5.1e-7                # six printed decimals
+    assert not os.path.exists(tmp_path / "measurements.csv")  # benchmark_type None writes no timings
+
+
+def test_output_format_is_fixed_six_decimals_with_header(cross, tmp_path):
+    left = np.array([[[1.0, 2.0], [3.0, 4.0]]], np.float32)
+    right = np.array([[[0.5, 0.25], [2.0, 1.0]]], np.float32)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    assert run(cross, "run", "--out", tmp_path / "o.csv", "cpu_one_to_one", tmp_path / "l.csv",
+               tmp_path / "r.csv", cwd=tmp_path).returncode == 0
+    lines = open(tmp_path / "o.csv").read().splitlines()
+    assert lines[0] == "# 3,3,1"
+    assert lines[1] == "1.000000,4.000000,4.000000"          # shifts (-1,-1), (0,-1), (1,-1)
+    assert lines[2] == "3.250000,11.000000,9.000000"
+    assert lines[3] == "0.750000,2.500000,2.000000"
+
+
+def test_non_square_results_are_written_row_by_row(cross, oracle, tmp_path):
+    left, right = seeded_inputs(2, 9, 1, 1, 3)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    assert run(cross, "run", "-o", tmp_path / "o.csv", "cpu_one_to_one", tmp_path / "l.csv", tmp_path / "r.csv",
+               cwd=tmp_path).returncode == 0
+    got = read_matrices(tmp_path / "o.csv")
+    assert got.shape == (1, 3, 17)
+    assert np.abs(got - oracle.run("one_to_one", left, right)).max() <= 5.1e-7
+
+
+def test_timing_csv_layouts(cross, tmp_path):
+    left, right = seeded_inputs(6, 6, 1, 1, 4)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    base = ["cpu_one_to_one", tmp_path / "l.csv", tmp_path / "r.csv"]
+    # Compute: one label, adaptive repetition until min_time
+    r = run(cross, "run", "-b", "Compute", "-m", "0.01", "-t", tmp_path / "c.csv", *base, cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    rows = open(tmp_path / "c.csv").read().splitlines()
+    assert rows[0] == "Computation,Computation_iterations"
+    ns, it = (int(v) for v in rows[1].split(","))
+    assert ns > 0 and it >= 1 and ns * it >= 0.01e9 * 0.9
+    # CommonSteps: the seven step labels (cross_corr.hpp:168-176)
+    r = run(cross, "run", "-b", "CommonSteps", "-m", "0.001", "-t", tmp_path / "s.csv", "--no_progress", *base,
+            cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    rows = open(tmp_path / "s.csv").read().splitlines()
+    labels = ["Load", "Prepare", "Transfer", "Run", "Finalize", "Free", "Store"]
+    assert rows[0] == ",".join(f"{l},{l}_iterations" for l in labels)
+    assert len(rows[1].split(",")) == 14 and r.stdout == ""
+    # append + outer loops: no second header, one row per loop; outputs get _<loop> suffixes
+    r = run(cross, "run", "-b", "Compute", "-m", "0.001", "-a", "-l", "2", "-t", tmp_path / "c.csv",
+            "-o", tmp_path / "res.csv", *base, cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    assert len(open(tmp_path / "c.csv").read().splitlines()) == 4
+    assert os.path.exists(tmp_path / "res_0.csv") and os.path.exists(tmp_path / "res_1.csv")
+    # default timing file name
+    r = run(cross, "run", "-b", "Compute", "-m", "0.001", *base, cwd=tmp_path)
+    assert r.returncode == 0 and os.path.exists(tmp_path / "measurements.csv")
+
+
+def test_validate_option_and_command(cross, oracle, tmp_path):
+    left, right = seeded_inputs(7, 5, 1, 2, 6)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    base = ["cpu_one_to_many", tmp_path / "l.csv", tmp_path / "r.csv"]
+    # --validate without a value recomputes on the CPU: zero error, human-readable block
+    r = run(cross, "run", "-v", *base, cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    assert "Difference from valid values:" in r.stdout and "Max: 0" in r.stdout
+    # machine-readable form with --no_progress (validate.hpp:58-66)
+    r = run(cross, "run", "--validate", "--no_progress", *base, cwd=tmp_path)
+    assert r.stdout.splitlines() == ["Max,Mean,Stddev", "0.000000e+00,0.000000e+00,0.000000e+00"]
+    # --validate <file>, given the way the reference's driver does (executable.py:137-145)
+    assert run(cross, "run", "-o", tmp_path / "valid.csv", *base, cwd=tmp_path).returncode == 0
+    r = run(cross, "run", "--validate", tmp_path / "valid.csv", "--no_progress", *base, cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    mx = float(r.stdout.splitlines()[1].split(",")[0])
+    assert 0 <= mx < 1e-3                                     # file holds six decimals; small corner sums
+    # `cross validate`: template first, files to check after it
+    wrong = oracle.run("one_to_many", left, right) * 1.001
+    write_matrices(tmp_path / "wrong.csv", wrong)
+    r = run(cross, "validate", "-c", "-p", tmp_path / "valid.csv", tmp_path / "valid.csv", tmp_path / "wrong.csv")
+    assert r.returncode == 0, r.stderr
+    lines = r.stdout.splitlines()
+    assert lines[0] == "Max,Mean,Stddev" and float(lines[1].split(",")[0]) == 0.0
+    assert abs(float(lines[2].split(",")[0]) - 1e-3) < 1e-4
+
+
+def test_exit_codes(cross, tmp_path):
+    left, right = seeded_inputs(4, 4, 1, 1, 1)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    l, rr = tmp_path / "l.csv", tmp_path / "r.csv"
+    r = run(cross, "run", "nai_fastest_ever", l, rr)
+    assert r.returncode == 1 and 'Unknown algorithm "nai_fastest_ever", expected one of' in r.stderr
+    assert run(cross, "run", "--bogus", "cpu_one_to_one", l, rr).returncode == 1
+    assert run(cross, "run", "cpu_one_to_one", l).returncode == 1
+    assert run(cross, "run", "-b", "Sometimes", "cpu_one_to_one", l, rr).returncode == 1
+    assert run(cross, "run", "-d", "double", "cpu_one_to_one", l, rr).returncode == 1
+    r = run(cross, "run", "cpu_one_to_one", l, tmp_path / "missing.csv")
+    assert r.returncode == 3 and "data loading step" in r.stderr
+    r = run(cross, "run", "fft_orig_one_to_one", l, rr)
+    assert r.returncode == 1 and "FFT engine" in r.stderr
+    # wrong matrix counts for the mode, sizes that differ, broken files: computation-step errors
+    write_matrices(tmp_path / "two.csv", np.zeros((2, 4, 4), np.float32))
+    assert run(cross, "run", "cpu_one_to_one", l, tmp_path / "two.csv").returncode == 3
+    write_matrices(tmp_path / "big.csv", np.zeros((1, 5, 4), np.float32))
+    r = run(cross, "run", "cpu_one_to_one", l, tmp_path / "big.csv")
+    assert r.returncode == 3 and "expected ref and target to be the same size" in r.stderr
+    (tmp_path / "short.csv").write_text("# 2,2,1\n1,2\n3\n")
+    r = run(cross, "run", "cpu_one_to_one", tmp_path / "short.csv", tmp_path / "short.csv")
+    assert r.returncode == 3 and "too short" in r.stderr
+    (tmp_path / "nohdr.csv").write_text("1,2\n3,4\n")
+    assert run(cross, "run", "cpu_one_to_one", tmp_path / "nohdr.csv", tmp_path / "nohdr.csv").returncode == 3
+    # algorithm arguments outside their range: exit 1 before anything is loaded
+    (tmp_path / "bad.json").write_text(json.dumps({"warps_per_thread_block": 0}))
+    r = run(cross, "run", "--args_path", tmp_path / "bad.json", "nai_shuffle_one_to_one", l, rr)
+    assert r.returncode == 1 and "Invalid algorithm argument value" in r.stderr
+    (tmp_path / "bad2.json").write_text(json.dumps({"distribution_type": "hexagon"}))
+    assert run(cross, "run", "--args_path", tmp_path / "bad2.json", "nai_shuffle_work_distribution_one_to_one",
+               l, rr).returncode == 1
+    (tmp_path / "bad3.json").write_text(json.dumps({"shifts_per_thread_block": 16, "shared_mem_rows": 8}))
+    assert run(cross, "run", "--args_path", tmp_path / "bad3.json", "nai_warp_per_shift_shared_mem_one_to_one",
+               l, rr).returncode == 1
+    (tmp_path / "broken.json").write_text("{ \"warps_per_thread_block\": ")
+    assert run(cross, "run", "--args_path", tmp_path / "broken.json", "nai_shuffle_one_to_one", l, rr).returncode == 2
+
+
+# ---- GPU --------------------------------------------------------------------------------------------
+GPU_ALGS = [
+    ("nai_orig_one_to_one", "one_to_one", 24, 24, 1, 1, {}),
+    ("nai_shuffle_multirow_both_one_to_one", "one_to_one", 40, 33, 1, 1,
+     {"warps_per_thread_block": 4, "shifts_per_thread": 8, "left_rows_per_iteration": 8}),
+    ("nai_shuffle_work_distribution_one_to_one", "one_to_one", 32, 32, 1, 1, {"rows_per_thread": 5}),
+    ("nai_warp_per_shift_one_to_one", "one_to_one", 16, 16, 1, 1, {"shifts_per_thread_block": 16}),
+    ("nai_warp_per_shift_shared_mem_one_to_many", "one_to_many", 16, 20, 1, 5, {}),
+    ("nai_block_per_shift_one_to_one", "one_to_one", 9, 9, 1, 1, {"block_size": 64}),
+    ("nai_shuffle_multirow_both_multimat_right_one_to_many", "one_to_many", 32, 32, 1, 9,
+     {"right_matrices_per_thread": 4}),
+    ("nai_shuffle_multirow_both_multimat_right_n_to_mn", "n_to_mn", 16, 24, 3, 12, {}),
+    ("nai_orig_n_to_mn", "n_to_mn", 8, 8, 2, 6, {}),
+    ("nai_shuffle_multirow_both_multimat_both_n_to_m", "n_to_m", 24, 16, 3, 5, {}),
+    ("nai_shuffle_multimat_both_work_distribution_n_to_m", "n_to_m", 20, 20, 2, 3, {"rows_per_thread": 7}),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("alg,mode,rows,cols,nl,nr,args", GPU_ALGS)
+def test_gpu_algorithms_files_match_the_oracle(cross, oracle, tmp_path, alg, mode, rows, cols, nl, nr, args):
+    """Files in, files out, in the reference's FILE order for every mode (n_to_mn: right and
+    result matrix t*n + l belong to left l) -- the grouping the library wants stays inside."""
+    left, right = seeded_inputs(rows, cols, nl, nr, 23)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    (tmp_path / "args.json").write_text(json.dumps(args))
+    r = run(cross, "run", "--out", tmp_path / "o.csv", "--validate", "--times", tmp_path / "t.csv", "--no_progress",
+            "--args_path", tmp_path / "args.json", "--benchmark_type", "Algorithm", "--outer_loops", "1",
+            "--min_time", "0.01", alg, tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    want = oracle.run(mode, left, right, acc64=True)
+    got = read_matrices(tmp_path / "o.csv")
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max() + 5.1e-7
+    # --validate (in-process CPU recompute): Max relative element error is float rounding
+    stats = r.stdout.splitlines()
+    assert stats[0] == "Max,Mean,Stddev" and float(stats[1].split(",")[0]) < 1e-4
+    # timing CSV: Kernel, Kernel_iterations, then the algorithm's properties in registry order
+    head, row = open(tmp_path / "t.csv").read().splitlines()[:2]
+    cols_ = head.split(",")
+    assert cols_[:2] == ["Kernel", "Kernel_iterations"]
+    vals = row.split(",")
+    assert len(vals) == len(cols_) and int(vals[0]) > 0 and int(vals[1]) >= 1
+    for k, v in args.items():
+        assert vals[cols_.index(k)] == str(v)
+
+
+@pytest.mark.gpu
+def test_gpu_property_columns_follow_the_reference_order(cross, tmp_path):
+    left, right = seeded_inputs(16, 16, 2, 4, 2)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    r = run(cross, "run", "-b", "Algorithm", "-m", "0.001", "-t", tmp_path / "t.csv",
+            "nai_warp_per_shift_shared_mem_n_to_m", tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    head, row = open(tmp_path / "t.csv").read().splitlines()
+    assert head == ("Kernel,Kernel_iterations,shifts_per_thread_block,shared_mem_row_size,shared_mem_rows,"
+                    "strided_load,column_group_per_block,right_matrices_per_block,num_cuda_streams")
+    assert row.split(",")[2:] == ["16", "32", "16", "1", "0", "8", "8"]
+
+
+@pytest.mark.gpu
+def test_gpu_devices_option_shards_without_changing_results(cross, tmp_path):
+    import torch
+    ndev = min(torch.cuda.device_count(), 2)
+    left, right = seeded_inputs(16, 16, 4, 8, 5)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    outs = []
+    for nd in sorted({1, ndev}):
+        r = run(cross, "run", "--devices", nd, "-o", tmp_path / f"o{nd}.csv",
+                "nai_shuffle_multirow_both_multimat_both_n_to_m", tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+        assert r.returncode == 0, r.stderr
+        outs.append(open(tmp_path / f"o{nd}.csv").read())
+    assert all(o == outs[0] for o in outs)
+    r = run(cross, "run", "--devices", 99, "nai_orig_n_to_m", tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 2 and "--devices" in r.stderr
