@@ -29,8 +29,9 @@ namespace xcorr {
 // Per right row ry the thread walks the left row's columns u in chunks of 8:
 //     acc[t][j] += L[(ry + cy_t) mod Hp][u] * R[ry][(u - cx0 - j) mod Wp],  j in [0,16)
 // The R values a chunk needs are a 23-wide window that slides by one per step; each chunk
-// refills its 8 new entries with two 16-byte loads, the left values are two 16-byte loads
-// per y class.  TY*16 FFMA per step against (TY + 1)/4 loads, and no shuffles.
+// fetches it with six 16-byte loads (all lanes of a matrix read the same addresses), the
+// left values are two 16-byte loads per y class: 128*TY FFMA against 2*TY + 6 loads, no
+// shuffles, no loop-carried window registers.
 //
 // x wrap: column j has wrapped while u < cx0 + j.  Instead of two accumulator sets the
 // slice is walked twice with one set: pass B (wrapped part, output shift cx - Wp) takes the
@@ -43,7 +44,6 @@ namespace xcorr {
 // unwrapped) one at the end of the slice.
 
 enum Pass : int { kPassWrapped = 0, kPassUnwrapped = 1 };
-constexpr int kWin = kTX + 7;     // window entries a chunk reads
 
 // 16-byte shared-memory load through a 32-bit shared-window address (one register per
 // address instead of the two a generic pointer takes).
@@ -54,28 +54,34 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
     return v;
 }
 
-// The 8 new window entries of a chunk: R[...] at `addr` -> w[15..22].
-__device__ __forceinline__ void window_refill(float (&w)[kWin], uint32_t addr) {
-    const float4 a0 = lds128(addr), a1 = lds128(addr + 16);
-    w[15] = a0.x; w[16] = a0.y; w[17] = a0.z; w[18] = a0.w;
-    w[19] = a1.x; w[20] = a1.y; w[21] = a1.z; w[22] = a1.w;
-}
-
-__device__ __forceinline__ void window_shift(float (&w)[kWin]) {
+// Load the N4*4 floats at `addr` into w[FIRST ...].
+template<int FIRST, int N4, int LEN>
+__device__ __forceinline__ void window_load(float (&w)[LEN], uint32_t addr) {
 #pragma unroll
-    for (int i = 0; i < kWin - 8; ++i) w[i] = w[i + 8];
+    for (int i = 0; i < N4; ++i) {
+        const float4 v = lds128(addr + 16 * i);
+        w[FIRST + 4 * i] = v.x; w[FIRST + 4 * i + 1] = v.y; w[FIRST + 4 * i + 2] = v.z; w[FIRST + 4 * i + 3] = v.w;
+    }
 }
 
-// One chunk of 8 steps.  TRI < 0: every (step, column) pair.  TRI = 0 / 1: first / second
-// chunk of the tile's own columns, where only the pairs on the pass's side of the diagonal
-// count: step >= j for the unwrapped pass, step < j for the wrapped one.
+// One chunk of 8 steps: acc[t][j] += L_t[u0 + kk] * w[16 + kk - j], where w[i] holds
+// R[(u0 - cx0 - 16 + i) mod Wp].  TRI < 0: every (step, column) pair.  TRI = 0 / 1: first /
+// second chunk of the tile's own columns, where only the pairs on the pass's side of the
+// diagonal count: step >= j for the unwrapped pass, step < j for the wrapped one.
 template<int TY, int TRI, int PASS>
-__device__ __forceinline__ void tile_chunk(float (&acc)[TY][kTX], const float (&w)[kWin],
+__device__ __forceinline__ void tile_chunk(float (&acc)[TY][kTX], const float (&w)[24],
                                            const uint32_t (&lp)[TY], uint32_t col_bytes) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
 #pragma unroll
         for (int t = 0; t < TY; ++t) {
+            bool any = TRI < 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+#pragma unroll
+                for (int j = 0; j < kTX; ++j)
+                    any = any || (((8 * TRI + 4 * half + k) >= j) == (PASS == kPassUnwrapped));
+            if (!any) continue;               // this half contributes nothing on this side
             const float4 lv = lds128(lp[t] + col_bytes + 16 * half);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -85,151 +91,148 @@ __device__ __forceinline__ void tile_chunk(float (&acc)[TY][kTX], const float (&
                 for (int j = 0; j < kTX; ++j) {
                     const int step = 8 * (TRI < 0 ? 0 : TRI) + kk;
                     const bool take = TRI < 0 || ((step >= j) == (PASS == kPassUnwrapped));
-                    if (take) acc[t][j] = fmaf(l, w[15 + kk - j], acc[t][j]);
+                    if (take) acc[t][j] = fmaf(l, w[16 + kk - j], acc[t][j]);
                 }
             }
         }
     }
 }
 
-// All chunks of one right row for one pass.
-template<int TY, int PASS>
+// All chunks of one right row for one pass.  `rrow` is the shared address of the row's
+// first element, `lp` the shared addresses of the TY left rows.
+template<int TY>
 __device__ __forceinline__ void tile_row(float (&acc)[TY][kTX], const uint32_t (&lp)[TY], uint32_t rrow,
-                                         int cx0, int Wp, int nchunks) {
-    float w[kWin];
-    const int cb = cx0 >> 3;                 // first chunk of the tile's own columns
-    if (PASS == kPassWrapped) {
-        // window of the first chunk: R[Wp - cx0 - 15 .. Wp - cx0 - 1]
-        uint32_t rp = rrow + (uint32_t)(Wp - cx0 - 16) * 4;
-        {
-            const float4 a0 = lds128(rp), a1 = lds128(rp + 16), a2 = lds128(rp + 32), a3 = lds128(rp + 48);
-            w[0] = a0.y; w[1] = a0.z; w[2] = a0.w;
-            w[3] = a1.x; w[4] = a1.y; w[5] = a1.z; w[6] = a1.w;
-            w[7] = a2.x; w[8] = a2.y; w[9] = a2.z; w[10] = a2.w;
-            w[11] = a3.x; w[12] = a3.y; w[13] = a3.z; w[14] = a3.w;
-        }
-        rp += 64;
+                                         int pass, int cb, int c_begin, int c_end, uint32_t roff_bytes,
+                                         int Wp) {
+    // chunks taken in full: the same code for both passes
 #pragma unroll 1
-        for (int c = 0; c < cb; ++c, rp += 32) {
-            window_refill(w, rp);
-            tile_chunk<TY, -1, PASS>(acc, w, lp, (uint32_t)c * 32);
-            window_shift(w);
-        }
-        // the tile's own columns, lower triangle; no new window entries are needed
+    for (int c = c_begin; c < c_end; ++c) {
+        float w[24];
+        window_load<0, 6>(w, rrow + roff_bytes + (uint32_t)c * 32);
+        tile_chunk<TY, -1, 0>(acc, w, lp, (uint32_t)c * 32);
+    }
+    // the two chunks of the tile's own columns: one triangle per pass
+    float w[24];
+    if (pass == kPassWrapped) {
+        // step < j: w[16 + kk - j] with kk - j in [-15, -1] -> R[Wp - 15 .. Wp - 1]
+        window_load<0, 4>(w, rrow + (uint32_t)(Wp - 16) * 4);          // w[i] = R[Wp - 16 + i]
+        tile_chunk<TY, 0, kPassWrapped>(acc, w, lp, (uint32_t)cb * 32);
+        // second chunk: step = 8 + kk, R[Wp + 8 + kk - j]: shift the window view by 8
+        float w2[24];
 #pragma unroll
-        for (int i = 15; i < kWin; ++i) w[i] = 0.f;
-        tile_chunk<TY, 0, PASS>(acc, w, lp, (uint32_t)cb * 32);
-        window_shift(w);
-        tile_chunk<TY, 1, PASS>(acc, w, lp, (uint32_t)(cb + 1) * 32);
+        for (int i = 0; i < 8; ++i) w2[i] = w[i + 8];                  // w2[i] = R[Wp - 8 + i]
+        tile_chunk<TY, 1, kPassWrapped>(acc, w2, lp, (uint32_t)(cb + 1) * 32);
     } else {
-        uint32_t rp = rrow;
-#pragma unroll
-        for (int i = 0; i < 15; ++i) w[i] = 0.f;
-        window_refill(w, rp);
-        tile_chunk<TY, 0, PASS>(acc, w, lp, (uint32_t)cb * 32);
-        window_shift(w);
-        window_refill(w, rp + 32);
-        tile_chunk<TY, 1, PASS>(acc, w, lp, (uint32_t)(cb + 1) * 32);
-        window_shift(w);
-        rp += 64;
-#pragma unroll 1
-        for (int c = cb + 2; c < nchunks; ++c, rp += 32) {
-            window_refill(w, rp);
-            tile_chunk<TY, -1, PASS>(acc, w, lp, (uint32_t)c * 32);
-            window_shift(w);
-        }
+        // step >= j: first chunk w[16 + kk - j], kk - j in [0, 7] -> R[0 .. 7]
+        window_load<16, 2>(w, rrow);                                    // w[16 + i] = R[i]
+        tile_chunk<TY, 0, kPassUnwrapped>(acc, w, lp, (uint32_t)cb * 32);
+        // second chunk: R[8 + kk - j], 8 + kk - j in [0, 15]
+        float w2[24];
+        window_load<8, 4>(w2, rrow);                                    // w2[8 + i] = R[i]
+        tile_chunk<TY, 1, kPassUnwrapped>(acc, w2, lp, (uint32_t)(cb + 1) * 32);
     }
 }
 
 // Write one y class's 16 sums of one pass to output row `orow`.  Deliberately a rolled loop
 // over a local-memory copy: the flush runs once per class, pass and slice, and unrolled it
 // costs the hot loop dozens of registers.
-template<int PASS>
 __device__ __forceinline__ void tile_emit_row(float* __restrict__ dst, int orow, int OW, int W, int Wp,
-                                              int cx0, const float* vals, int combine) {
+                                              int cx0, const float* vals, int combine, int pass) {
     float* o = dst + (size_t)orow * OW;
 #pragma unroll 1
     for (int j = 0; j < kTX; ++j) {
         const int cx = cx0 + j;
         // unwrapped: shift sx = cx; wrapped: shift sx = cx - Wp
-        const int col = PASS == kPassUnwrapped ? cx + W - 1 : cx - Wp + W - 1;
-        const bool ok = PASS == kPassUnwrapped ? cx < W : col >= 0;
+        const int col = pass == kPassUnwrapped ? cx + W - 1 : cx - Wp + W - 1;
+        const bool ok = pass == kPassUnwrapped ? cx < W : col >= 0;
         if (ok) {
             if (combine == kAtomic) atomicAdd(o + col, vals[j]); else o[col] = vals[j];
         }
     }
 }
 
-// One pass over the slice's rows for one thread.
-template<int TY, int PASS>
-__device__ __forceinline__ void tile_pass(const TilePlan& p, float* __restrict__ dst, uint32_t sL_addr,
-                                          uint32_t rmat_addr, int r0, int r1, int cy0, int cya, int cx0,
-                                          bool lane_live) {
+// Both passes over the slice's rows for one thread.
+template<int TY>
+__device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict__ dst, uint32_t sL_addr,
+                                            uint32_t rmat_addr, int r0, int r1, int cy0, int cya, int cx0,
+                                            bool lane_live) {
     const int H = p.H, W = p.W, Hp = p.Hp, Wp = p.Wp;
     const int OW = 2 * W - 1;
     const uint32_t stage_bytes = (uint32_t)(p.nstage * p.LS * 4);
-    uint32_t lofs[TY];                        // byte offset of class t's staged left row
-#pragma unroll
-    for (int t = 0; t < TY; ++t) {
-        int i = cy0 + p.SL * t - cya;        // staged row for ry = r0
-        if (i >= p.nstage) i -= p.nstage;
-        lofs[t] = (uint32_t)(i * p.LS * 4);
-    }
-    float acc[TY][kTX];
-#pragma unroll
-    for (int t = 0; t < TY; ++t)
-#pragma unroll
-        for (int j = 0; j < kTX; ++j) acc[t][j] = 0.f;
+    const int cb = cx0 >> 3;                  // first chunk of the tile's own columns
 
-    uint32_t rrow = rmat_addr;
 #pragma unroll 1
-    for (int ry = r0; ry < r1; ++ry, rrow += (uint32_t)Wp * 4) {
-        // a class that starts wrapping at this row: its unwrapped-in-y part is complete
-        // (the wrap rows of a lane's classes differ, so at most one matches)
-        int tsel = -1;
-#pragma unroll
-        for (int t = 0; t < TY; ++t)
-            if (ry == Hp - (cy0 + p.SL * t) && ry > r0) tsel = t;
-        if (tsel >= 0) {
-            float vals[kTX];
-#pragma unroll
-            for (int t = 0; t < TY; ++t) {
-                if (t == tsel) {
-#pragma unroll
-                    for (int j = 0; j < kTX; ++j) { vals[j] = acc[t][j]; acc[t][j] = 0.f; }
-                }
-            }
-            const int cyt = cy0 + p.SL * tsel;
-            if (lane_live && cyt < H)
-                tile_emit_row<PASS>(dst, cyt + H - 1, OW, W, Wp, cx0, vals, p.combine);
-        }
-
-        uint32_t lp[TY];
-#pragma unroll
-        for (int t = 0; t < TY; ++t) lp[t] = sL_addr + lofs[t];
-        tile_row<TY, PASS>(acc, lp, rrow, cx0, Wp, p.NCH);
+    for (int pass = 0; pass < 2; ++pass) {
+        // wrapped pass: chunks [0, cb) with window R[Wp - cx0 - 16 + 8c ...];
+        // unwrapped pass: chunks [cb + 2, NCH) with window R[8(c - cb) - 16 ...]
+        const int c_begin = pass == kPassWrapped ? 0 : cb + 2;
+        const int c_end = pass == kPassWrapped ? cb : p.NCH;
+        const uint32_t roff_bytes = pass == kPassWrapped ? (uint32_t)(Wp - cx0 - 16) * 4
+                                                         : (uint32_t)(-(8 * cb + 16) * 4);
+        uint32_t lofs[TY];                    // byte offset of class t's staged left row
 #pragma unroll
         for (int t = 0; t < TY; ++t) {
-            lofs[t] += (uint32_t)p.LS * 4;
-            if (lofs[t] == stage_bytes) lofs[t] = 0;
+            int i = cy0 + p.SL * t - cya;    // staged row for ry = r0
+            if (i >= p.nstage) i -= p.nstage;
+            lofs[t] = (uint32_t)(i * p.LS * 4);
         }
-    }
+        float acc[TY][kTX];
+#pragma unroll
+        for (int t = 0; t < TY; ++t)
+#pragma unroll
+            for (int j = 0; j < kTX; ++j) acc[t][j] = 0.f;
 
-    // end of the slice: the sums belong to the wrapped output row if the class wrapped
-    // inside (or before) the slice, else to the unwrapped one
-    if (!lane_live) return;
-    float vals[TY][kTX];
-#pragma unroll
-    for (int t = 0; t < TY; ++t)
-#pragma unroll
-        for (int j = 0; j < kTX; ++j) vals[t][j] = acc[t][j];
+        uint32_t rrow = rmat_addr;
 #pragma unroll 1
-    for (int t = 0; t < TY; ++t) {
-        const int cyt = cy0 + p.SL * t;
-        const bool wrapped = r1 > Hp - cyt;
-        const int sy = wrapped ? cyt - Hp : cyt;
-        if (sy > -H && sy < H)
-            tile_emit_row<PASS>(dst, sy + H - 1, OW, W, Wp, cx0, vals[t], p.combine);
+        for (int ry = r0; ry < r1; ++ry, rrow += (uint32_t)Wp * 4) {
+            // a class that starts wrapping at this row: its unwrapped-in-y part is complete
+            // (the wrap rows of a lane's classes differ, so at most one matches)
+            int tsel = -1;
+#pragma unroll
+            for (int t = 0; t < TY; ++t)
+                if (ry == Hp - (cy0 + p.SL * t) && ry > r0) tsel = t;
+            if (tsel >= 0) {
+                float vals[kTX];
+#pragma unroll
+                for (int t = 0; t < TY; ++t) {
+                    if (t == tsel) {
+#pragma unroll
+                        for (int j = 0; j < kTX; ++j) { vals[j] = acc[t][j]; acc[t][j] = 0.f; }
+                    }
+                }
+                const int cyt = cy0 + p.SL * tsel;
+                if (lane_live && cyt < H)
+                    tile_emit_row(dst, cyt + H - 1, OW, W, Wp, cx0, vals, p.combine, pass);
+            }
+
+            uint32_t lp[TY];
+#pragma unroll
+            for (int t = 0; t < TY; ++t) lp[t] = sL_addr + lofs[t];
+            tile_row<TY>(acc, lp, rrow, pass, cb, c_begin, c_end, roff_bytes, Wp);
+#pragma unroll
+            for (int t = 0; t < TY; ++t) {
+                lofs[t] += (uint32_t)p.LS * 4;
+                if (lofs[t] == stage_bytes) lofs[t] = 0;
+            }
+        }
+
+        // end of the slice: the sums belong to the wrapped output row if the class wrapped
+        // inside (or before) the slice, else to the unwrapped one
+        if (lane_live) {
+            float vals[TY][kTX];
+#pragma unroll
+            for (int t = 0; t < TY; ++t)
+#pragma unroll
+                for (int j = 0; j < kTX; ++j) vals[t][j] = acc[t][j];
+#pragma unroll 1
+            for (int t = 0; t < TY; ++t) {
+                const int cyt = cy0 + p.SL * t;
+                const bool wrapped = r1 > Hp - cyt;
+                const int sy = wrapped ? cyt - Hp : cyt;
+                if (sy > -H && sy < H)
+                    tile_emit_row(dst, sy + H - 1, OW, W, Wp, cx0, vals[t], p.combine, pass);
+            }
+        }
     }
 }
 
@@ -335,8 +338,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) tile_kernel(const TileArgs 
     const uint32_t sL_addr = (uint32_t)__cvta_generic_to_shared(sL);
     const uint32_t rmat_addr = (uint32_t)__cvta_generic_to_shared(sR + (size_t)m * p.RMS);
 
-    tile_pass<TY, kPassWrapped>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live);
-    tile_pass<TY, kPassUnwrapped>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live);
+    tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live);
 }
 
 // Sum the per-slice partial images in slice order.  Slice s wrote output row `orow`
