@@ -130,14 +130,21 @@ void finish_plan(TilePlan& p, const PairMap& pm) {
     p.LS = p.Wp + 4;
     p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
     p.threads = 32 * p.WX * p.WY;
-    p.smem_bytes = ((size_t)p.nstage * p.LS + (size_t)p.ML * p.RMS) * sizeof(float);
+    // staged left rows, staged right rows, per-warp flush staging (16 x 17 floats + 16 addresses)
+    p.smem_bytes = ((size_t)p.nstage * p.LS + (size_t)p.ML * p.RMS) * sizeof(float) +
+                   (size_t)(p.threads / 32) * (16 * (kTX + 1) * 4 + 16 * 8);
 }
 
-// Per-shape plan of the tile kernel.
+// Per-shape plan of the tile kernel: micro-tile height, lane split, block shape and how the
+// right rows are divided -- none (one block per task, plain stores), S equal slices per task
+// (partials combined by atomics or through the workspace) or stream-K (the (task, row)
+// units of all tasks cut evenly over as many blocks as fit on the GPU; a block's share is a
+// run of whole tasks plus at most two partial ones, partial ones added atomically).
+// Every candidate gets an estimated time; the smallest wins.
 xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, const DeviceInfo& dev,
                        TilePlan* out) {
     TilePlan best{};
-    double best_score = -1.0;
+    double best_time = -1.0;
     const int want_ty = h ? h->overlap_rows : 0;
     const int want_sl = h ? h->class_lanes : 0;
     if (want_ty < 0 || want_ty > kMaxTY) return fail(XCORR_ERR_INVALID_HINT, "overlap_rows must be 0..4");
@@ -150,8 +157,17 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
     if (want_s < 0 || want_s > H) return fail(XCORR_ERR_INVALID_HINT, "row_slices must be 0..rows");
     const int want_combine = h ? h->combine : 0;
     if (want_combine < 0 || want_combine > 3) return fail(XCORR_ERR_INVALID_HINT, "unknown combine mode");
+    const int want_sk = h ? h->stream_k : 0;
+    if (want_sk < 0 || want_sk > 2) return fail(XCORR_ERR_INVALID_HINT, "stream_k must be 0 (auto), 1 (off) or 2 (on)");
+    if (want_sk == 2 && (want_s > 1 || want_combine == XCORR_COMBINE_STORE || want_combine == XCORR_COMBINE_WORKSPACE))
+        return fail(XCORR_ERR_INVALID_HINT, "stream_k=2 excludes row_slices > 1 and combine=store/workspace");
+    if (want_combine == XCORR_COMBINE_STORE && want_s > 1)
+        return fail(XCORR_ERR_INVALID_HINT, "combine=store needs row_slices=1");
 
-    static const double ty_eff[5] = {0.0, 0.55, 0.80, 0.93, 1.0};
+    const double out_bytes = (double)pm.n_left * pm.m * (2.0 * H - 1) * (2.0 * W - 1) * 4.0;
+    // measured: 2, 3 and 4 y classes per thread run the inner loop about equally fast
+    static const double ty_eff[5] = {0.0, 0.55, 0.95, 1.0, 1.0};
+
     for (int TY = 1; TY <= kMaxTY; ++TY) {
         if (want_ty && TY != want_ty) continue;
         for (int SL = 1; SL <= 32; SL *= 2) {
@@ -159,80 +175,117 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
             TilePlan p{};
             p.H = H; p.W = W; p.TY = TY; p.SL = SL; p.WX = 1; p.WY = 1; p.S = 1;
             finish_plan(p, pm);
-            // warps of a block: all x tiles if they fit, y groups after that
-            const int cap = 8;
-            int WX = want_wx ? want_wx : largest_divisor_at_most(p.NTX, p.NTX > cap ? kMaxWarps : cap);
-            if (!want_wx && p.NTX > kMaxWarps) WX = largest_divisor_at_most(p.NTX, kMaxWarps);
-            int WY = want_wy ? want_wy : largest_divisor_at_most(p.NGY, std::max(1, cap / WX));
-            if (WX * WY > kMaxWarps) continue;
-            p.WX = WX; p.WY = WY;
-
-            // Estimated time = executed multiply-adds of the busiest SM / SM rate, bounded
-            // below by one warp's serial issue time, + cost of combining row slices.
-            // Automatic plans only use combinations that are bit-reproducible: one slice
-            // (plain stores), two slices (two commuting atomic adds onto zero) or any
-            // number through the workspace (fixed-order reduction).
-            const double npairs = (double)pm.n_left * pm.m;
-            const double out_bytes = npairs * (2.0 * H - 1) * (2.0 * W - 1) * 4.0;
-            const double sm_rate = 128.0 * 1.8e9 * 0.8 * ty_eff[TY];
-            const int s_lo = want_s ? want_s : 1;
-            const int s_hi = want_s ? want_s : std::min(H, 64);
-            for (int S = s_lo; S <= s_hi; ++S) {
-                p.S = S;
-                finish_plan(p, pm);
-                if (p.smem_bytes > dev.smem_optin) continue;
-                const double tasks = (double)pm.n_left * p.RG * p.CX * p.CY * S;
-                if (tasks > 2147483647.0) continue;
-                const double rs = (double)H / S;
-                const double macs_per_block = (double)p.threads * rs * p.Wp * TY * kTX;
-                const double busiest = std::ceil(tasks / dev.sm_count);
-                // resident warps per SM (128 registers per thread, 1 KB of shared memory
-                // reserved per block): below ~12 the FFMA pipe idles on shared-memory latency
-                const int by_smem = (int)((dev.smem_optin + 1024) / (p.smem_bytes + 1024));
-                const int by_regs = 65536 / (128 * p.threads);
-                const int resident = std::max(1, std::min(by_smem, by_regs)) * (p.threads / 32);
-                const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident);
-                // shared-memory wavefronts per 8-step chunk against its FFMA issue slots
-                const double wavefronts = 2.0 * TY * std::max(1, p.SL / 8) + 2.0 * std::max(1, p.ML / 8);
-                const double smem_util = 4.0 * wavefronts / (8.0 * TY * kTX);
-                const double smem_eff = 1.0 / (1.0 + std::max(0.0, smem_util - 0.4));
-                const double t_rate = busiest * macs_per_block / (sm_rate * occ_eff * smem_eff) * (rs + 0.25) / rs;
-                // one warp issues at most one FFMA per clock: a lower bound for tiny inputs
-                const double t_serial = 2.0 * rs * p.Wp * TY * kTX / 1.8e9 / 2.0;
-                int comb = want_combine;
-                if (comb == XCORR_COMBINE_AUTO) comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
-                // a memset or a second kernel in front of / behind the main one costs a few us
-                double t_combine = 0.0;
-                if (comb == kAtomic) t_combine = 2e-6 + out_bytes / 3e12 + S * out_bytes / 1.5e12;
-                else if (comb == kWorkspace) t_combine = 3e-6 + (2.0 * S + 1.0) * out_bytes / 3e12;
-                const double t = std::max(t_rate, t_serial) + t_combine;
-                const double score = 1.0 / t;
-                if (score > best_score * 1.0001) {
-                    best_score = score;
-                    best = p;
+            // warps of a block: x tiles first, y groups after that, up to 16 warps
+            std::vector<std::pair<int, int>> shapes;
+            if (want_wx && want_wy) {
+                shapes.emplace_back(want_wx, want_wy);
+            } else {
+                for (int cap : {4, 8, 16}) {
+                    int WX = want_wx ? want_wx : largest_divisor_at_most(p.NTX, cap);
+                    int WY = want_wy ? want_wy : largest_divisor_at_most(p.NGY, std::max(1, cap / WX));
+                    if (WX * WY <= kMaxWarps) shapes.emplace_back(WX, WY);
+                }
+            }
+            for (const auto& shape : shapes) {
+                p.WX = shape.first; p.WY = shape.second;
+                const double sm_rate = 128.0 * 1.8e9 * 0.8 * ty_eff[TY];
+                // candidates: S equal slices per task (S = 1: no split), and stream-K
+                std::vector<std::pair<int, bool>> splits;
+                const bool sk_allowed = want_s <= 1 && want_combine != XCORR_COMBINE_STORE &&
+                                        want_combine != XCORR_COMBINE_WORKSPACE;
+                if (want_sk == 2) {
+                    splits.emplace_back(1, true);
+                } else {
+                    const int s_lo = want_s ? want_s : 1;
+                    const int s_hi = want_s ? want_s : std::min(H, 64);
+                    for (int S = s_lo; S <= s_hi; ++S) splits.emplace_back(S, false);
+                    if (want_sk == 0 && want_s == 0 && sk_allowed) splits.emplace_back(1, true);
+                }
+                for (const auto& split : splits) {
+                    const int S = split.first;
+                    const bool sk = split.second;
+                    p.S = S;
+                    p.stream_k = sk ? 1 : 0;
+                    finish_plan(p, pm);
+                    if (p.smem_bytes > dev.smem_optin) continue;
+                    const double tasks = (double)pm.n_left * p.RG * p.CX * p.CY;
+                    if (tasks * S > 2147483647.0) continue;
+                    // resident warps per SM (128 registers per thread, 1 KB of shared memory
+                    // reserved per block): below ~12 the FFMA pipe idles on shared-memory latency
+                    const int by_smem = (int)((dev.smem_optin + 1024) / (p.smem_bytes + 1024));
+                    const int regs = (p.threads <= kSmallBlockThreads && TY >= 3) ? 168 : 128;
+                    const int by_regs = 65536 / (regs * p.threads);
+                    const int blocks_sm = std::max(1, std::min(by_smem, by_regs));
+                    const int resident = blocks_sm * (p.threads / 32);
+                    const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident);
+                    // shared-memory wavefronts per 8-step chunk against its FFMA issue slots
+                    const double wavefronts = 2.0 * TY * std::max(1, p.SL / 8) + 6.0 * std::max(1, p.ML / 8);
+                    const double smem_util = 4.0 * wavefronts / (8.0 * TY * kTX);
+                    const double smem_eff = 1.0 / (1.0 + std::max(0.0, smem_util - 0.4));
+                    // measured on B200 over the plan space of the benchmark shapes: large blocks
+                    // (12..16 warps sharing one staging) and many right matrices per warp run
+                    // up to ~15 % faster than small blocks / few matrices per warp
+                    const int warps_blk = p.threads / 32;
+                    const double block_prior = warps_blk >= 12 ? 1.0 : warps_blk >= 8 ? 0.93 : warps_blk >= 4 ? 0.87 : 0.8;
+                    const double lanes_prior = p.ML >= 8 ? 1.0 : p.ML == 4 ? 0.96 : p.ML == 2 ? 0.92 : 0.9;
+                    const double rate = sm_rate * occ_eff * smem_eff * block_prior * lanes_prior;
+                    // filling the staging buffers: bytes over ~64 B/clk from L2 plus a latency
+                    // chain, paid once per block (per segment) and hidden only by other blocks
+                    const double t_stage = ((double)p.smem_bytes / 64.0 + 2000.0) / 1.9e9;
+                    double t;
+                    int comb;
+                    unsigned grid;
+                    if (sk) {
+                        const double units = tasks * H;
+                        double G = (double)dev.sm_count * blocks_sm;
+                        if (G > units) G = units;
+                        grid = (unsigned)G;
+                        const double rows_per_block = units / G;
+                        const double macs_per_row = (double)p.threads * p.Wp * TY * kTX;
+                        // every block: its rows, plus a fixed cost per segment (staging, flush)
+                        const double segments = rows_per_block / H + 1.0;
+                        const double t_rate = std::ceil(G / dev.sm_count) * ((rows_per_block + 0.25 * segments) *
+                                              macs_per_row / rate + segments * t_stage);
+                        const double t_serial = rows_per_block * p.Wp * TY * kTX / 1.8e9;
+                        const double split_share = std::min(1.0, 2.0 * G / tasks);   // outputs added atomically
+                        // more than two parts of a task do not commute: last bits then vary run to run
+                        const double order_penalty = tasks >= G ? 1.0 : 1.03;
+                        t = (std::max(t_rate, t_serial) + 4e-6 + out_bytes / 3e12 + split_share * 2.3 * out_bytes / 0.4e12) *
+                            order_penalty;
+                        comb = kAtomic;
+                    } else {
+                        const double rs = (double)H / S;
+                        const double macs_per_block = (double)p.threads * rs * p.Wp * TY * kTX;
+                        const double busiest = std::ceil(tasks * S / dev.sm_count);
+                        const double t_rate = busiest * (macs_per_block / rate * (rs + 0.25) / rs + t_stage);
+                        // one warp issues at most one FFMA per clock: a lower bound for tiny inputs
+                        const double t_serial = rs * p.Wp * TY * kTX / 1.8e9;
+                        comb = want_combine;
+                        if (comb == XCORR_COMBINE_AUTO) comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
+                        // a memset or a second kernel in front of / behind the main one costs a few us
+                        double t_combine = 0.0;
+                        if (comb == kAtomic) t_combine = 4e-6 + out_bytes / 3e12 + S * out_bytes / 0.4e12;
+                        else if (comb == kWorkspace) t_combine = 4e-6 + (2.0 * S + 1.0) * out_bytes / 3e12;
+                        t = std::max(t_rate, t_serial) + t_combine;
+                        grid = (unsigned)(tasks * S);
+                    }
+                    if (best_time < 0.0 || t < best_time * 0.9999) {
+                        best_time = t;
+                        best = p;
+                        best.combine = comb;
+                        best.grid = grid;
+                        best.tasks = (unsigned)tasks;
+                    }
                 }
             }
         }
     }
-    if (best_score < 0.0)
+    if (best_time < 0.0)
         return fail(XCORR_ERR_UNSUPPORTED, "no tile plan fits in shared memory for this shape / these hints");
 
     const unsigned long long total_out = (unsigned long long)pm.n_left * pm.m *
                                          (2ull * H - 1) * (2ull * W - 1);
-    if (best.S == 1) {
-        if (want_combine == XCORR_COMBINE_ATOMIC) best.combine = kAtomic;
-        else if (want_combine == XCORR_COMBINE_WORKSPACE) best.combine = kWorkspace;
-        else best.combine = kStore;
-    } else {
-        if (want_combine == XCORR_COMBINE_STORE)
-            return fail(XCORR_ERR_INVALID_HINT, "combine=store needs row_slices=1");
-        if (want_combine == XCORR_COMBINE_ATOMIC) best.combine = kAtomic;
-        else if (want_combine == XCORR_COMBINE_WORKSPACE) best.combine = kWorkspace;
-        // two addends onto a zeroed word commute: atomics stay bit-reproducible
-        else best.combine = best.S == 2 ? kAtomic : kWorkspace;
-    }
     best.workspace_bytes = best.combine == kWorkspace ? (size_t)best.S * total_out * sizeof(float) : 0;
-    best.grid = (unsigned)((unsigned long long)pm.n_left * best.RG * best.CX * best.CY * best.S);
     *out = best;
     return XCORR_OK;
 }
@@ -256,9 +309,9 @@ std::string describe_plan(const TilePlan& p) {
     char buf[512];
     std::snprintf(buf, sizeof buf,
                   "kernel=tile<TY=%d> grid=(%u,1,1) block=(%d,1,1) smem=%zu plan{H=%d W=%d Hp=%d Wp=%d SL=%d ML=%d "
-                  "WX=%d WY=%d CX=%d CY=%d RG=%d S=%d nstage=%d combine=%s workspace=%zu}",
+                  "WX=%d WY=%d CX=%d CY=%d RG=%d S=%d stream_k=%d tasks=%u nstage=%d combine=%s workspace=%zu}",
                   p.TY, p.grid, p.threads, p.smem_bytes, p.H, p.W, p.Hp, p.Wp, p.SL, p.ML, p.WX, p.WY,
-                  p.CX, p.CY, p.RG, p.S, p.nstage,
+                  p.CX, p.CY, p.RG, p.S, p.stream_k, p.tasks, p.nstage,
                   p.combine == kStore ? "store" : p.combine == kAtomic ? "atomic" : "workspace",
                   p.workspace_bytes);
     return buf;

@@ -133,21 +133,48 @@ __device__ __forceinline__ void tile_row(float (&acc)[TY][kTX], const uint32_t (
     }
 }
 
-// Write one y class's 16 sums of one pass to output row `orow`.  Deliberately a rolled loop
-// over a local-memory copy: the flush runs once per class, pass and slice, and unrolled it
-// costs the hot loop dozens of registers.
-__device__ __forceinline__ void tile_emit_row(float* __restrict__ dst, int orow, int OW, int W, int Wp,
-                                              int cx0, const float* vals, int combine, int pass) {
-    float* o = dst + (size_t)orow * OW;
+// Per-warp staging area of the output flush: 16 rows of 16 sums (+1 padding word per row)
+// and the 16 rows' destination addresses.
+constexpr int kFlushRowWords = kTX + 1;
+constexpr int kFlushBytesPerWarp = 16 * kFlushRowWords * 4 + 16 * 8;
+
+// Write 16 sums per lane to the lanes' own output rows (lane -> one y class of one right
+// matrix; `rowptr` = start of that output row, `has` = the lane has a row to write).  Done by
+// the whole warp through a shared-memory transpose, 16 lanes per output row, so that a store
+// instruction covers two rows of 16 consecutive floats instead of 32 scattered words: the
+// result arrays are as large as the whole working set, and one-word-per-sector stores (or
+// atomics) made the flush a fifth of the run time.  Must be called by all 32 lanes.
+__device__ __forceinline__ void warp_flush(float* scratch, const float (&vals)[kTX], bool has, float* rowptr,
+                                           int cx0, int W, int Wp, int pass, int combine, int lane) {
+    unsigned long long* sbase = reinterpret_cast<unsigned long long*>(scratch + 16 * kFlushRowWords);
+    const unsigned have = __ballot_sync(0xffffffffu, has);
+    const int c = lane & 15;
+    const int cx = cx0 + c;
+    // unwrapped pass: shift sx = cx; wrapped pass: shift sx = cx - Wp
+    const int col = pass == kPassUnwrapped ? cx + W - 1 : cx - Wp + W - 1;
+    const bool ok = pass == kPassUnwrapped ? cx < W : col >= 0;
 #pragma unroll 1
-    for (int j = 0; j < kTX; ++j) {
-        const int cx = cx0 + j;
-        // unwrapped: shift sx = cx; wrapped: shift sx = cx - Wp
-        const int col = pass == kPassUnwrapped ? cx + W - 1 : cx - Wp + W - 1;
-        const bool ok = pass == kPassUnwrapped ? cx < W : col >= 0;
-        if (ok) {
-            if (combine == kAtomic) atomicAdd(o + col, vals[j]); else o[col] = vals[j];
+    for (int hw = 0; hw < 2; ++hw) {
+        const unsigned m16 = (have >> (16 * hw)) & 0xffffu;
+        if (m16 == 0) continue;                       // warp-uniform
+        if ((lane >> 4) == hw) {
+            float* row = scratch + (lane & 15) * kFlushRowWords;
+#pragma unroll
+            for (int j = 0; j < kTX; ++j) row[j] = vals[j];
+            sbase[lane & 15] = has ? reinterpret_cast<unsigned long long>(rowptr) : 0ull;
         }
+        __syncwarp();
+#pragma unroll 1
+        for (int i = 0; i < 8; ++i) {
+            if (((m16 >> (2 * i)) & 3u) == 0) continue;   // warp-uniform
+            const int r = 2 * i + (lane >> 4);
+            float* base = reinterpret_cast<float*>(sbase[r]);
+            if (base != nullptr && ok) {
+                const float v = scratch[r * kFlushRowWords + c];
+                if (combine == kAtomic) atomicAdd(base + col, v); else base[col] = v;
+            }
+        }
+        __syncwarp();
     }
 }
 
@@ -155,10 +182,12 @@ __device__ __forceinline__ void tile_emit_row(float* __restrict__ dst, int orow,
 template<int TY>
 __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict__ dst, uint32_t sL_addr,
                                             uint32_t rmat_addr, int r0, int r1, int cy0, int cya, int cx0,
-                                            bool lane_live) {
+                                            bool lane_live, int combine, float* flush_scratch, int lane) {
     const int H = p.H, W = p.W, Hp = p.Hp, Wp = p.Wp;
     const int OW = 2 * W - 1;
-    const uint32_t stage_bytes = (uint32_t)(p.nstage * p.LS * 4);
+    // staged left rows of this segment: circular (all Hp rows) or a window of rows
+    const int nstage = min(r1 - r0 + p.WY * p.SL * TY - 1, Hp);
+    const uint32_t stage_bytes = (uint32_t)(nstage * p.LS * 4);
     const int cb = cx0 >> 3;                  // first chunk of the tile's own columns
 
 #pragma unroll 1
@@ -173,7 +202,7 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
 #pragma unroll
         for (int t = 0; t < TY; ++t) {
             int i = cy0 + p.SL * t - cya;    // staged row for ry = r0
-            if (i >= p.nstage) i -= p.nstage;
+            if (i >= nstage) i -= nstage;
             lofs[t] = (uint32_t)(i * p.LS * 4);
         }
         float acc[TY][kTX];
@@ -191,8 +220,10 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
 #pragma unroll
             for (int t = 0; t < TY; ++t)
                 if (ry == Hp - (cy0 + p.SL * t) && ry > r0) tsel = t;
-            if (tsel >= 0) {
+            if (__any_sync(0xffffffffu, tsel >= 0)) {
                 float vals[kTX];
+#pragma unroll
+                for (int j = 0; j < kTX; ++j) vals[j] = 0.f;
 #pragma unroll
                 for (int t = 0; t < TY; ++t) {
                     if (t == tsel) {
@@ -200,9 +231,9 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
                         for (int j = 0; j < kTX; ++j) { vals[j] = acc[t][j]; acc[t][j] = 0.f; }
                     }
                 }
-                const int cyt = cy0 + p.SL * tsel;
-                if (lane_live && cyt < H)
-                    tile_emit_row(dst, cyt + H - 1, OW, W, Wp, cx0, vals, p.combine, pass);
+                const int cyt = cy0 + p.SL * (tsel < 0 ? 0 : tsel);
+                const bool has = tsel >= 0 && lane_live && cyt < H;
+                warp_flush(flush_scratch, vals, has, dst + (size_t)(cyt + H - 1) * OW, cx0, W, Wp, pass, combine, lane);
             }
 
             uint32_t lp[TY];
@@ -218,127 +249,145 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
 
         // end of the slice: the sums belong to the wrapped output row if the class wrapped
         // inside (or before) the slice, else to the unwrapped one
-        if (lane_live) {
-            float vals[TY][kTX];
 #pragma unroll
-            for (int t = 0; t < TY; ++t)
-#pragma unroll
-                for (int j = 0; j < kTX; ++j) vals[t][j] = acc[t][j];
-#pragma unroll 1
-            for (int t = 0; t < TY; ++t) {
-                const int cyt = cy0 + p.SL * t;
-                const bool wrapped = r1 > Hp - cyt;
-                const int sy = wrapped ? cyt - Hp : cyt;
-                if (sy > -H && sy < H)
-                    tile_emit_row(dst, sy + H - 1, OW, W, Wp, cx0, vals[t], p.combine, pass);
-            }
+        for (int t = 0; t < TY; ++t) {
+            const int cyt = cy0 + p.SL * t;
+            const bool wrapped = r1 > Hp - cyt;
+            const int sy = wrapped ? cyt - Hp : cyt;
+            const bool has = lane_live && sy > -H && sy < H;
+            warp_flush(flush_scratch, acc[t], has, dst + (size_t)(sy + H - 1) * OW, cx0, W, Wp, pass, combine, lane);
         }
     }
 }
 
-template<int TY>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) tile_kernel(const TileArgs a) {
+// BOUND = 384: blocks of up to 12 warps, up to 168 registers per thread (nothing of the hot
+// loop spills for TY = 4); BOUND = 512: blocks of 13..16 warps at 128 registers.
+template<int TY, int BOUND>
+__global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     extern __shared__ __align__(16) float smem[];
     const TilePlan& p = a.p;
     float* sL = smem;
     float* sR = smem + (size_t)p.nstage * p.LS;
-
-    // ---- which task
-    unsigned task = blockIdx.x;
-    const int s = task % p.S;   task /= p.S;
-    const int bx = task % p.CX; task /= p.CX;
-    const int by = task % p.CY; task /= p.CY;
-    const int rg = task % p.RG;
-    const int l = task / p.RG;
-
     const int H = p.H, W = p.W, Hp = p.Hp, Wp = p.Wp;
-    const int r0 = (int)(((long long)s * H) / p.S);
-    const int r1 = (int)(((long long)(s + 1) * H) / p.S);
-    const int cls_per_block = p.WY * p.SL * TY;
-    const int cya = by * cls_per_block;          // first y class of the block
-    int rowbase = r0 + cya;
-    if (rowbase >= Hp) rowbase -= Hp;
-
     const int tid = threadIdx.x, nthr = blockDim.x;
 
-    // ---- stage the left rows: staged row i holds left row (rowbase + i) mod Hp, zeros
-    //      where the padded matrix is zero.
-    {
-        const float* gL = a.left + (size_t)l * H * W;
-        const int units = p.LS >> 2;             // float4 per staged row (last one is padding)
-        const int total = p.nstage * units;
-        for (int idx = tid; idx < total; idx += nthr) {
-            const int i = idx / units, c4 = idx - i * units;
-            int row = rowbase + i;
-            if (row >= Hp) row -= Hp;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            const int x = c4 * 4;
-            if (row < H && x < W) {
-                const float* g = gL + (size_t)row * W + x;
-                if (a.vec_ok) {
-                    v = __ldg(reinterpret_cast<const float4*>(g));
-                } else {
-                    v.x = __ldg(g);
-                    if (x + 1 < W) v.y = __ldg(g + 1);
-                    if (x + 2 < W) v.z = __ldg(g + 2);
-                    if (x + 3 < W) v.w = __ldg(g + 3);
-                }
-            }
-            *reinterpret_cast<float4*>(sL + (size_t)i * p.LS + x) = v;
-        }
+    // ---- the block's share of the work, in units of (block task, right row).
+    //      Slices: block = (task, slice), one segment.  Stream-K: the units of all tasks are
+    //      cut into gridDim.x equal ranges; a range is one or more segments, each a run of
+    //      rows of one task.
+    unsigned long long u, uend;
+    int slice = 0;
+    if (p.stream_k) {
+        const unsigned long long total = (unsigned long long)p.tasks * H;
+        u = total * blockIdx.x / gridDim.x;
+        uend = total * (blockIdx.x + 1) / gridDim.x;
+    } else {
+        const unsigned task = blockIdx.x / p.S;
+        slice = blockIdx.x - task * p.S;
+        u = (unsigned long long)task * H + (unsigned)(((long long)slice * H) / p.S);
+        uend = (unsigned long long)task * H + (unsigned)(((long long)(slice + 1) * H) / p.S);
     }
-    // ---- stage rows [r0, r1) of the block's ML right matrices, zeros for the padding
-    //      columns and for matrices past the end of the left's group.
-    {
-        const int units = Wp >> 2;
-        const int rs = r1 - r0;
-        const int per_mat = rs * units;
-        const int total = p.ML * per_mat;
-        for (int idx = tid; idx < total; idx += nthr) {
-            const int m = idx / per_mat;
-            const int rem = idx - m * per_mat;
-            const int rr = rem / units, c4 = rem - rr * units;
-            const unsigned j = (unsigned)rg * p.ML + m;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            const int x = c4 * 4;
-            if (j < a.pm.m && x < W) {
-                const size_t rmat = (size_t)l * a.pm.right_stride + j;
-                const float* g = a.right + (rmat * H + (r0 + rr)) * W + x;
-                if (a.vec_ok) {
-                    v = __ldg(reinterpret_cast<const float4*>(g));
-                } else {
-                    v.x = __ldg(g);
-                    if (x + 1 < W) v.y = __ldg(g + 1);
-                    if (x + 2 < W) v.z = __ldg(g + 2);
-                    if (x + 3 < W) v.w = __ldg(g + 3);
-                }
-            }
-            *reinterpret_cast<float4*>(sR + (size_t)m * p.RMS + (size_t)rr * Wp + x) = v;
-        }
-    }
-    __syncthreads();
 
-    // ---- which tile
     const int warp = tid >> 5, lane = tid & 31;
     const int wx = warp % p.WX, wy = warp / p.WX;
-    const int tile_x = bx * p.WX + wx;
-    const int grp_y = by * p.WY + wy;
-    if (tile_x >= p.NTX || grp_y >= p.NGY) return;
-
     const int q = lane & (p.SL - 1);
     const int m = lane >> p.logSL;
-    const unsigned jright = (unsigned)rg * p.ML + m;
-    const bool lane_live = jright < a.pm.m;
-    const int cx0 = tile_x * kTX;
-    const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
-
-    const size_t out_mat = (size_t)l * a.pm.m + jright;
-    float* dst = (p.combine == kWorkspace ? a.ws + (size_t)s * a.total_out : a.out)
-                 + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
     const uint32_t sL_addr = (uint32_t)__cvta_generic_to_shared(sL);
     const uint32_t rmat_addr = (uint32_t)__cvta_generic_to_shared(sR + (size_t)m * p.RMS);
+    float* flush_scratch = reinterpret_cast<float*>(
+        reinterpret_cast<char*>(sR + (size_t)p.ML * p.RMS) + (size_t)warp * kFlushBytesPerWarp);
 
-    tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live);
+    while (u < uend) {
+        unsigned task = (unsigned)(u / (unsigned)H);
+        const int r0 = (int)(u - (unsigned long long)task * H);
+        const int r1 = (int)min((unsigned long long)H, r0 + (uend - u));
+        u += (unsigned)(r1 - r0);
+        const int bx = task % p.CX; task /= p.CX;
+        const int by = task % p.CY; task /= p.CY;
+        const int rg = task % p.RG;
+        const int l = task / p.RG;
+        // a whole task is written with plain stores, a part of one is added to the zeroed output
+        const int combine = p.stream_k ? ((r0 == 0 && r1 == H) ? (int)kStore : (int)kAtomic) : p.combine;
+
+        const int cls_per_block = p.WY * p.SL * TY;
+        const int cya = by * cls_per_block;          // first y class of the block
+        int rowbase = r0 + cya;
+        if (rowbase >= Hp) rowbase -= Hp;
+
+        // ---- stage the left rows: staged row i holds left row (rowbase + i) mod Hp, zeros
+        //      where the padded matrix is zero.
+        {
+            const float* gL = a.left + (size_t)l * H * W;
+            const int units = p.LS >> 2;             // float4 per staged row (last one is padding)
+            const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);
+            const int total = nstage * units;
+            for (int idx = tid; idx < total; idx += nthr) {
+                const int i = idx / units, c4 = idx - i * units;
+                int row = rowbase + i;
+                if (row >= Hp) row -= Hp;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                const int x = c4 * 4;
+                if (row < H && x < W) {
+                    const float* g = gL + (size_t)row * W + x;
+                    if (a.vec_ok) {
+                        v = __ldg(reinterpret_cast<const float4*>(g));
+                    } else {
+                        v.x = __ldg(g);
+                        if (x + 1 < W) v.y = __ldg(g + 1);
+                        if (x + 2 < W) v.z = __ldg(g + 2);
+                        if (x + 3 < W) v.w = __ldg(g + 3);
+                    }
+                }
+                *reinterpret_cast<float4*>(sL + (size_t)i * p.LS + x) = v;
+            }
+        }
+        // ---- stage rows [r0, r1) of the block's ML right matrices, zeros for the padding
+        //      columns and for matrices past the end of the left's group.
+        {
+            const int units = Wp >> 2;
+            const int rs = r1 - r0;
+            const int per_mat = rs * units;
+            const int total = p.ML * per_mat;
+            for (int idx = tid; idx < total; idx += nthr) {
+                const int mm = idx / per_mat;
+                const int rem = idx - mm * per_mat;
+                const int rr = rem / units, c4 = rem - rr * units;
+                const unsigned j = (unsigned)rg * p.ML + mm;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                const int x = c4 * 4;
+                if (j < a.pm.m && x < W) {
+                    const size_t rmat = (size_t)l * a.pm.right_stride + j;
+                    const float* g = a.right + (rmat * H + (r0 + rr)) * W + x;
+                    if (a.vec_ok) {
+                        v = __ldg(reinterpret_cast<const float4*>(g));
+                    } else {
+                        v.x = __ldg(g);
+                        if (x + 1 < W) v.y = __ldg(g + 1);
+                        if (x + 2 < W) v.z = __ldg(g + 2);
+                        if (x + 3 < W) v.w = __ldg(g + 3);
+                    }
+                }
+                *reinterpret_cast<float4*>(sR + (size_t)mm * p.RMS + (size_t)rr * Wp + x) = v;
+            }
+        }
+        __syncthreads();
+
+        // ---- this warp's tile
+        const int tile_x = bx * p.WX + wx;
+        const int grp_y = by * p.WY + wy;
+        if (tile_x < p.NTX && grp_y < p.NGY) {
+            const unsigned jright = (unsigned)rg * p.ML + m;
+            const bool lane_live = jright < a.pm.m;
+            const int cx0 = tile_x * kTX;
+            const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
+            const size_t out_mat = (size_t)l * a.pm.m + jright;
+            float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out : a.out)
+                         + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
+            tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live, combine,
+                            flush_scratch, lane);
+        }
+        __syncthreads();                          // the next segment reuses the staging buffers
+    }
 }
 
 // Sum the per-slice partial images in slice order.  Slice s wrote output row `orow`
@@ -448,15 +497,21 @@ __global__ void __launch_bounds__(1024) ffma_probe_kernel(float* sink, float b, 
 // ------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------
-template<int TY>
-static cudaError_t launch_tile_ty(const TileArgs& a, cudaStream_t stream) {
+template<int TY, int BOUND>
+static cudaError_t launch_tile_variant(const TileArgs& a, cudaStream_t stream) {
     if (a.p.smem_bytes > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(tile_kernel<TY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(tile_kernel<TY, BOUND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)a.p.smem_bytes);
         if (e != cudaSuccess) return e;
     }
-    tile_kernel<TY><<<a.p.grid, a.p.threads, a.p.smem_bytes, stream>>>(a);
+    tile_kernel<TY, BOUND><<<a.p.grid, a.p.threads, a.p.smem_bytes, stream>>>(a);
     return cudaGetLastError();
+}
+
+template<int TY>
+static cudaError_t launch_tile_ty(const TileArgs& a, cudaStream_t stream) {
+    return a.p.threads <= kSmallBlockThreads ? launch_tile_variant<TY, kSmallBlockThreads>(a, stream)
+                                             : launch_tile_variant<TY, kMaxWarps * 32>(a, stream);
 }
 
 cudaError_t launch_tile(const TileArgs& a, cudaStream_t stream) {

@@ -22,6 +22,7 @@ namespace xcorr {
 constexpr int kTX = 16;           // x classes per thread (one 16-wide tile)
 constexpr int kMaxTY = 4;         // y classes per thread
 constexpr int kMaxWarps = 16;     // warps per block
+constexpr int kSmallBlockThreads = 384;  // blocks up to this size run the 168-register build of the kernel
 constexpr int kSmemLimit = 227 * 1024;
 
 enum Combine : int { kStore = 1, kAtomic = 2, kWorkspace = 3 };
@@ -47,10 +48,12 @@ struct TilePlan {
     int NGY;           // y-class groups = Hp / (SL*TY)
     int WX, WY;        // warps of a block along x tiles / y groups
     int CX, CY;        // blocks needed along x tiles / y groups
-    int S;             // row slices of the right matrices
+    int S;             // row slices of the right matrices (1 when stream_k)
+    int stream_k;      // 1: the (task, row) units are cut evenly over `grid` blocks
+    unsigned tasks;    // block tasks = n_left * RG * CX * CY
     int RSmax;         // rows of the longest slice
     int RG;            // right-matrix groups per left = ceil(m / ML)
-    int nstage;        // left rows staged in shared memory
+    int nstage;        // left rows staged in shared memory (at most; a short segment stages fewer)
     int LS;            // floats between staged left rows (Wp + 4: row*LS/4 odd -> conflict-free float4)
     int RMS;           // floats between the staged right matrices of one block
     int threads;

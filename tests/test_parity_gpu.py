@@ -104,6 +104,10 @@ TILE_VARIANTS = [
     dict(overlap_rows=4, class_lanes=32, row_slices=7, combine="workspace", warps_x=2, warps_y=1),
     dict(overlap_rows=1, class_lanes=4, row_slices=1, warps_x=1, warps_y=3),
     dict(overlap_rows=2, class_lanes=8, row_slices=4, combine="workspace", warps_x=3, warps_y=2),
+    dict(stream_k=2),
+    dict(stream_k=2, overlap_rows=2, class_lanes=8, warps_x=1, warps_y=2),
+    dict(stream_k=2, overlap_rows=4, class_lanes=2, warps_x=2, warps_y=1),
+    dict(stream_k=1),
 ]
 
 
@@ -159,7 +163,8 @@ def test_invalid_hints_are_rejected(xc):
     left, right = seeded_inputs(8, 8, 1, 1, 1)
     for bad in (dict(overlap_rows=5), dict(class_lanes=3), dict(warps_x=5, warps_y=4), dict(row_slices=9),
                 dict(kernel=9), dict(kernel="overlap_wise", block_threads=100),
-                dict(combine="store", row_slices=2)):
+                dict(combine="store", row_slices=2), dict(stream_k=3), dict(stream_k=2, row_slices=2),
+                dict(stream_k=2, combine="workspace")):
         with pytest.raises(xc.XcorrError) as e:
             gpu_run(xc, "one_to_one", left, right, xc.make_hints(**bad))
         assert e.value.status == 3, bad
