@@ -144,6 +144,34 @@ XCORR_API xcorr_status xcorr_n_to_m_f32(const float* d_left, const float* d_righ
                                         const xcorr_hints* hints,
                                         void* d_workspace, size_t workspace_bytes, void* stream);
 
+/* One pair without any allocation.  (No counterpart in the reference: its algorithm classes
+ * always allocate their device buffers themselves, one_to_one.hpp:112-118.)
+ *
+ * For callers that must not, or cannot, call cudaMalloc at the point where they need a result:
+ * code running inside a real-time or latency-critical loop, a plug-in whose host forbids device
+ * allocation after start-up, a process whose memory pool is owned by another runtime.  The single
+ * 256x256-sized pair is the case that needs scratch memory at all (its rows are divided over
+ * all SMs and the partial results are summed afterwards, see xcorr_workspace_bytes); this entry
+ * point runs exactly that path with the partial results in an array that is part of the library
+ * image instead of a caller-provided workspace.
+ *
+ *  - The array holds xcorr_noalloc_scratch_bytes() = 32 MiB and exists on every GPU that loads the
+ *    library, from load to process exit, whether this entry point is used or not.
+ *  - Results of more than 32 MiB, i.e. (2*rows-1)*(2*cols-1) > 8 Mi floats (inputs beyond about
+ *    1024 x 1024), are refused with XCORR_ERR_UNSUPPORTED and a message naming the limit.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
+ *    keeps it; make that first call before any stream capture starts on the device.
+ *  - All calls share the array, and it keeps what the last call left in it.  Nothing has to be
+ *    cleared between calls -- every word the summation reads was written earlier in the same
+ *    call -- but two calls that overlap on one GPU (different streams, different threads) race on
+ *    it: issue them on one stream or otherwise order them.
+ *  - Calls no cudaMalloc / cudaFree and no allocating library routine; asynchronous on `stream`
+ *    like the other device entry points; the result equals xcorr_one_to_one_f32 with
+ *    combine = workspace up to the float rounding of a possibly different number of row slices. */
+XCORR_API xcorr_status xcorr_one_to_one_noalloc_f32(const float* d_left, const float* d_right, float* d_out,
+                                                    uint32_t rows, uint32_t cols, void* stream);
+XCORR_API size_t xcorr_noalloc_scratch_bytes(void);
+
 /* Mode-generic form of the four above (same contract). */
 XCORR_API xcorr_status xcorr_run_f32(int32_t mode, const float* d_left, const float* d_right, float* d_out,
                                      uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,

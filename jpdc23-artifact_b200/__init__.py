@@ -82,6 +82,9 @@ def lib() -> C.CDLL:
     L.xcorr_one_to_many_f32.argtypes = [vp, vp, vp, u32, u32, u32, hp, vp, sz, vp]
     L.xcorr_n_to_mn_f32.argtypes = [vp, vp, vp, u32, u32, u32, u32, hp, vp, sz, vp]
     L.xcorr_n_to_m_f32.argtypes = [vp, vp, vp, u32, u32, u32, u32, hp, vp, sz, vp]
+    L.xcorr_one_to_one_noalloc_f32.argtypes = [vp, vp, vp, u32, u32, vp]
+    L.xcorr_noalloc_scratch_bytes.argtypes = []
+    L.xcorr_noalloc_scratch_bytes.restype = sz
     L.xcorr_workspace_bytes.argtypes = [i32, u32, u32, u32, u32, hp]
     L.xcorr_workspace_bytes.restype = sz
     L.xcorr_describe_plan.argtypes = [i32, u32, u32, u32, u32, hp, C.c_char_p, sz]

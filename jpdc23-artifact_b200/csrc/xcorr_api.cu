@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cmath>
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -142,7 +143,7 @@ void finish_plan(TilePlan& p, const PairMap& pm) {
 // run of whole tasks plus at most two partial ones, partial ones added atomically).
 // Every candidate gets an estimated time; the smallest wins.
 xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, const DeviceInfo& dev,
-                       TilePlan* out) {
+                       TilePlan* out, size_t max_workspace_bytes = SIZE_MAX) {
     TilePlan best{};
     double best_time = -1.0;
     const int want_ty = h ? h->overlap_rows : 0;
@@ -208,6 +209,8 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
                     p.stream_k = sk ? 1 : 0;
                     finish_plan(p, pm);
                     if (p.smem_bytes > dev.smem_optin) continue;
+                    if (!sk && want_combine == XCORR_COMBINE_WORKSPACE &&
+                        (double)S * out_bytes > (double)max_workspace_bytes) continue;
                     const double tasks = (double)pm.n_left * p.RG * p.CX * p.CY;
                     if (tasks * S > 2147483647.0) continue;
                     // resident warps per SM (128 registers per thread, 1 KB of shared memory
@@ -387,6 +390,50 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
     return XCORR_OK;
 }
 
+// ---- entry point that allocates nothing --------------------------------------------------
+xcorr_status run_one_to_one_noalloc(const float* d_left, const float* d_right, float* d_out,
+                                    uint32_t rows, uint32_t cols, void* stream_v) {
+    if (!d_left || !d_right || !d_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+    PairMap pm{};
+    xcorr_status st = check_sizes(XCORR_ONE_TO_ONE, rows, cols, 1, 1, &pm);
+    if (st != XCORR_OK) return st;
+    const int H = (int)rows, W = (int)cols;
+    const unsigned long long total_out = (2ull * H - 1) * (2ull * W - 1);
+    const size_t limit = noalloc_scratch_bytes();
+    if (total_out * sizeof(float) > limit) {
+        char msg[256];
+        std::snprintf(msg, sizeof msg,
+                      "a %u x %u pair has a result of %llu bytes; the built-in scratch of the entry point that "
+                      "allocates nothing holds %zu bytes (results up to %zu floats, e.g. 1024 x 1024 inputs)",
+                      rows, cols, total_out * 4ull, limit, limit / sizeof(float));
+        return fail(XCORR_ERR_UNSUPPORTED, msg);
+    }
+    DeviceInfo dev;
+    if ((st = current_device_info(&dev)) != XCORR_OK) return st;
+    // the scratch array's device address, looked up once per device with that device current
+    float* scratch = nullptr;
+    XC_CUDA(noalloc_scratch_address(&scratch));
+    // same kernels and plan space as xcorr_one_to_one_f32 with combine = workspace, the
+    // number of row slices capped by what the scratch array holds
+    xcorr_hints hints{};
+    hints.kernel = XCORR_KERNEL_TILE;
+    hints.combine = XCORR_COMBINE_WORKSPACE;
+    TilePlan p{};
+    if ((st = plan_tile(pm, H, W, &hints, dev, &p, limit)) != XCORR_OK) return st;
+    TileArgs a{};
+    a.left = d_left; a.right = d_right; a.out = d_out; a.ws = scratch;
+    a.p = p; a.pm = pm; a.total_out = total_out;
+    a.vec_ok = (W % 4 == 0) && reinterpret_cast<uintptr_t>(d_left) % 16 == 0 &&
+               reinterpret_cast<uintptr_t>(d_right) % 16 == 0;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    t_last_launch = describe_plan(p);
+    XC_CUDA(launch_tile(a, stream));
+    ++t_launch_count;
+    XC_CUDA(launch_reduce_partials(scratch, d_out, total_out, H, W, p.Hp, p.S, dev.sm_count, stream));
+    ++t_launch_count;
+    return XCORR_OK;
+}
+
 // ---- host-buffer front end -------------------------------------------------------------
 struct HostCache {
     std::mutex mutex;
@@ -460,6 +507,13 @@ xcorr_status xcorr_one_to_one_f32(const float* d_left, const float* d_right, flo
     return run_device(XCORR_ONE_TO_ONE, d_left, d_right, d_out, rows, cols, 1, 1, hints,
                       d_workspace, workspace_bytes, stream);
 }
+
+xcorr_status xcorr_one_to_one_noalloc_f32(const float* d_left, const float* d_right, float* d_out,
+                                          uint32_t rows, uint32_t cols, void* stream) {
+    return run_one_to_one_noalloc(d_left, d_right, d_out, rows, cols, stream);
+}
+
+size_t xcorr_noalloc_scratch_bytes(void) { return noalloc_scratch_bytes(); }
 
 xcorr_status xcorr_one_to_many_f32(const float* d_left, const float* d_right, float* d_out,
                                    uint32_t rows, uint32_t cols, uint32_t n_right, const xcorr_hints* hints,

@@ -10,6 +10,7 @@
 // plus the fixed-order reduction of workspace partials and the FFMA peak probe.
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <mutex>
 
 #include "xcorr_plan.h"
 #include "xcorr_launch.h"
@@ -563,6 +564,40 @@ cudaError_t launch_warp_per_overlap(const float* left, const float* right, float
     *grid_out = grid;
     *block_out = block;
     return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// scratch for callers that cannot allocate
+// ------------------------------------------------------------------------------------------
+// Partial images of xcorr_one_to_one_noalloc_f32: S * (2*rows-1) * (2*cols-1) floats, written
+// by tile_kernel and summed by reduce_partials_kernel.  A file-scope device array: it exists
+// on every GPU that loads this library, from load until the process exits, and is shared by
+// all calls (calls that overlap on one GPU would race on it).
+constexpr size_t kNoAllocScratchFloats = (size_t)8 << 20;            // 32 MiB
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+size_t noalloc_scratch_bytes() { return kNoAllocScratchFloats * sizeof(float); }
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address
+// a kernel could be given: the address is asked for once per device, with that device
+// current, and cached.
+cudaError_t noalloc_scratch_address(float** ptr) {
+    constexpr int kDevices = 64;
+    static std::mutex mutex;
+    static float* address[kDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (address[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        address[dev] = static_cast<float*>(p);
+    }
+    *ptr = address[dev];
+    return cudaSuccess;
 }
 
 cudaError_t launch_ffma_probe(float* sink, int iters, int blocks, cudaStream_t stream) {

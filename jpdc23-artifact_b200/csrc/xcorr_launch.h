@@ -16,4 +16,9 @@ cudaError_t launch_warp_per_overlap(const float* left, const float* right, float
                                     int sm_count, dim3* grid_out, dim3* block_out, cudaStream_t stream);
 cudaError_t launch_ffma_probe(float* sink, int iters, int blocks, cudaStream_t stream);
 
+// Built-in scratch of the entry point that allocates nothing: size, and the array's device
+// address on the current device (looked up once per device).
+size_t noalloc_scratch_bytes();
+cudaError_t noalloc_scratch_address(float** ptr);
+
 }  // namespace xcorr
