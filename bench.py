@@ -79,6 +79,32 @@ def config_inputs(k, rank=0):
     return left, right
 
 
+def strong_shard(xc, k, world, rank):
+    """The part of configuration k that rank `rank` of `world` owns when the configuration
+    itself is split (strong scaling): (units_first, units_count, n_left, n_right) where the
+    units are right matrices for one_to_many and left matrices (with all / their own rights)
+    for n_to_m / n_to_mn.  one_to_one does not shard: rank 0 owns it."""
+    mode, r, c, nl, nr = CONFIGS[k]
+    if mode == "one_to_one":
+        return (0, 1, 1, 1) if rank == 0 else (0, 0, 0, 0)
+    units = nr if mode == "one_to_many" else nl
+    first, count = xc.shard_range(units, world, rank)
+    if mode == "one_to_many":
+        return first, count, 1, count
+    if mode == "n_to_m":
+        return first, count, count, nr
+    return first, count, count, count * (nr // nl)
+
+
+def max_over_ranks(values, dist=None, device="cpu"):
+    """Element-wise maximum of a list of floats over all ranks (identity without a group)."""
+    import torch
+    vec = torch.tensor(values, dtype=torch.float64, device=device)
+    if dist is not None and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(vec, op=dist.ReduceOp.MAX)
+    return vec.cpu().tolist()
+
+
 def load_package():
     name = "jpdc23_artifact_b200"
     if name in sys.modules:
@@ -206,19 +232,25 @@ def run_reference_arm(args):
     threads = os.cpu_count() or 1
     vals = []
     desc = kind = ""
-    for _ in range(args.warmup if args.warmup < 1 else 1):
-        cpu_baseline(2.0, threads)
-    per_step = max(3.0, min(30.0, 120.0 / max(1, args.steps)))
+    # Each step is a bounded sample of the workload (about --cpu-seconds of CPU work; the one
+    # 256x256 pair is indivisible for the reference code and takes ~2.5 s on one core).  The
+    # whole run is kept within a few minutes by capping the number of steps actually timed;
+    # the value is a rate (GFLOP/s over the samples), so fewer steps do not change its meaning.
+    per_step = max(1.0, min(30.0, args.cpu_seconds))
+    budget_s = 150.0
+    steps_run = max(1, min(args.steps, int(budget_s / (per_step * 0.5 + 2.5))))
+    for _ in range(min(args.warmup, 1)):
+        cpu_baseline(min(per_step, 2.0), threads)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps_run):
         v, kind, desc = cpu_baseline(per_step, threads)
         vals.append(v)
     wall = time.perf_counter() - t0
     value = statistics.mean(vals)
     line = {
         "impl": "reference", "metric": "xcorr_gflops", "value": value, "unit": "GFLOP/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * wall / args.steps, "higher_is_better": True, "scaling": "weak",
+        "n_gpus": args.gpus, "steps": steps_run, "steps_requested": args.steps, "warmup": min(args.warmup, 1),
+        "ms_per_step": 1e3 * wall / steps_run, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": "GFLOP/s", "cores": threads, "kind": kind,
@@ -253,7 +285,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--cpu-seconds", type=float, default=6.0)
     ap.add_argument("--only", default="", help="comma-separated subset of C1..C5 (profiling runs; "
                     "the default line always covers all five)")
     ap.add_argument("--hints", default="", help='JSON {"C3": {"overlap_rows": 4, ...}}: force plan hints of '
@@ -349,19 +381,11 @@ def main():
         for k, (mode, r, c, nl, nr) in CONFIGS.items():
             if mode == "one_to_one":
                 continue
-            units = nr if mode == "one_to_many" else nl
-            first, count = xc.shard_range(units, world, rank)
+            first, count, a_nl, a_nr = strong_shard(xc, k, world, rank)
             if count == 0:
                 strong_ms[k] = 0.0
                 continue
             d = dev[k]
-            m = nr // nl if mode == "n_to_mn" else nr
-            if mode == "one_to_many":
-                a_nl, a_nr = 1, count
-            elif mode == "n_to_m":
-                a_nl, a_nr = count, nr
-            else:
-                a_nl, a_nr = count, count * m
 
             def shard_launch():
                 xc.run_device(mode, d["left"].data_ptr(), d["right"].data_ptr(), d["out"].data_ptr(),
@@ -408,11 +432,8 @@ def main():
     ffma_flops, _ = xc.ffma_peak_probe(stream)
 
     # ---- max over ranks
-    vec = torch.tensor([region_ms, e2e_ms] + [per_ms[k] for k in CONFIGS] +
-                       [strong_ms.get(k, 0.0) for k in CONFIGS], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(vec, op=dist.ReduceOp.MAX)
-    vec = vec.cpu().tolist()
+    vec = max_over_ranks([region_ms, e2e_ms] + [per_ms[k] for k in CONFIGS] +
+                         [strong_ms.get(k, 0.0) for k in CONFIGS], dist if world > 1 else None, "cuda")
     region_ms, e2e_ms = vec[0], vec[1]
     per_ms_max = dict(zip(CONFIGS, vec[2:2 + len(CONFIGS)]))
     strong_max = dict(zip(CONFIGS, vec[2 + len(CONFIGS):]))

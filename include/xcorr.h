@@ -100,12 +100,18 @@ typedef struct xcorr_hints {
     int32_t warps_y;           /* TILE: warps of a block along y-class groups */
     int32_t row_slices;        /* TILE: number of slices the right rows are split into (cf. rows_per_thread) */
     int32_t block_threads;     /* OVERLAP_WISE / WARP_PER_OVERLAP: threads per block */
-    int32_t stream_k;          /* TILE: 0 auto; 1 never; 2 always cut the (block task, right row) units of
-                                  all tasks evenly over one resident wave of blocks.  A block then works on
-                                  whole tasks (plain stores) and at most two partial ones (atomic adds onto
-                                  the zeroed output); when a task ends up in more than two parts the last
-                                  bits of a result can differ between runs, as with the reference's
-                                  atomicAdd "work distribution" kernels */
+    int32_t schedule;          /* TILE: how work reaches the blocks.  0 auto;
+                                  1 static: one block per block task (and row slice);
+                                  2 stream-K: the (block task, right row) units of all tasks are cut evenly
+                                    over one resident wave of blocks; a block works on whole tasks (plain
+                                    stores) and at most two partial ones (atomic adds onto the zeroed
+                                    output).  A task that ends up in more than two parts makes the last
+                                    bits of a result vary between runs, as with the reference's atomicAdd
+                                    "work distribution" kernels;
+                                  3 warp queue: the warp tasks (one 16-wide x tile and one y group of one
+                                    matrix group, all rows) are cut evenly over one resident wave of
+                                    blocks whose warps take them from a shared counter: plain stores,
+                                    bit-reproducible, balanced to one warp task per SM */
     int32_t reserved[7];
 } xcorr_hints;
 

@@ -126,14 +126,14 @@ void finish_plan(TilePlan& p, const PairMap& pm) {
     p.CY = (p.NGY + p.WY - 1) / p.WY;
     p.RSmax = (p.H + p.S - 1) / p.S;
     p.RG = (int)((pm.m + p.ML - 1) / p.ML);
-    const int cls_per_block = p.WY * p.SL * p.TY;
+    const int cls_per_block = p.schedule == kSchedWarpQueue ? p.Hp : p.WY * p.SL * p.TY;
     p.nstage = std::min(p.RSmax + cls_per_block - 1, p.Hp);
     p.LS = p.Wp + 4;
     p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
     p.threads = 32 * p.WX * p.WY;
     // staged left rows, staged right rows, per-warp flush staging (16 x 17 floats + 16 addresses)
     p.smem_bytes = ((size_t)p.nstage * p.LS + (size_t)p.ML * p.RMS) * sizeof(float) +
-                   (size_t)(p.threads / 32) * (16 * (kTX + 1) * 4 + 16 * 8);
+                   (size_t)(p.threads / 32) * (16 * (kTX + 1) * 4 + 16 * 8) + 16;   // + the warp queue's counter
 }
 
 // Per-shape plan of the tile kernel: micro-tile height, lane split, block shape and how the
@@ -158,10 +158,15 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
     if (want_s < 0 || want_s > H) return fail(XCORR_ERR_INVALID_HINT, "row_slices must be 0..rows");
     const int want_combine = h ? h->combine : 0;
     if (want_combine < 0 || want_combine > 3) return fail(XCORR_ERR_INVALID_HINT, "unknown combine mode");
-    const int want_sk = h ? h->stream_k : 0;
-    if (want_sk < 0 || want_sk > 2) return fail(XCORR_ERR_INVALID_HINT, "stream_k must be 0 (auto), 1 (off) or 2 (on)");
-    if (want_sk == 2 && (want_s > 1 || want_combine == XCORR_COMBINE_STORE || want_combine == XCORR_COMBINE_WORKSPACE))
-        return fail(XCORR_ERR_INVALID_HINT, "stream_k=2 excludes row_slices > 1 and combine=store/workspace");
+    const int want_sched = h ? h->schedule : 0;
+    if (want_sched < 0 || want_sched > 3)
+        return fail(XCORR_ERR_INVALID_HINT, "schedule must be 0 (auto), 1 (static), 2 (stream-K) or 3 (warp queue)");
+    if (want_sched == kSchedStreamK &&
+        (want_s > 1 || want_combine == XCORR_COMBINE_STORE || want_combine == XCORR_COMBINE_WORKSPACE))
+        return fail(XCORR_ERR_INVALID_HINT, "schedule=2 (stream-K) excludes row_slices > 1 and combine=store/workspace");
+    if (want_sched == kSchedWarpQueue &&
+        (want_s > 1 || want_combine == XCORR_COMBINE_ATOMIC || want_combine == XCORR_COMBINE_WORKSPACE))
+        return fail(XCORR_ERR_INVALID_HINT, "schedule=3 (warp queue) writes with plain stores: no row_slices, no atomic/workspace");
     if (want_combine == XCORR_COMBINE_STORE && want_s > 1)
         return fail(XCORR_ERR_INVALID_HINT, "combine=store needs row_slices=1");
 
@@ -174,9 +179,22 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
         for (int SL = 1; SL <= 32; SL *= 2) {
             if (want_sl && SL != want_sl) continue;
             TilePlan p{};
-            p.H = H; p.W = W; p.TY = TY; p.SL = SL; p.WX = 1; p.WY = 1; p.S = 1;
+            p.H = H; p.W = W; p.TY = TY; p.SL = SL; p.WX = 1; p.WY = 1; p.S = 1; p.schedule = kSchedStatic;
             finish_plan(p, pm);
             // warps of a block: x tiles first, y groups after that, up to 16 warps
+            // block shapes: x tiles first, y groups after that, up to 16 warps; the warp
+            // queue only needs a warp count (WX = warps, WY = 1)
+            struct Cand { int WX, WY, S, sched; };
+            std::vector<Cand> cands;
+            const bool static_ok = want_sched == 0 || want_sched == kSchedStatic;
+            const bool streamk_ok = (want_sched == 0 || want_sched == kSchedStreamK) && want_s <= 1 &&
+                                    want_combine != XCORR_COMBINE_STORE && want_combine != XCORR_COMBINE_WORKSPACE;
+            // The warp queue is only taken on request: measured on B200 it loses to the static
+            // schedule on every benchmark shape, because a warp task cannot be shared and a warp
+            // is bound to one of the SM's four schedulers, so its balance is no finer than the
+            // static one's while its blocks keep fewer warps busy.
+            const bool queue_ok = want_sched == kSchedWarpQueue && want_s <= 1 &&
+                                  want_combine != XCORR_COMBINE_ATOMIC && want_combine != XCORR_COMBINE_WORKSPACE;
             std::vector<std::pair<int, int>> shapes;
             if (want_wx && want_wy) {
                 shapes.emplace_back(want_wx, want_wy);
@@ -188,97 +206,114 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
                 }
             }
             for (const auto& shape : shapes) {
-                p.WX = shape.first; p.WY = shape.second;
-                const double sm_rate = 128.0 * 1.8e9 * 0.8 * ty_eff[TY];
-                // candidates: S equal slices per task (S = 1: no split), and stream-K
-                std::vector<std::pair<int, bool>> splits;
-                const bool sk_allowed = want_s <= 1 && want_combine != XCORR_COMBINE_STORE &&
-                                        want_combine != XCORR_COMBINE_WORKSPACE;
-                if (want_sk == 2) {
-                    splits.emplace_back(1, true);
-                } else {
+                if (static_ok) {
                     const int s_lo = want_s ? want_s : 1;
                     const int s_hi = want_s ? want_s : std::min(H, 64);
-                    for (int S = s_lo; S <= s_hi; ++S) splits.emplace_back(S, false);
-                    if (want_sk == 0 && want_s == 0 && sk_allowed) splits.emplace_back(1, true);
+                    for (int S = s_lo; S <= s_hi; ++S) cands.push_back({shape.first, shape.second, S, kSchedStatic});
                 }
-                for (const auto& split : splits) {
-                    const int S = split.first;
-                    const bool sk = split.second;
-                    p.S = S;
-                    p.stream_k = sk ? 1 : 0;
-                    finish_plan(p, pm);
-                    if (p.smem_bytes > dev.smem_optin) continue;
-                    if (!sk && want_combine == XCORR_COMBINE_WORKSPACE &&
-                        (double)S * out_bytes > (double)max_workspace_bytes) continue;
-                    const double tasks = (double)pm.n_left * p.RG * p.CX * p.CY;
-                    if (tasks * S > 2147483647.0) continue;
-                    // resident warps per SM (128 registers per thread, 1 KB of shared memory
-                    // reserved per block): below ~12 the FFMA pipe idles on shared-memory latency
-                    const int by_smem = (int)((dev.smem_optin + 1024) / (p.smem_bytes + 1024));
-                    const int regs = (p.threads <= kSmallBlockThreads && TY >= 3) ? 168 : 128;
-                    const int by_regs = 65536 / (regs * p.threads);
-                    const int blocks_sm = std::max(1, std::min(by_smem, by_regs));
-                    const int resident = blocks_sm * (p.threads / 32);
-                    const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident);
-                    // shared-memory wavefronts per 8-step chunk against its FFMA issue slots
-                    const double wavefronts = 2.0 * TY * std::max(1, p.SL / 8) + 6.0 * std::max(1, p.ML / 8);
-                    const double smem_util = 4.0 * wavefronts / (8.0 * TY * kTX);
-                    const double smem_eff = 1.0 / (1.0 + std::max(0.0, smem_util - 0.4));
-                    // measured on B200 over the plan space of the benchmark shapes: large blocks
-                    // (12..16 warps sharing one staging) and many right matrices per warp run
-                    // up to ~15 % faster than small blocks / few matrices per warp
-                    const int warps_blk = p.threads / 32;
-                    const double block_prior = warps_blk >= 12 ? 1.0 : warps_blk >= 8 ? 0.93 : warps_blk >= 4 ? 0.87 : 0.8;
-                    const double lanes_prior = p.ML >= 8 ? 1.0 : p.ML == 4 ? 0.96 : p.ML == 2 ? 0.92 : 0.9;
-                    const double rate = sm_rate * occ_eff * smem_eff * block_prior * lanes_prior;
-                    // filling the staging buffers: bytes over ~64 B/clk from L2 plus a latency
-                    // chain, paid once per block (per segment) and hidden only by other blocks
-                    const double t_stage = ((double)p.smem_bytes / 64.0 + 2000.0) / 1.9e9;
-                    double t;
-                    int comb;
-                    unsigned grid;
-                    if (sk) {
-                        const double units = tasks * H;
-                        double G = (double)dev.sm_count * blocks_sm;
-                        if (G > units) G = units;
-                        grid = (unsigned)G;
-                        const double rows_per_block = units / G;
-                        const double macs_per_row = (double)p.threads * p.Wp * TY * kTX;
-                        // every block: its rows, plus a fixed cost per segment (staging, flush)
-                        const double segments = rows_per_block / H + 1.0;
-                        const double t_rate = std::ceil(G / dev.sm_count) * ((rows_per_block + 0.25 * segments) *
-                                              macs_per_row / rate + segments * t_stage);
-                        const double t_serial = rows_per_block * p.Wp * TY * kTX / 1.8e9;
-                        const double split_share = std::min(1.0, 2.0 * G / tasks);   // outputs added atomically
-                        // more than two parts of a task do not commute: last bits then vary run to run
-                        const double order_penalty = tasks >= G ? 1.0 : 1.03;
-                        t = (std::max(t_rate, t_serial) + 4e-6 + out_bytes / 3e12 + split_share * 2.3 * out_bytes / 0.4e12) *
-                            order_penalty;
-                        comb = kAtomic;
-                    } else {
-                        const double rs = (double)H / S;
-                        const double macs_per_block = (double)p.threads * rs * p.Wp * TY * kTX;
-                        const double busiest = std::ceil(tasks * S / dev.sm_count);
-                        const double t_rate = busiest * (macs_per_block / rate * (rs + 0.25) / rs + t_stage);
-                        // one warp issues at most one FFMA per clock: a lower bound for tiny inputs
-                        const double t_serial = rs * p.Wp * TY * kTX / 1.8e9;
-                        comb = want_combine;
-                        if (comb == XCORR_COMBINE_AUTO) comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
-                        // a memset or a second kernel in front of / behind the main one costs a few us
-                        double t_combine = 0.0;
-                        if (comb == kAtomic) t_combine = 4e-6 + out_bytes / 3e12 + S * out_bytes / 0.4e12;
-                        else if (comb == kWorkspace) t_combine = 4e-6 + (2.0 * S + 1.0) * out_bytes / 3e12;
-                        t = std::max(t_rate, t_serial) + t_combine;
-                        grid = (unsigned)(tasks * S);
-                    }
-                    if (best_time < 0.0 || t < best_time * 0.9999) {
-                        best_time = t;
-                        best = p;
-                        best.combine = comb;
-                        best.grid = grid;
-                        best.tasks = (unsigned)tasks;
-                    }
+                if (streamk_ok) cands.push_back({shape.first, shape.second, 1, kSchedStreamK});
+            }
+            if (queue_ok) {
+                if (want_wx || want_wy) {
+                    const int nw = (want_wx ? want_wx : 1) * (want_wy ? want_wy : 1);
+                    cands.push_back({nw, 1, 1, kSchedWarpQueue});
+                } else {
+                    for (int nw : {8, 12, 16}) cands.push_back({nw, 1, 1, kSchedWarpQueue});
+                }
+            }
+
+            const double sm_rate = 128.0 * 1.8e9 * 0.8 * ty_eff[TY];
+            for (const Cand& c : cands) {
+                p.WX = c.WX; p.WY = c.WY; p.S = c.S; p.schedule = c.sched;
+                finish_plan(p, pm);
+                if (p.smem_bytes > dev.smem_optin) continue;
+                if (c.sched == kSchedStatic && want_combine == XCORR_COMBINE_WORKSPACE &&
+                    (double)c.S * out_bytes > (double)max_workspace_bytes) continue;
+                const double groups = (double)pm.n_left * p.RG;
+                const double tasks = c.sched == kSchedWarpQueue ? groups : groups * p.CX * p.CY;
+                if (tasks * c.S > 2147483647.0 || groups * p.NGY * p.NTX > 4.0e9) continue;
+                // resident warps per SM (1 KB of shared memory reserved per block): below ~12
+                // the FFMA pipe idles on shared-memory latency
+                const int by_smem = (int)((dev.smem_optin + 1024) / (p.smem_bytes + 1024));
+                const int regs = (p.threads <= kSmallBlockThreads && TY >= 3) ? 168 : 128;
+                const int by_regs = 65536 / (regs * p.threads);
+                const int blocks_sm = std::max(1, std::min(by_smem, by_regs));
+                const int resident = blocks_sm * (p.threads / 32);
+                const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident);
+                // shared-memory wavefronts per 8-step chunk against its FFMA issue slots
+                const double wavefronts = 2.0 * TY * std::max(1, p.SL / 8) + 6.0 * std::max(1, p.ML / 8);
+                const double smem_util = 4.0 * wavefronts / (8.0 * TY * kTX);
+                const double smem_eff = 1.0 / (1.0 + std::max(0.0, smem_util - 0.4));
+                // measured on B200 over the plan space of the benchmark shapes: large blocks
+                // (12..16 warps sharing one staging) and many right matrices per warp run
+                // up to ~15 % faster than small blocks / few matrices per warp
+                const int warps_blk = p.threads / 32;
+                const double block_prior = warps_blk >= 12 ? 1.0 : warps_blk >= 8 ? 0.93 : warps_blk >= 4 ? 0.87 : 0.8;
+                const double lanes_prior = p.ML >= 8 ? 1.0 : p.ML == 4 ? 0.96 : p.ML == 2 ? 0.92 : 0.9;
+                const double rate = sm_rate * occ_eff * smem_eff * block_prior * lanes_prior;
+                // filling the staging buffers: bytes over ~64 B/clk from L2 plus a latency
+                // chain, paid once per block (per segment / phase)
+                const double t_stage = ((double)p.smem_bytes / 64.0 + 2000.0) / 1.9e9;
+                double t;
+                int comb;
+                unsigned grid;
+                if (c.sched == kSchedWarpQueue) {
+                    const double per_group = (double)p.NGY * p.NTX;
+                    const double wtasks = groups * per_group;
+                    double G = (double)dev.sm_count * blocks_sm;
+                    if (G > wtasks) G = wtasks;
+                    grid = (unsigned)G;
+                    const double macs_per_wtask = 32.0 * H * p.Wp * TY * kTX;
+                    const double per_block = std::ceil(wtasks / G);
+                    const double phases = wtasks / G / per_group + 1.0;
+                    // a warp is bound to one of the SM's four schedulers and a task cannot be
+                    // shared: the busiest scheduler runs ceil(tasks of the block / 4) tasks
+                    const double t_rate = std::ceil(G / dev.sm_count) *
+                                          (4.0 * std::ceil(per_block / 4.0) * macs_per_wtask / rate + phases * t_stage);
+                    const double t_serial = std::ceil(per_block / warps_blk) * H * p.Wp * TY * kTX / 1.8e9;
+                    t = std::max(t_rate, t_serial);
+                    comb = kStore;
+                } else if (c.sched == kSchedStreamK) {
+                    const double units = tasks * H;
+                    double G = (double)dev.sm_count * blocks_sm;
+                    if (G > units) G = units;
+                    grid = (unsigned)G;
+                    const double rows_per_block = units / G;
+                    const double macs_per_row = (double)p.threads * p.Wp * TY * kTX;
+                    // every block: its rows, plus a fixed cost per segment (staging, flush)
+                    const double segments = rows_per_block / H + 1.0;
+                    const double t_rate = std::ceil(G / dev.sm_count) * ((rows_per_block + 0.25 * segments) *
+                                          macs_per_row / rate + segments * t_stage);
+                    const double t_serial = rows_per_block * p.Wp * TY * kTX / 1.8e9;
+                    const double split_share = std::min(1.0, 2.0 * G / tasks);   // outputs added atomically
+                    // more than two parts of a task do not commute: last bits then vary run to run
+                    const double order_penalty = tasks >= G ? 1.0 : 1.03;
+                    t = (std::max(t_rate, t_serial) + 4e-6 + out_bytes / 3e12 + split_share * 2.3 * out_bytes / 0.4e12) *
+                        order_penalty;
+                    comb = kAtomic;
+                } else {
+                    const int S = c.S;
+                    const double rs = (double)H / S;
+                    const double macs_per_block = (double)p.threads * rs * p.Wp * TY * kTX;
+                    const double busiest = std::ceil(tasks * S / dev.sm_count);
+                    const double t_rate = busiest * (macs_per_block / rate * (rs + 0.25) / rs + t_stage);
+                    // one warp issues at most one FFMA per clock: a lower bound for tiny inputs
+                    const double t_serial = rs * p.Wp * TY * kTX / 1.8e9;
+                    comb = want_combine;
+                    if (comb == XCORR_COMBINE_AUTO) comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
+                    // a memset or a second kernel in front of / behind the main one costs a few us
+                    double t_combine = 0.0;
+                    if (comb == kAtomic) t_combine = 4e-6 + out_bytes / 3e12 + S * out_bytes / 0.4e12;
+                    else if (comb == kWorkspace) t_combine = 4e-6 + (2.0 * S + 1.0) * out_bytes / 3e12;
+                    t = std::max(t_rate, t_serial) + t_combine;
+                    grid = (unsigned)(tasks * S);
+                }
+                if (best_time < 0.0 || t < best_time * 0.9999) {
+                    best_time = t;
+                    best = p;
+                    best.combine = comb;
+                    best.grid = grid;
+                    best.tasks = (unsigned)tasks;
                 }
             }
         }
@@ -312,9 +347,11 @@ std::string describe_plan(const TilePlan& p) {
     char buf[512];
     std::snprintf(buf, sizeof buf,
                   "kernel=tile<TY=%d> grid=(%u,1,1) block=(%d,1,1) smem=%zu plan{H=%d W=%d Hp=%d Wp=%d SL=%d ML=%d "
-                  "WX=%d WY=%d CX=%d CY=%d RG=%d S=%d stream_k=%d tasks=%u nstage=%d combine=%s workspace=%zu}",
+                  "WX=%d WY=%d CX=%d CY=%d RG=%d S=%d schedule=%s tasks=%u nstage=%d combine=%s workspace=%zu}",
                   p.TY, p.grid, p.threads, p.smem_bytes, p.H, p.W, p.Hp, p.Wp, p.SL, p.ML, p.WX, p.WY,
-                  p.CX, p.CY, p.RG, p.S, p.stream_k, p.tasks, p.nstage,
+                  p.CX, p.CY, p.RG, p.S,
+                  p.schedule == kSchedStatic ? "static" : p.schedule == kSchedStreamK ? "stream-k" : "warp-queue",
+                  p.tasks, p.nstage,
                   p.combine == kStore ? "store" : p.combine == kAtomic ? "atomic" : "workspace",
                   p.workspace_bytes);
     return buf;

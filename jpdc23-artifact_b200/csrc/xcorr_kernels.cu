@@ -183,11 +183,12 @@ __device__ __forceinline__ void warp_flush(float* scratch, const float (&vals)[k
 template<int TY>
 __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict__ dst, uint32_t sL_addr,
                                             uint32_t rmat_addr, int r0, int r1, int cy0, int cya, int cx0,
-                                            bool lane_live, int combine, float* flush_scratch, int lane) {
+                                            bool lane_live, int combine, float* flush_scratch, int lane,
+                                            int cls_per_block) {
     const int H = p.H, W = p.W, Hp = p.Hp, Wp = p.Wp;
     const int OW = 2 * W - 1;
     // staged left rows of this segment: circular (all Hp rows) or a window of rows
-    const int nstage = min(r1 - r0 + p.WY * p.SL * TY - 1, Hp);
+    const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);
     const uint32_t stage_bytes = (uint32_t)(nstage * p.LS * 4);
     const int cb = cx0 >> 3;                  // first chunk of the tile's own columns
 
@@ -272,13 +273,21 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     const int H = p.H, W = p.W, Hp = p.Hp, Wp = p.Wp;
     const int tid = threadIdx.x, nthr = blockDim.x;
 
-    // ---- the block's share of the work, in units of (block task, right row).
-    //      Slices: block = (task, slice), one segment.  Stream-K: the units of all tasks are
-    //      cut into gridDim.x equal ranges; a range is one or more segments, each a run of
-    //      rows of one task.
+    // ---- the block's share of the work.
+    //      Static: block = (block task, slice): one segment of right rows.
+    //      Stream-K: the (block task, right row) units of all tasks are cut into gridDim.x
+    //      equal ranges; a range is one or more segments, each a run of rows of one task.
+    //      Warp queue: the warp tasks (one x tile and one y group of one matrix group, all
+    //      rows) are cut into gridDim.x equal ranges; a range is one or more phases, each the
+    //      tasks of one matrix group, which the block's warps take from a shared counter.
     unsigned long long u, uend;
     int slice = 0;
-    if (p.stream_k) {
+    const int tasks_per_group = p.NGY * p.NTX;
+    if (p.schedule == kSchedWarpQueue) {
+        const unsigned long long total = (unsigned long long)p.tasks * tasks_per_group;
+        u = total * blockIdx.x / gridDim.x;
+        uend = total * (blockIdx.x + 1) / gridDim.x;
+    } else if (p.schedule == kSchedStreamK) {
         const unsigned long long total = (unsigned long long)p.tasks * H;
         u = total * blockIdx.x / gridDim.x;
         uend = total * (blockIdx.x + 1) / gridDim.x;
@@ -297,20 +306,35 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     const uint32_t rmat_addr = (uint32_t)__cvta_generic_to_shared(sR + (size_t)m * p.RMS);
     float* flush_scratch = reinterpret_cast<float*>(
         reinterpret_cast<char*>(sR + (size_t)p.ML * p.RMS) + (size_t)warp * kFlushBytesPerWarp);
+    int* queue = reinterpret_cast<int*>(reinterpret_cast<char*>(sR + (size_t)p.ML * p.RMS) +
+                                        (size_t)(nthr >> 5) * kFlushBytesPerWarp);
 
     while (u < uend) {
-        unsigned task = (unsigned)(u / (unsigned)H);
-        const int r0 = (int)(u - (unsigned long long)task * H);
-        const int r1 = (int)min((unsigned long long)H, r0 + (uend - u));
-        u += (unsigned)(r1 - r0);
-        const int bx = task % p.CX; task /= p.CX;
-        const int by = task % p.CY; task /= p.CY;
-        const int rg = task % p.RG;
-        const int l = task / p.RG;
-        // a whole task is written with plain stores, a part of one is added to the zeroed output
-        const int combine = p.stream_k ? ((r0 == 0 && r1 == H) ? (int)kStore : (int)kAtomic) : p.combine;
+        int r0, r1, bx, by, rg, l, combine, q_first = 0, q_count = 0;
+        if (p.schedule == kSchedWarpQueue) {
+            const unsigned group = (unsigned)(u / (unsigned)tasks_per_group);
+            q_first = (int)(u - (unsigned long long)group * tasks_per_group);
+            q_count = (int)min((unsigned long long)(tasks_per_group - q_first), uend - u);
+            u += (unsigned)q_count;
+            r0 = 0; r1 = H; bx = 0; by = 0;
+            rg = group % p.RG;
+            l = group / p.RG;
+            combine = kStore;
+        } else {
+            unsigned task = (unsigned)(u / (unsigned)H);
+            r0 = (int)(u - (unsigned long long)task * H);
+            r1 = (int)min((unsigned long long)H, r0 + (uend - u));
+            u += (unsigned)(r1 - r0);
+            bx = task % p.CX; task /= p.CX;
+            by = task % p.CY; task /= p.CY;
+            rg = task % p.RG;
+            l = task / p.RG;
+            // a whole task is written with plain stores, a part of one is added to the zeroed output
+            combine = p.schedule == kSchedStreamK ? ((r0 == 0 && r1 == H) ? (int)kStore : (int)kAtomic) : p.combine;
+        }
 
-        const int cls_per_block = p.WY * p.SL * TY;
+        // y classes the staged left rows must serve: the block's groups, or all in queue mode
+        const int cls_per_block = p.schedule == kSchedWarpQueue ? Hp : p.WY * p.SL * TY;
         const int cya = by * cls_per_block;          // first y class of the block
         int rowbase = r0 + cya;
         if (rowbase >= Hp) rowbase -= Hp;
@@ -371,12 +395,27 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 *reinterpret_cast<float4*>(sR + (size_t)mm * p.RMS + (size_t)rr * Wp + x) = v;
             }
         }
+        if (p.schedule == kSchedWarpQueue && tid == 0) *queue = 0;
         __syncthreads();
 
-        // ---- this warp's tile
-        const int tile_x = bx * p.WX + wx;
-        const int grp_y = by * p.WY + wy;
-        if (tile_x < p.NTX && grp_y < p.NGY) {
+        // ---- this warp's tile(s): its fixed tile of the block task, or tiles popped from the queue
+        int item = 0;
+        if (p.schedule == kSchedWarpQueue) {
+            if (lane == 0) item = atomicAdd(queue, 1);
+            item = __shfl_sync(0xffffffffu, item, 0);
+        }
+        while (true) {
+            int tile_x, grp_y;
+            if (p.schedule == kSchedWarpQueue) {
+                if (item >= q_count) break;
+                const int t = q_first + item;
+                grp_y = t / p.NTX;
+                tile_x = t - grp_y * p.NTX;
+            } else {
+                tile_x = bx * p.WX + wx;
+                grp_y = by * p.WY + wy;
+                if (item != 0 || tile_x >= p.NTX || grp_y >= p.NGY) break;
+            }
             const unsigned jright = (unsigned)rg * p.ML + m;
             const bool lane_live = jright < a.pm.m;
             const int cx0 = tile_x * kTX;
@@ -385,34 +424,45 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out : a.out)
                          + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
             tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live, combine,
-                            flush_scratch, lane);
+                            flush_scratch, lane, cls_per_block);
+            if (p.schedule == kSchedWarpQueue) {
+                if (lane == 0) item = atomicAdd(queue, 1);
+                item = __shfl_sync(0xffffffffu, item, 0);
+            } else {
+                item = 1;
+            }
         }
         __syncthreads();                          // the next segment reuses the staging buffers
     }
 }
 
-// Sum the per-slice partial images in slice order.  Slice s wrote output row `orow`
-// (shift sy = orow - (H-1)) iff it holds rows before the class's wrap row (sy >= 0) or
-// after it (sy < 0); the other slices' words are unwritten and are skipped.
+// Sum the per-slice partial images in slice order.  One block per output row: slice s wrote
+// output row `orow` (shift sy = orow - (H-1)) iff it holds right rows before the class's wrap
+// row (sy >= 0) or after it (sy < 0); the other slices' words are unwritten and are skipped.
+// The row's contributing slices are a contiguous range, found once per block.
 __global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ ws,
                                                               float* __restrict__ out,
                                                               unsigned long long total_out,
                                                               int H, int W, int Hp, int S) {
-    const unsigned long long OW = 2ull * W - 1, OE = OW * (2ull * H - 1);
-    for (unsigned long long o = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x;
-         o < total_out; o += (unsigned long long)gridDim.x * blockDim.x) {
-        const unsigned long long oi = o % OE;
-        const int orow = (int)(oi / OW);
+    const int OW = 2 * W - 1, OH = 2 * H - 1;
+    const unsigned long long rows_total = total_out / (unsigned long long)OW;   // matrices * OH
+    for (unsigned long long grow = blockIdx.x; grow < rows_total; grow += gridDim.x) {
+        const int orow = (int)(grow % (unsigned long long)OH);
         const int sy = orow - (H - 1);
         const int wrap_row = sy >= 0 ? Hp - sy : -sy;
-        float sum = 0.f;
-        for (int s = 0; s < S; ++s) {
-            const int r0 = (int)(((long long)s * H) / S);
-            const int r1 = (int)(((long long)(s + 1) * H) / S);
-            const bool wrote = sy >= 0 ? r0 < wrap_row : r1 > wrap_row;
-            if (wrote) sum += ws[(unsigned long long)s * total_out + o];
+        // slices with r0 < wrap_row (sy >= 0) or r1 > wrap_row (sy < 0)
+        int s_first = 0, s_last = S;              // [s_first, s_last)
+        if (sy >= 0) {
+            while (s_last > 0 && (int)(((long long)(s_last - 1) * H) / S) >= wrap_row) --s_last;
+        } else {
+            while (s_first < S && (int)(((long long)(s_first + 1) * H) / S) <= wrap_row) ++s_first;
         }
-        out[o] = sum;
+        const unsigned long long base = grow * (unsigned long long)OW;
+        for (int x = threadIdx.x; x < OW; x += blockDim.x) {
+            float sum = 0.f;
+            for (int s = s_first; s < s_last; ++s) sum += ws[(unsigned long long)s * total_out + base + x];
+            out[base + x] = sum;
+        }
     }
 }
 
@@ -527,11 +577,13 @@ cudaError_t launch_tile(const TileArgs& a, cudaStream_t stream) {
 
 cudaError_t launch_reduce_partials(const float* ws, float* out, unsigned long long total_out,
                                    int H, int W, int Hp, int S, int sm_count, cudaStream_t stream) {
-    unsigned long long blocks = (total_out + 255) / 256;
-    unsigned long long cap = (unsigned long long)sm_count * 16;
+    const unsigned long long rows_total = total_out / (2ull * W - 1);
+    unsigned long long blocks = rows_total;
+    const unsigned long long cap = (unsigned long long)sm_count * 32;
     if (blocks > cap) blocks = cap;
     if (blocks == 0) blocks = 1;
-    reduce_partials_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ws, out, total_out, H, W, Hp, S);
+    const int threads = 2 * W - 1 >= 256 ? 256 : 2 * W - 1 >= 128 ? 128 : 64;
+    reduce_partials_kernel<<<(unsigned)blocks, threads, 0, stream>>>(ws, out, total_out, H, W, Hp, S);
     return cudaGetLastError();
 }
 

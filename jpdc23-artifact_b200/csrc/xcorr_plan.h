@@ -26,6 +26,7 @@ constexpr int kSmallBlockThreads = 384;  // blocks up to this size run the 168-r
 constexpr int kSmemLimit = 227 * 1024;
 
 enum Combine : int { kStore = 1, kAtomic = 2, kWorkspace = 3 };
+enum Schedule : int { kSchedStatic = 1, kSchedStreamK = 2, kSchedWarpQueue = 3 };
 
 // How the pairs of a mode are enumerated: left l in [0, n_left) meets rights
 // l*right_stride + j, j in [0, m); the result matrix is l*m + j.
@@ -48,9 +49,9 @@ struct TilePlan {
     int NGY;           // y-class groups = Hp / (SL*TY)
     int WX, WY;        // warps of a block along x tiles / y groups
     int CX, CY;        // blocks needed along x tiles / y groups
-    int S;             // row slices of the right matrices (1 when stream_k)
-    int stream_k;      // 1: the (task, row) units are cut evenly over `grid` blocks
-    unsigned tasks;    // block tasks = n_left * RG * CX * CY
+    int S;             // row slices of the right matrices (1 unless the schedule is static)
+    int schedule;      // Schedule
+    unsigned tasks;    // block tasks = n_left * RG * CX * CY (warp queue: matrix groups = n_left * RG)
     int RSmax;         // rows of the longest slice
     int RG;            // right-matrix groups per left = ceil(m / ML)
     int nstage;        // left rows staged in shared memory (at most; a short segment stages fewer)

@@ -104,10 +104,14 @@ TILE_VARIANTS = [
     dict(overlap_rows=4, class_lanes=32, row_slices=7, combine="workspace", warps_x=2, warps_y=1),
     dict(overlap_rows=1, class_lanes=4, row_slices=1, warps_x=1, warps_y=3),
     dict(overlap_rows=2, class_lanes=8, row_slices=4, combine="workspace", warps_x=3, warps_y=2),
-    dict(stream_k=2),
-    dict(stream_k=2, overlap_rows=2, class_lanes=8, warps_x=1, warps_y=2),
-    dict(stream_k=2, overlap_rows=4, class_lanes=2, warps_x=2, warps_y=1),
-    dict(stream_k=1),
+    dict(schedule=2),
+    dict(schedule=2, overlap_rows=2, class_lanes=8, warps_x=1, warps_y=2),
+    dict(schedule=2, overlap_rows=4, class_lanes=2, warps_x=2, warps_y=1),
+    dict(schedule=1),
+    dict(schedule=3),
+    dict(schedule=3, overlap_rows=2, class_lanes=4, warps_x=3, warps_y=1),
+    dict(schedule=3, overlap_rows=4, class_lanes=16, warps_x=16, warps_y=1),
+    dict(schedule=3, overlap_rows=3, class_lanes=1, warps_x=2, warps_y=4),
 ]
 
 
@@ -163,8 +167,8 @@ def test_invalid_hints_are_rejected(xc):
     left, right = seeded_inputs(8, 8, 1, 1, 1)
     for bad in (dict(overlap_rows=5), dict(class_lanes=3), dict(warps_x=5, warps_y=4), dict(row_slices=9),
                 dict(kernel=9), dict(kernel="overlap_wise", block_threads=100),
-                dict(combine="store", row_slices=2), dict(stream_k=3), dict(stream_k=2, row_slices=2),
-                dict(stream_k=2, combine="workspace")):
+                dict(combine="store", row_slices=2), dict(schedule=4), dict(schedule=2, row_slices=2),
+                dict(schedule=2, combine="workspace")):
         with pytest.raises(xc.XcorrError) as e:
             gpu_run(xc, "one_to_one", left, right, xc.make_hints(**bad))
         assert e.value.status == 3, bad
@@ -236,7 +240,8 @@ def test_modes_are_consistent_with_each_other(xc):
     equals one_to_many of left l with its own rights -- bit for bit under the same forced
     plan (same summation order), within rounding under the automatic per-shape plans."""
     left, right = seeded_inputs(32, 32, 4, 8, 42)
-    forced = xc.make_hints(kernel="tile", overlap_rows=4, class_lanes=16, warps_x=4, warps_y=1, row_slices=1)
+    forced = xc.make_hints(kernel="tile", overlap_rows=4, class_lanes=16, warps_x=4, warps_y=1, row_slices=1,
+                           schedule=1)
     for hints, exact in ((forced, True), (None, False)):
         n2m = gpu_run(xc, "n_to_m", left, right, hints)
         n2mn = gpu_run(xc, "n_to_mn", left, right, hints)   # left l with rights 2l, 2l+1
@@ -267,7 +272,8 @@ def test_sharded_entry_point_equals_single_device(xc, mode, nl, nr):
     ndev = torch.cuda.device_count()
     devices = [i % ndev for i in range(3)]
     left, right = seeded_inputs(16, 24, nl, nr, 9)
-    forced = xc.make_hints(kernel="tile", overlap_rows=2, class_lanes=8, warps_x=2, warps_y=1, row_slices=1)
+    forced = xc.make_hints(kernel="tile", overlap_rows=2, class_lanes=8, warps_x=2, warps_y=1, row_slices=1,
+                           schedule=1)
     one = xc.run_host(mode, left, right, forced)
     many = xc.run_host(mode, left, right, forced, devices=devices)
     assert np.array_equal(one, many)
