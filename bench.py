@@ -465,10 +465,13 @@ def main():
                                    "shifts_per_s": shifts_of(k) / ts if ts > 0 else None}
             per_config[k] = entry
         dom = max(CONFIGS, key=lambda k: per_ms_max[k])
-        traffic = None
-        tp = os.path.join(ROOT, "profiles", "dram_traffic.json")
+        traffic = None     # DRAM bytes per launch of the dominant kernel, from the committed ncu summary
+        tp = os.path.join(ROOT, "profiles", "dram_traffic.txt")
         if os.path.exists(tp):
-            traffic = json.load(open(tp)).get(dom)
+            for tl in open(tp):
+                parts = tl.split()
+                if len(parts) == 2 and parts[0] == dom:
+                    traffic = int(parts[1])
         achieved = flop_of(dom) / (per_ms_max[dom] * 1e-3) / 1e12
         roofline = {
             "bound": "fp32_ffma", "kernel": plans[dom].split(" ")[0].replace("kernel=", "") + f" ({dom})",

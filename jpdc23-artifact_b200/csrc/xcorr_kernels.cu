@@ -105,8 +105,10 @@ template<int TY>
 __device__ __forceinline__ void tile_row(float (&acc)[TY][kTX], const uint32_t (&lp)[TY], uint32_t rrow,
                                          int pass, int cb, int c_begin, int c_end, uint32_t roff_bytes,
                                          int Wp) {
-    // chunks taken in full: the same code for both passes
-#pragma unroll 1
+    // chunks taken in full: the same code for both passes.  Unrolled by two so that the loads
+    // of the next chunk are issued under the FFMAs of the current one (+5..10 % measured on
+    // B200); unrolling further overflows the instruction cache for TY >= 3.
+#pragma unroll 2
     for (int c = c_begin; c < c_end; ++c) {
         float w[24];
         window_load<0, 6>(w, rrow + roff_bytes + (uint32_t)c * 32);
