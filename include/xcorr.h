@@ -112,7 +112,11 @@ typedef struct xcorr_hints {
                                     matrix group, all rows) are cut evenly over one resident wave of
                                     blocks whose warps take them from a shared counter: plain stores,
                                     bit-reproducible, balanced to one warp task per SM */
-    int32_t reserved[7];
+    int32_t host_chunks;       /* host-buffer entry points only: number of pieces the independent result
+                                  matrices are cut into so that the input copy, the kernel and the result
+                                  copy of successive pieces overlap.  0 auto (by result size, 1..8);
+                                  1 one piece (copy in, run, copy out) */
+    int32_t reserved[6];
 } xcorr_hints;
 
 /* ---- device-pointer entry points ------------------------------------------------------
@@ -210,7 +214,13 @@ XCORR_API int32_t xcorr_validate_input_size(int32_t mode, uint32_t rows, uint32_
  * transfer (H2D), run, finalize (D2H), free -- main.cpp:123-174, one_to_one.hpp:112-135 and
  * the other modes' naive_gpu_* classes.  Host pointers in, host result out; synchronous.
  * Device buffers are cached per device and reused across calls.  n_to_mn takes and
- * returns GROUPED order like the device entry point. */
+ * returns GROUPED order like the device entry point.
+ * Results of more than a few MB are produced in pieces (blocks of right matrices for
+ * one_to_many, of left matrices for n_to_m / n_to_mn; hints->host_chunks) on three streams,
+ * so that the result copy of one piece runs under the kernel of the next and the input copy
+ * of the one after; this needs page-locked host buffers to take effect (pageable ones work,
+ * without overlap).  The reference copies, runs and copies back in sequence
+ * (cross_corr.hpp:32-72 "Compute" steps). */
 XCORR_API xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, const float* h_right, float* h_out,
                                           uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                                           const xcorr_hints* hints, int32_t device);

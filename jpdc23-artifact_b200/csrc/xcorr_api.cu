@@ -131,9 +131,9 @@ void finish_plan(TilePlan& p, const PairMap& pm) {
     p.LS = p.Wp + 4;
     p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
     p.threads = 32 * p.WX * p.WY;
-    // staged left rows, staged right rows, per-warp flush staging (16 x 17 floats + 16 addresses)
+    // staged left rows, staged right rows, per-warp flush staging
     p.smem_bytes = ((size_t)p.nstage * p.LS + (size_t)p.ML * p.RMS) * sizeof(float) +
-                   (size_t)(p.threads / 32) * (16 * (kTX + 1) * 4 + 16 * 8) + 16;   // + the warp queue's counter
+                   (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;   // + the warp queue's counter
 }
 
 // Per-shape plan of the tile kernel: micro-tile height, lane split, block shape and how the
@@ -142,8 +142,8 @@ void finish_plan(TilePlan& p, const PairMap& pm) {
 // units of all tasks cut evenly over as many blocks as fit on the GPU; a block's share is a
 // run of whole tasks plus at most two partial ones, partial ones added atomically).
 // Every candidate gets an estimated time; the smallest wins.
-xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, const DeviceInfo& dev,
-                       TilePlan* out, size_t max_workspace_bytes = SIZE_MAX) {
+xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints* h, const DeviceInfo& dev,
+                              TilePlan* out, size_t max_workspace_bytes) {
     TilePlan best{};
     double best_time = -1.0;
     const int want_ty = h ? h->overlap_rows : 0;
@@ -328,6 +328,52 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
     return XCORR_OK;
 }
 
+// The search above looks at a few thousand candidates (~0.1 ms of host time), which is as
+// long as the kernel of a small input: plans are remembered per (shape, counts, hints, device).
+struct PlanKey {
+    uint32_t n_left, m, right_stride;
+    int H, W;
+    int hint[7];
+    int sm_count;
+    size_t smem_optin, max_ws;
+    bool operator==(const PlanKey& o) const {
+        return n_left == o.n_left && m == o.m && right_stride == o.right_stride && H == o.H && W == o.W &&
+               std::memcmp(hint, o.hint, sizeof hint) == 0 && sm_count == o.sm_count &&
+               smem_optin == o.smem_optin && max_ws == o.max_ws;
+    }
+};
+constexpr int kPlanCacheSize = 64;
+struct PlanCache {
+    std::mutex mutex;
+    PlanKey key[kPlanCacheSize];
+    TilePlan plan[kPlanCacheSize];
+    int used = 0, next = 0;
+};
+PlanCache g_plan_cache;
+
+xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, const DeviceInfo& dev,
+                       TilePlan* out, size_t max_workspace_bytes = SIZE_MAX) {
+    PlanKey k{};
+    k.n_left = pm.n_left; k.m = pm.m; k.right_stride = pm.right_stride; k.H = H; k.W = W;
+    if (h) {
+        k.hint[0] = h->overlap_rows; k.hint[1] = h->class_lanes; k.hint[2] = h->warps_x; k.hint[3] = h->warps_y;
+        k.hint[4] = h->row_slices;   k.hint[5] = h->combine;     k.hint[6] = h->schedule;
+    }
+    k.sm_count = dev.sm_count; k.smem_optin = dev.smem_optin; k.max_ws = max_workspace_bytes;
+    {
+        std::lock_guard<std::mutex> lock(g_plan_cache.mutex);
+        for (int i = 0; i < g_plan_cache.used; ++i)
+            if (g_plan_cache.key[i] == k) { *out = g_plan_cache.plan[i]; return XCORR_OK; }
+    }
+    const xcorr_status st = plan_tile_search(pm, H, W, h, dev, out, max_workspace_bytes);
+    if (st != XCORR_OK) return st;
+    std::lock_guard<std::mutex> lock(g_plan_cache.mutex);
+    const int slot = g_plan_cache.used < kPlanCacheSize ? g_plan_cache.used++ : (g_plan_cache.next++ % kPlanCacheSize);
+    g_plan_cache.key[slot] = k;
+    g_plan_cache.plan[slot] = *out;
+    return XCORR_OK;
+}
+
 int pick_kernel(const xcorr_hints* h) {
     const int k = h ? h->kernel : XCORR_KERNEL_AUTO;
     return k == XCORR_KERNEL_AUTO ? XCORR_KERNEL_TILE : k;
@@ -472,13 +518,24 @@ xcorr_status run_one_to_one_noalloc(const float* d_left, const float* d_right, f
 }
 
 // ---- host-buffer front end -------------------------------------------------------------
+// Copy in, run, copy out -- in pieces: the independent result matrices are cut into up to
+// kMaxHostChunks blocks; the input copy of a block, its kernel and its result copy run on
+// three streams chained by events, so that the result copy (the longest of the three for
+// this path: the result is 2-4 times the size of the input) hides the other two.
+constexpr int kMaxHostChunks = 8;
+
 struct HostCache {
     std::mutex mutex;
     float* d_left = nullptr;  size_t left_bytes = 0;
     float* d_right = nullptr; size_t right_bytes = 0;
     float* d_out = nullptr;   size_t out_bytes = 0;
     void* d_ws = nullptr;     size_t ws_bytes = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;       // kernels
+    cudaStream_t copy_in = nullptr;      // host -> device
+    cudaStream_t copy_out = nullptr;     // device -> host
+    cudaEvent_t in_done[kMaxHostChunks] = {};
+    cudaEvent_t run_done[kMaxHostChunks] = {};
+    bool events = false;
 };
 HostCache g_host_cache[kMaxDevices];
 
@@ -492,10 +549,29 @@ xcorr_status grow(T** ptr, size_t* have, size_t need) {
     return XCORR_OK;
 }
 
+// Number of pieces for a host-buffer call: one for one pair; otherwise one per 10 MiB of
+// result, each piece keeping at least 128 pairs so that its kernel still fills the GPU
+// (measured on B200 with the benchmark shapes: 3 pieces for 33 MB of result, 7-8 for 74 MB).
+int host_chunk_count(int32_t mode, const PairMap& pm, uint32_t units, size_t obytes, const xcorr_hints* hints) {
+    if (mode == XCORR_ONE_TO_ONE || units <= 1) return 1;
+    long long k;
+    if (hints && hints->host_chunks > 0) {
+        k = hints->host_chunks;
+    } else {
+        const unsigned long long pairs = (unsigned long long)pm.n_left * pm.m;
+        k = (long long)(obytes / (10ull << 20));
+        k = std::min<long long>(k, (long long)(pairs / 128));
+    }
+    k = std::min<long long>(k, kMaxHostChunks);
+    k = std::min<long long>(k, units);
+    return (int)std::max<long long>(k, 1);
+}
+
 xcorr_status run_host(int32_t mode, const float* h_left, const float* h_right, float* h_out,
                       uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                       const xcorr_hints* hints, int32_t device) {
     if (!h_left || !h_right || !h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+    if (hints && hints->host_chunks < 0) return fail(XCORR_ERR_INVALID_HINT, "host_chunks must be 0 (auto) or positive");
     PairMap pm{};
     xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
     if (st != XCORR_OK) return st;
@@ -506,6 +582,15 @@ xcorr_status run_host(int32_t mode, const float* h_left, const float* h_right, f
     HostCache& c = g_host_cache[device];
     std::lock_guard<std::mutex> lock(c.mutex);
     if (!c.stream) XC_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    if (!c.copy_in) XC_CUDA(cudaStreamCreateWithFlags(&c.copy_in, cudaStreamNonBlocking));
+    if (!c.copy_out) XC_CUDA(cudaStreamCreateWithFlags(&c.copy_out, cudaStreamNonBlocking));
+    if (!c.events) {
+        for (int i = 0; i < kMaxHostChunks; ++i) {
+            XC_CUDA(cudaEventCreateWithFlags(&c.in_done[i], cudaEventDisableTiming));
+            XC_CUDA(cudaEventCreateWithFlags(&c.run_done[i], cudaEventDisableTiming));
+        }
+        c.events = true;
+    }
     const size_t in_elems = (size_t)rows * cols;
     const size_t out_elems = (size_t)(2 * rows - 1) * (2 * cols - 1);
     const size_t lbytes = in_elems * n_left * sizeof(float);
@@ -514,15 +599,80 @@ xcorr_status run_host(int32_t mode, const float* h_left, const float* h_right, f
     if ((st = grow(&c.d_left, &c.left_bytes, lbytes)) != XCORR_OK) return st;
     if ((st = grow(&c.d_right, &c.right_bytes, rbytes)) != XCORR_OK) return st;
     if ((st = grow(&c.d_out, &c.out_bytes, obytes)) != XCORR_OK) return st;
-    const size_t wsb = xcorr_workspace_bytes(mode, rows, cols, n_left, n_right, hints);
+
+    // the units a piece is made of: right matrices (one_to_many) or left matrices with all
+    // (n_to_m) / their own (n_to_mn) right matrices
+    const uint32_t units = mode == XCORR_ONE_TO_MANY ? n_right : mode == XCORR_ONE_TO_ONE ? 1u : n_left;
+    const int chunks = host_chunk_count(mode, pm, units, obytes, hints);
+
+    // workspace: the largest need among the pieces (they run one after the other)
+    size_t wsb = 0;
+    for (int i = 0; i < chunks; ++i) {
+        uint32_t first = 0, count = 0;
+        xcorr_shard_range(units, chunks, i, &first, &count);
+        if (count == 0) continue;
+        const uint32_t nl = mode == XCORR_ONE_TO_MANY || mode == XCORR_ONE_TO_ONE ? n_left : count;
+        const uint32_t nr = mode == XCORR_ONE_TO_MANY ? count : mode == XCORR_N_TO_MN ? count * pm.m : n_right;
+        wsb = std::max(wsb, xcorr_workspace_bytes(mode, rows, cols, nl, nr, hints));
+    }
     if ((st = grow(&c.d_ws, &c.ws_bytes, wsb)) != XCORR_OK) return st;
-    XC_CUDA(cudaMemcpyAsync(c.d_left, h_left, lbytes, cudaMemcpyHostToDevice, c.stream));
-    XC_CUDA(cudaMemcpyAsync(c.d_right, h_right, rbytes, cudaMemcpyHostToDevice, c.stream));
-    st = run_device(mode, c.d_left, c.d_right, c.d_out, rows, cols, n_left, n_right, hints,
-                    c.d_ws, c.ws_bytes, c.stream);
-    if (st != XCORR_OK) return st;
-    XC_CUDA(cudaMemcpyAsync(h_out, c.d_out, obytes, cudaMemcpyDeviceToHost, c.stream));
-    XC_CUDA(cudaStreamSynchronize(c.stream));
+
+    // the operand every piece needs goes first
+    if (mode == XCORR_ONE_TO_MANY || mode == XCORR_ONE_TO_ONE)
+        XC_CUDA(cudaMemcpyAsync(c.d_left, h_left, lbytes, cudaMemcpyHostToDevice, c.copy_in));
+    else if (mode == XCORR_N_TO_M)
+        XC_CUDA(cudaMemcpyAsync(c.d_right, h_right, rbytes, cudaMemcpyHostToDevice, c.copy_in));
+
+    std::string plans;
+    for (int i = 0; i < chunks; ++i) {
+        uint32_t first = 0, count = 0;
+        xcorr_shard_range(units, chunks, i, &first, &count);
+        if (count == 0) continue;
+        const float* dl = c.d_left;
+        const float* dr = c.d_right;
+        float* dout = c.d_out;
+        float* hout = h_out;
+        uint32_t nl = n_left, nr = n_right;
+        size_t piece_out = obytes;
+        if (mode == XCORR_ONE_TO_ONE) {
+            XC_CUDA(cudaMemcpyAsync(c.d_right, h_right, rbytes, cudaMemcpyHostToDevice, c.copy_in));
+        } else if (mode == XCORR_ONE_TO_MANY) {
+            const size_t off = (size_t)first * in_elems;
+            XC_CUDA(cudaMemcpyAsync(c.d_right + off, h_right + off, (size_t)count * in_elems * sizeof(float),
+                                    cudaMemcpyHostToDevice, c.copy_in));
+            dr += off; nr = count;
+            dout += (size_t)first * out_elems; hout += (size_t)first * out_elems;
+            piece_out = (size_t)count * out_elems * sizeof(float);
+        } else {
+            const size_t loff = (size_t)first * in_elems;
+            XC_CUDA(cudaMemcpyAsync(c.d_left + loff, h_left + loff, (size_t)count * in_elems * sizeof(float),
+                                    cudaMemcpyHostToDevice, c.copy_in));
+            dl += loff; nl = count;
+            if (mode == XCORR_N_TO_MN) {
+                const size_t roff = (size_t)first * pm.m * in_elems;
+                XC_CUDA(cudaMemcpyAsync(c.d_right + roff, h_right + roff,
+                                        (size_t)count * pm.m * in_elems * sizeof(float),
+                                        cudaMemcpyHostToDevice, c.copy_in));
+                dr += roff; nr = count * pm.m;
+            }
+            dout += (size_t)first * pm.m * out_elems; hout += (size_t)first * pm.m * out_elems;
+            piece_out = (size_t)count * pm.m * out_elems * sizeof(float);
+        }
+        XC_CUDA(cudaEventRecord(c.in_done[i], c.copy_in));
+        XC_CUDA(cudaStreamWaitEvent(c.stream, c.in_done[i], 0));
+        st = run_device(mode, dl, dr, dout, rows, cols, nl, nr, hints, c.d_ws, c.ws_bytes, c.stream);
+        if (st != XCORR_OK) {
+            // let what was queued finish before the buffers can be reused
+            cudaStreamSynchronize(c.copy_in); cudaStreamSynchronize(c.stream); cudaStreamSynchronize(c.copy_out);
+            return st;
+        }
+        if (chunks > 1 && i == 0) plans = t_last_launch;
+        XC_CUDA(cudaEventRecord(c.run_done[i], c.stream));
+        XC_CUDA(cudaStreamWaitEvent(c.copy_out, c.run_done[i], 0));
+        XC_CUDA(cudaMemcpyAsync(hout, dout, piece_out, cudaMemcpyDeviceToHost, c.copy_out));
+    }
+    XC_CUDA(cudaStreamSynchronize(c.copy_out));
+    if (chunks > 1) t_last_launch = "host_chunks=" + std::to_string(chunks) + " first{" + plans + "}";
     return XCORR_OK;
 }
 
@@ -712,6 +862,13 @@ void xcorr_release_host_cache(void) {
         if (c.d_out) cudaFree(c.d_out);
         if (c.d_ws) cudaFree(c.d_ws);
         if (c.stream) cudaStreamDestroy(c.stream);
+        if (c.copy_in) cudaStreamDestroy(c.copy_in);
+        if (c.copy_out) cudaStreamDestroy(c.copy_out);
+        if (c.events) {
+            for (int i = 0; i < kMaxHostChunks; ++i) { cudaEventDestroy(c.in_done[i]); cudaEventDestroy(c.run_done[i]); }
+            c.events = false;
+        }
+        c.copy_in = c.copy_out = nullptr;
         c.d_left = c.d_right = c.d_out = nullptr;
         c.d_ws = nullptr;
         c.left_bytes = c.right_bytes = c.out_bytes = c.ws_bytes = 0;

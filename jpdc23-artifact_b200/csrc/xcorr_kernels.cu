@@ -105,14 +105,19 @@ template<int TY>
 __device__ __forceinline__ void tile_row(float (&acc)[TY][kTX], const uint32_t (&lp)[TY], uint32_t rrow,
                                          int pass, int cb, int c_begin, int c_end, uint32_t roff_bytes,
                                          int Wp) {
-    // chunks taken in full: the same code for both passes.  Unrolled by two so that the loads
-    // of the next chunk are issued under the FFMAs of the current one (+5..10 % measured on
-    // B200); unrolling further overflows the instruction cache for TY >= 3.
-#pragma unroll 2
-    for (int c = c_begin; c < c_end; ++c) {
+    // chunks taken in full: the same code for both passes.  A tile is two chunks wide and the
+    // padded row a whole number of tiles, so both passes take an even number of full chunks:
+    // two per trip, no remainder.  Two chunks in flight let the loads of the second run under
+    // the FFMAs of the first (+5..10 % measured on B200 against one per trip); four per trip
+    // overflow the instruction cache for TY >= 3.
+#pragma unroll 1
+    for (int c = c_begin; c < c_end; c += 2) {
         float w[24];
         window_load<0, 6>(w, rrow + roff_bytes + (uint32_t)c * 32);
+        float v[24];
+        window_load<0, 6>(v, rrow + roff_bytes + (uint32_t)c * 32 + 32);
         tile_chunk<TY, -1, 0>(acc, w, lp, (uint32_t)c * 32);
+        tile_chunk<TY, -1, 0>(acc, v, lp, (uint32_t)c * 32 + 32);
     }
     // the two chunks of the tile's own columns: one triangle per pass
     float w[24];
@@ -136,49 +141,53 @@ __device__ __forceinline__ void tile_row(float (&acc)[TY][kTX], const uint32_t (
     }
 }
 
-// Per-warp staging area of the output flush: 16 rows of 16 sums (+1 padding word per row)
-// and the 16 rows' destination addresses.
+// Per-warp staging area of the output flush: 32 rows of 16 sums (+1 padding word per row)
+// and the 32 rows' destination addresses (xcorr_plan.h: kFlushBytesPerWarp).
 constexpr int kFlushRowWords = kTX + 1;
-constexpr int kFlushBytesPerWarp = 16 * kFlushRowWords * 4 + 16 * 8;
+static_assert(kFlushBytesPerWarp == 32 * kFlushRowWords * 4 + 32 * 8, "flush staging size");
 
 // Write 16 sums per lane to the lanes' own output rows (lane -> one y class of one right
 // matrix; `rowptr` = start of that output row, `has` = the lane has a row to write).  Done by
 // the whole warp through a shared-memory transpose, 16 lanes per output row, so that a store
-// instruction covers two rows of 16 consecutive floats instead of 32 scattered words: the
-// result arrays are as large as the whole working set, and one-word-per-sector stores (or
-// atomics) made the flush a fifth of the run time.  Must be called by all 32 lanes.
+// instruction covers two rows of 16 consecutive floats instead of 32 scattered words.
+// The code is one straight run -- 17 stores to shared memory, one warp barrier, 32 loads, 16
+// global stores -- because what a flush costs is not its instructions but its dependent
+// stalls: the other warps of the scheduler are in the FFMA loop and always ready, so every
+// time this warp waits for a result it gets its next issue slot only some hundred cycles
+// later (measured on B200: a flush written as a loop of dependent load -> store steps took
+// ~10,000 cycles and warps spent 30-50 % of their life in it).  Must be called by all 32 lanes.
 __device__ __forceinline__ void warp_flush(float* scratch, const float (&vals)[kTX], bool has, float* rowptr,
                                            int cx0, int W, int Wp, int pass, int combine, int lane) {
-    unsigned long long* sbase = reinterpret_cast<unsigned long long*>(scratch + 16 * kFlushRowWords);
-    const unsigned have = __ballot_sync(0xffffffffu, has);
+    unsigned long long* sbase = reinterpret_cast<unsigned long long*>(scratch + 32 * kFlushRowWords);
+    float* row = scratch + lane * kFlushRowWords;
+#pragma unroll
+    for (int j = 0; j < kTX; ++j) row[j] = vals[j];
+    sbase[lane] = has ? reinterpret_cast<unsigned long long>(rowptr) : 0ull;
+    __syncwarp();
     const int c = lane & 15;
     const int cx = cx0 + c;
     // unwrapped pass: shift sx = cx; wrapped pass: shift sx = cx - Wp
     const int col = pass == kPassUnwrapped ? cx + W - 1 : cx - Wp + W - 1;
     const bool ok = pass == kPassUnwrapped ? cx < W : col >= 0;
-#pragma unroll 1
-    for (int hw = 0; hw < 2; ++hw) {
-        const unsigned m16 = (have >> (16 * hw)) & 0xffffu;
-        if (m16 == 0) continue;                       // warp-uniform
-        if ((lane >> 4) == hw) {
-            float* row = scratch + (lane & 15) * kFlushRowWords;
+    const int half = lane >> 4;
+    float v[16];
+    float* base[16];
 #pragma unroll
-            for (int j = 0; j < kTX; ++j) row[j] = vals[j];
-            sbase[lane & 15] = has ? reinterpret_cast<unsigned long long>(rowptr) : 0ull;
-        }
-        __syncwarp();
-#pragma unroll 1
-        for (int i = 0; i < 8; ++i) {
-            if (((m16 >> (2 * i)) & 3u) == 0) continue;   // warp-uniform
-            const int r = 2 * i + (lane >> 4);
-            float* base = reinterpret_cast<float*>(sbase[r]);
-            if (base != nullptr && ok) {
-                const float v = scratch[r * kFlushRowWords + c];
-                if (combine == kAtomic) atomicAdd(base + col, v); else base[col] = v;
-            }
-        }
-        __syncwarp();
+    for (int i = 0; i < 16; ++i) {
+        const int r = 2 * i + half;
+        base[i] = reinterpret_cast<float*>(sbase[r]);
+        v[i] = scratch[r * kFlushRowWords + c];
     }
+    if (combine == kAtomic) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (base[i] != nullptr && ok) atomicAdd(base[i] + col, v[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (base[i] != nullptr && ok) base[i][col] = v[i];
+    }
+    __syncwarp();
 }
 
 // Both passes over the slice's rows for one thread.
@@ -193,6 +202,8 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
     const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);
     const uint32_t stage_bytes = (uint32_t)(nstage * p.LS * 4);
     const int cb = cx0 >> 3;                  // first chunk of the tile's own columns
+    // first right row at which one of the warp's classes wraps in y (classes cyw .. cyw + SL*TY - 1)
+    const int wrap_lo = Hp - ((cy0 & ~(p.SL - 1)) + p.SL * TY - 1);
 
 #pragma unroll 1
     for (int pass = 0; pass < 2; ++pass) {
@@ -215,16 +226,25 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
 #pragma unroll
             for (int j = 0; j < kTX; ++j) acc[t][j] = 0.f;
 
+        // Rows r0 .. r1-1, then TY more trips that only write: trip r1 + t writes class t's
+        // final sums.  Keeping the end-of-slice writes in the row loop leaves one copy of the
+        // flush code in the kernel (instruction-cache footprint).
         uint32_t rrow = rmat_addr;
 #pragma unroll 1
-        for (int ry = r0; ry < r1; ++ry, rrow += (uint32_t)Wp * 4) {
-            // a class that starts wrapping at this row: its unwrapped-in-y part is complete
-            // (the wrap rows of a lane's classes differ, so at most one matches)
-            int tsel = -1;
+        for (int ry = r0; ry < r1 + TY; ++ry, rrow += (uint32_t)Wp * 4) {
+            const bool at_end = ry >= r1;
+            // A class that starts wrapping at this row: its unwrapped-in-y part is complete.
+            // The wrap rows of the warp's SL * TY classes are consecutive (one range check for
+            // the warp); those of a lane's classes differ, so at most one of them matches.
+            if (at_end || ((unsigned)(ry - wrap_lo) < (unsigned)(p.SL * TY) && ry > r0)) {
+                int tsel = -1;
+                if (at_end) {
+                    tsel = ry - r1;
+                } else {
 #pragma unroll
-            for (int t = 0; t < TY; ++t)
-                if (ry == Hp - (cy0 + p.SL * t) && ry > r0) tsel = t;
-            if (__any_sync(0xffffffffu, tsel >= 0)) {
+                    for (int t = 0; t < TY; ++t)
+                        if (ry == Hp - (cy0 + p.SL * t)) tsel = t;
+                }
                 float vals[kTX];
 #pragma unroll
                 for (int j = 0; j < kTX; ++j) vals[j] = 0.f;
@@ -236,8 +256,12 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
                     }
                 }
                 const int cyt = cy0 + p.SL * (tsel < 0 ? 0 : tsel);
-                const bool has = tsel >= 0 && lane_live && cyt < H;
-                warp_flush(flush_scratch, vals, has, dst + (size_t)(cyt + H - 1) * OW, cx0, W, Wp, pass, combine, lane);
+                // at the end of the slice the sums belong to the wrapped output row if the class
+                // wrapped inside (or before) the slice, else to the unwrapped one
+                const int sy = (at_end && r1 > Hp - cyt) ? cyt - Hp : cyt;
+                const bool has = tsel >= 0 && lane_live && sy > -H && sy < H;
+                warp_flush(flush_scratch, vals, has, dst + (size_t)(sy + H - 1) * OW, cx0, W, Wp, pass, combine, lane);
+                if (at_end) continue;
             }
 
             uint32_t lp[TY];
@@ -249,17 +273,6 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
                 lofs[t] += (uint32_t)p.LS * 4;
                 if (lofs[t] == stage_bytes) lofs[t] = 0;
             }
-        }
-
-        // end of the slice: the sums belong to the wrapped output row if the class wrapped
-        // inside (or before) the slice, else to the unwrapped one
-#pragma unroll
-        for (int t = 0; t < TY; ++t) {
-            const int cyt = cy0 + p.SL * t;
-            const bool wrapped = r1 > Hp - cyt;
-            const int sy = wrapped ? cyt - Hp : cyt;
-            const bool has = lane_live && sy > -H && sy < H;
-            warp_flush(flush_scratch, acc[t], has, dst + (size_t)(sy + H - 1) * OW, cx0, W, Wp, pass, combine, lane);
         }
     }
 }

@@ -24,6 +24,8 @@ constexpr int kMaxTY = 4;         // y classes per thread
 constexpr int kMaxWarps = 16;     // warps per block
 constexpr int kSmallBlockThreads = 384;  // blocks up to this size run the 168-register build of the kernel
 constexpr int kSmemLimit = 227 * 1024;
+// per-warp staging area of the output flush: 32 rows of kTX + 1 floats and 32 row addresses
+constexpr int kFlushBytesPerWarp = 32 * (kTX + 1) * 4 + 32 * 8;
 
 enum Combine : int { kStore = 1, kAtomic = 2, kWorkspace = 3 };
 enum Schedule : int { kSchedStatic = 1, kSchedStreamK = 2, kSchedWarpQueue = 3 };

@@ -284,6 +284,28 @@ def test_sharded_entry_point_equals_single_device(xc, mode, nl, nr):
     assert e.value.status == 7
 
 
+@pytest.mark.parametrize("mode,nl,nr", [("one_to_many", 1, 37), ("n_to_m", 7, 5), ("n_to_mn", 6, 18),
+                                        ("one_to_one", 1, 1)])
+@pytest.mark.parametrize("chunks", [1, 2, 3, 8])
+def test_host_entry_point_in_pieces(xc, oracle, mode, nl, nr, chunks):
+    """The host-buffer call cut into `chunks` pieces (copy in / kernel / copy out overlapped on
+    three streams) against the oracle, and bit-identical to the one-piece call under one forced
+    plan.  More pieces than units, and one pair, fall back to fewer pieces."""
+    left, right = seeded_inputs(20, 28, nl, nr, 13)
+    want = oracle_grouped(oracle, mode, left, right)
+    got = xc.run_host(mode, left, right, xc.make_hints(host_chunks=chunks))
+    assert rel_err(got, want) <= REL_TOL
+    forced = dict(kernel="tile", overlap_rows=2, class_lanes=8, warps_x=2, warps_y=1, row_slices=1, schedule=1)
+    one = xc.run_host(mode, left, right, xc.make_hints(host_chunks=1, **forced))
+    cut = xc.run_host(mode, left, right, xc.make_hints(host_chunks=chunks, **forced))
+    assert np.array_equal(one, cut)
+    if chunks > 1 and mode != "one_to_one":
+        assert xc.last_launch().startswith("host_chunks=")
+    with pytest.raises(xc.XcorrError) as e:
+        xc.run_host(mode, left, right, xc.make_hints(host_chunks=-1))
+    assert e.value.status == 3
+
+
 def test_launch_bookkeeping(xc):
     left, right = seeded_inputs(16, 16, 1, 1, 2)
     xc.reset_launch_count()
