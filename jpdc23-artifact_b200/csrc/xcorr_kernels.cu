@@ -55,6 +55,15 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
     return v;
 }
 
+// Asynchronous 16-byte copy global -> shared (no register round trip, so a thread can have all
+// the copies of a staging loop in flight at once); completed by stage_wait().
+__device__ __forceinline__ void stage_copy16(uint32_t dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void stage_wait() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
 // Load the N4*4 floats at `addr` into w[FIRST ...].
 template<int FIRST, int N4, int LEN>
 __device__ __forceinline__ void window_load(float (&w)[LEN], uint32_t addr) {
@@ -112,12 +121,16 @@ __device__ __forceinline__ void tile_row(float (&acc)[TY][kTX], const uint32_t (
     // overflow the instruction cache for TY >= 3.
 #pragma unroll 1
     for (int c = c_begin; c < c_end; c += 2) {
-        float w[24];
-        window_load<0, 6>(w, rrow + roff_bytes + (uint32_t)c * 32);
-        float v[24];
-        window_load<0, 6>(v, rrow + roff_bytes + (uint32_t)c * 32 + 32);
-        tile_chunk<TY, -1, 0>(acc, w, lp, (uint32_t)c * 32);
-        tile_chunk<TY, -1, 0>(acc, v, lp, (uint32_t)c * 32 + 32);
+        {
+            float w[24];
+            window_load<0, 6>(w, rrow + roff_bytes + (uint32_t)c * 32);
+            tile_chunk<TY, -1, 0>(acc, w, lp, (uint32_t)c * 32);
+        }
+        {
+            float w[24];
+            window_load<0, 6>(w, rrow + roff_bytes + (uint32_t)c * 32 + 32);
+            tile_chunk<TY, -1, 0>(acc, w, lp, (uint32_t)c * 32 + 32);
+        }
     }
     // the two chunks of the tile's own columns: one triangle per pass
     float w[24];
@@ -318,6 +331,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     const int q = lane & (p.SL - 1);
     const int m = lane >> p.logSL;
     const uint32_t sL_addr = (uint32_t)__cvta_generic_to_shared(sL);
+    const uint32_t sR_addr = (uint32_t)__cvta_generic_to_shared(sR);
     const uint32_t rmat_addr = (uint32_t)__cvta_generic_to_shared(sR + (size_t)m * p.RMS);
     float* flush_scratch = reinterpret_cast<float*>(
         reinterpret_cast<char*>(sR + (size_t)p.ML * p.RMS) + (size_t)warp * kFlushBytesPerWarp);
@@ -370,13 +384,13 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 if (row < H && x < W) {
                     const float* g = gL + (size_t)row * W + x;
                     if (a.vec_ok) {
-                        v = __ldg(reinterpret_cast<const float4*>(g));
-                    } else {
-                        v.x = __ldg(g);
-                        if (x + 1 < W) v.y = __ldg(g + 1);
-                        if (x + 2 < W) v.z = __ldg(g + 2);
-                        if (x + 3 < W) v.w = __ldg(g + 3);
+                        stage_copy16(sL_addr + (uint32_t)(i * p.LS + x) * 4, g);
+                        continue;
                     }
+                    v.x = __ldg(g);
+                    if (x + 1 < W) v.y = __ldg(g + 1);
+                    if (x + 2 < W) v.z = __ldg(g + 2);
+                    if (x + 3 < W) v.w = __ldg(g + 3);
                 }
                 *reinterpret_cast<float4*>(sL + (size_t)i * p.LS + x) = v;
             }
@@ -399,17 +413,18 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                     const size_t rmat = (size_t)l * a.pm.right_stride + j;
                     const float* g = a.right + (rmat * H + (r0 + rr)) * W + x;
                     if (a.vec_ok) {
-                        v = __ldg(reinterpret_cast<const float4*>(g));
-                    } else {
-                        v.x = __ldg(g);
-                        if (x + 1 < W) v.y = __ldg(g + 1);
-                        if (x + 2 < W) v.z = __ldg(g + 2);
-                        if (x + 3 < W) v.w = __ldg(g + 3);
+                        stage_copy16(sR_addr + (uint32_t)(mm * p.RMS + rr * Wp + x) * 4, g);
+                        continue;
                     }
+                    v.x = __ldg(g);
+                    if (x + 1 < W) v.y = __ldg(g + 1);
+                    if (x + 2 < W) v.z = __ldg(g + 2);
+                    if (x + 3 < W) v.w = __ldg(g + 3);
                 }
                 *reinterpret_cast<float4*>(sR + (size_t)mm * p.RMS + (size_t)rr * Wp + x) = v;
             }
         }
+        stage_wait();
         if (p.schedule == kSchedWarpQueue && tid == 0) *queue = 0;
         __syncthreads();
 
