@@ -225,6 +225,66 @@ def cpu_baseline(target_seconds: float, threads: int):
 
 
 # ---- the reference arm -----------------------------------------------------------------------------
+def reference_gpu_baseline(dev, iters=20):
+    """The reference's own best CUDA kernels, recompiled unmodified for sm_100 (optional
+    libraries under oracle/_ref/, see oracle/Makefile targets refcuda / refcuda_n2m), timed on
+    this GPU on the same resident inputs with the best published arguments: a reported
+    baseline next to `cpu_baseline`, nothing of the product runs through it.  Returns None
+    when the library was not built."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import pyoracle
+    if not pyoracle.ReferenceCuda.available():
+        return None
+    rc = pyoracle.ReferenceCuda()
+    side = [torch.cuda.Stream() for _ in range(8)]
+    legacy = torch.cuda.default_stream()        # launchers without a stream argument use it
+    out = {"kind": "reference CUDA kernels (grouped-overlap / multi-matrix families) compiled for sm_100",
+           "args": {"one_to_one": "4_8_8", "one_to_many": "4_4_4_4", "n_to_mn": "4_4_4_4 on 8 streams",
+                    "n_to_m": "4_4_4_4_4"}, "per_config": {}}
+    for k, (mode, r, c, nl, nr) in CONFIGS.items():
+        if mode == "n_to_m" and rc.n2m is None:
+            out["per_config"][k] = {"unavailable": "n-to-m kernel library not built (hours of compile time)"}
+            continue
+        d = dev[k]
+        res = torch.empty_like(d["out"])
+        L, R, O = d["left"].data_ptr(), d["right"].data_ptr(), res.data_ptr()
+
+        def run():
+            if mode == "one_to_one":
+                rc.one_to_one(L, R, O, r, c)
+            elif mode == "one_to_many":
+                rc.one_to_many(L, R, O, r, c, nr)
+            elif mode == "n_to_m":
+                rc.n_to_m(L, R, O, r, c, nl, nr)
+            else:
+                start = torch.cuda.Event()
+                start.record(legacy)
+                for s_ in side:
+                    s_.wait_event(start)
+                rc.n_to_mn(L, R, O, r, c, nl, nr, streams=[s_.cuda_stream for s_ in side])
+                for s_ in side:
+                    e = torch.cuda.Event()
+                    e.record(s_)
+                    legacy.wait_event(e)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            run()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record(legacy)
+        for _ in range(iters):
+            run()
+        b.record(legacy)
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / iters
+        diff = float((res - d["out"]).abs().max() / res.abs().max())
+        out["per_config"][k] = {"ms": ms, "gflops": flop_of(k) / (ms * 1e-3) / 1e9,
+                                "max_abs_diff_to_ours_over_max": diff}
+    return out
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -502,6 +562,14 @@ def main():
                     "result_probe": checksum},
             "gpu_launches": int(launches),
         }
+        if world == 1:
+            ref_gpu = reference_gpu_baseline(dev)
+            if ref_gpu is not None:
+                for k, e in ref_gpu["per_config"].items():
+                    if "ms" in e:
+                        e["ours_ms"] = per_ms_max[k]
+                        e["speedup"] = e["ms"] / per_ms_max[k]
+                line["reference_gpu_kernels"] = ref_gpu
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             v, kind, desc = cpu_baseline(args.cpu_seconds, threads)

@@ -284,11 +284,15 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const double segments = rows_per_block / H + 1.0;
                     const double t_rate = std::ceil(G / dev.sm_count) * ((rows_per_block + 0.25 * segments) *
                                           macs_per_row / rate + segments * t_stage);
-                    const double t_serial = rows_per_block * p.Wp * TY * kTX / 1.8e9;
+                    // the lone-warp latency bound of the static branch, per segment
+                    const double sk_flushes = 2.0 * (std::min<double>(p.SL * TY, rows_per_block) + TY) * segments;
+                    const double sk_row_cycles = 300.0 + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
+                    const double t_serial = (rows_per_block * sk_row_cycles + sk_flushes * 500.0 +
+                                             4000.0 * segments) / 1.9e9;
                     const double split_share = std::min(1.0, 2.0 * G / tasks);   // outputs added atomically
                     // more than two parts of a task do not commute: last bits then vary run to run
                     const double order_penalty = tasks >= G ? 1.0 : 1.03;
-                    t = (std::max(t_rate, t_serial) + 4e-6 + out_bytes / 3e12 + split_share * 2.3 * out_bytes / 0.4e12) *
+                    t = (std::max(t_rate, t_serial) + 5e-6 + out_bytes / 3e12 + split_share * 2.3 * out_bytes / 0.4e12) *
                         order_penalty;
                     comb = kAtomic;
                 } else {
@@ -297,14 +301,20 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const double macs_per_block = (double)p.threads * rs * p.Wp * TY * kTX;
                     const double busiest = std::ceil(tasks * S / dev.sm_count);
                     const double t_rate = busiest * (macs_per_block / rate * (rs + 0.25) / rs + t_stage);
-                    // one warp issues at most one FFMA per clock: a lower bound for tiny inputs
-                    const double t_serial = rs * p.Wp * TY * kTX / 1.8e9;
+                    // A lone warp is bound by latency, not by the SM's FFMA rate: per right row its
+                    // FFMAs one per clock plus ~150 cycles of row overhead per pass and ~40 per
+                    // chunk visit, ~500 cycles per output flush (SL * TY wrap flushes and TY final
+                    // ones per pass), ~4000 for the staging.  This decides the plan of tiny inputs
+                    // (16 x 16: many small warps tasks with few flushes beat one full warp).
+                    const double flushes = 2.0 * (std::min<double>(p.SL * TY, rs) + TY);
+                    const double row_cycles = 300.0 + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
+                    const double t_serial = (rs * row_cycles + flushes * 500.0 + 4000.0) / 1.9e9;
                     comb = want_combine;
                     if (comb == XCORR_COMBINE_AUTO) comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
                     // a memset or a second kernel in front of / behind the main one costs a few us
                     double t_combine = 0.0;
-                    if (comb == kAtomic) t_combine = 4e-6 + out_bytes / 3e12 + S * out_bytes / 0.4e12;
-                    else if (comb == kWorkspace) t_combine = 4e-6 + (2.0 * S + 1.0) * out_bytes / 3e12;
+                    if (comb == kAtomic) t_combine = 5e-6 + out_bytes / 3e12 + S * out_bytes / 0.4e12;
+                    else if (comb == kWorkspace) t_combine = 9e-6 + (2.0 * S + 1.0) * out_bytes / 3e12;
                     t = std::max(t_rate, t_serial) + t_combine;
                     grid = (unsigned)(tasks * S);
                 }

@@ -9,7 +9,10 @@ program never import or link anything from this directory.
   compiled unmodified into oracle/_ref/libxcorr_ref.so; available where that library was
   built (it needs the reference checkout at build time only).
 
-Both take float32 inputs of shape (n, rows, cols) and return outputs of shape
+* ``ReferenceCuda`` (end of file) -- the reference's own CUDA kernels recompiled for sm_100,
+  an optional GPU baseline.
+
+The two CPU checkers take float32 inputs of shape (n, rows, cols) and return outputs of shape
 (n_out, 2*rows-1, 2*cols-1) in the reference's result order (validate.hpp:230-291):
 one_to_many ``out[t]``, n_to_mn (file order) ``out[t*n_left + r]`` pairs with left ``r``,
 n_to_m ``out[r*n_right + t]``.
@@ -208,3 +211,72 @@ class Reference:
         if rc:
             raise RuntimeError("ref_validate_result failed")
         return tuple(stats)
+
+
+REFCUDA_SO = os.path.join(_HERE, "_ref", "libxcorr_refcuda.so")
+REFCUDA_N2M_SO = os.path.join(_HERE, "_ref", "libxcorr_refcuda_n2m.so")
+
+
+class ReferenceCuda:
+    """The reference's own best CUDA launchers (kernels.cuh:41-256), compiled unmodified for
+    sm_100 by ``make -C oracle refcuda`` / ``refcuda_n2m`` with the template limits of the best
+    published arguments.  A GPU baseline and a further parity witness; optional (the build
+    takes from ten minutes to hours and needs the reference checkout).
+
+    All methods take DEVICE pointers (ints) and launch asynchronously, like the reference's
+    launchers.  Arguments default to the best published ones: one_to_one ``4_8_8``
+    (warps, shifts per thread, left rows), one_to_many / n_to_mn ``4_4_4_4`` (warps, shifts per
+    right matrix, right matrices per thread, left rows), n_to_m ``4_4_4_4_4``.
+    """
+
+    def __init__(self, path: str = REFCUDA_SO, n2m_path: str = REFCUDA_N2M_SO):
+        self.lib = C.CDLL(path)
+        u32, vp = C.c_uint32, C.c_void_p
+        self.lib.refcuda_overlap_wise.argtypes = [vp, vp, vp, u32, u32, u32, u32]
+        self.lib.refcuda_one_to_one.argtypes = [vp, vp, vp, u32, u32, u32, u32, u32]
+        self.lib.refcuda_one_to_many.argtypes = [vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, vp]
+        for f in (self.lib.refcuda_overlap_wise, self.lib.refcuda_one_to_one, self.lib.refcuda_one_to_many):
+            f.restype = C.c_int
+        self.n2m = None
+        if os.path.exists(n2m_path):
+            self.n2m = C.CDLL(n2m_path)
+            self.n2m.refcuda_n_to_m.argtypes = [vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, u32, u32]
+            self.n2m.refcuda_n_to_m.restype = C.c_int
+
+    @staticmethod
+    def available(path: str = REFCUDA_SO) -> bool:
+        return os.path.exists(path)
+
+    @staticmethod
+    def _check(rc: int, what: str) -> None:
+        if rc != 0:
+            raise RuntimeError(f"reference launcher {what} rejected its arguments (code {rc})")
+
+    def overlap_wise(self, d_left, d_right, d_out, rows, cols, n_left=1, batch=1):
+        """run_cross_corr_naive_original: `batch` deformed matrices per reference matrix."""
+        self._check(self.lib.refcuda_overlap_wise(d_left, d_right, d_out, rows, cols, n_left, batch), "overlap_wise")
+
+    def one_to_one(self, d_left, d_right, d_out, rows, cols, warps=4, shifts=8, left_rows=8):
+        self._check(self.lib.refcuda_one_to_one(d_left, d_right, d_out, rows, cols, warps, shifts, left_rows),
+                    "one_to_one")
+
+    def one_to_many(self, d_left, d_right, d_out, rows, cols, n_right, warps=4, shifts=4, right_mats=4,
+                    left_rows=4, stream=0):
+        self._check(self.lib.refcuda_one_to_many(d_left, d_right, d_out, rows, cols, n_right, warps, shifts,
+                                                 right_mats, left_rows, stream), "one_to_many")
+
+    def n_to_mn(self, d_left, d_right, d_out, rows, cols, n_left, n_right, streams=(0,), **kw):
+        """One one_to_many launch per left matrix on round-robin streams, grouped order
+        (n_to_mn.hpp:553-571)."""
+        m = n_right // n_left
+        in_b, out_b = rows * cols * 4, (2 * rows - 1) * (2 * cols - 1) * 4
+        for l in range(n_left):
+            self.one_to_many(d_left + l * in_b, d_right + l * m * in_b, d_out + l * m * out_b, rows, cols, m,
+                             stream=streams[l % len(streams)], **kw)
+
+    def n_to_m(self, d_left, d_right, d_out, rows, cols, n_left, n_right, warps=4, shifts=4, left_mats=4,
+               right_mats=4, left_rows=4):
+        if self.n2m is None:
+            raise RuntimeError("the reference n-to-m kernel library was not built (make -C oracle refcuda_n2m)")
+        self._check(self.n2m.refcuda_n_to_m(d_left, d_right, d_out, rows, cols, n_left, n_right, warps, shifts,
+                                            left_mats, right_mats, left_rows), "n_to_m")

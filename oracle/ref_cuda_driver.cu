@@ -51,14 +51,4 @@ int refcuda_one_to_many(const float* left, const float* right, float* out, uint3
                              right_mats, left_rows, static_cast<cudaStream_t>(stream)); });
 }
 
-// multi-matrix-both + grouped-overlap, best n-to-m
-__attribute__((visibility("default")))
-int refcuda_n_to_m(const float* left, const float* right, float* out, uint32_t rows, uint32_t cols,
-                   uint32_t n_left, uint32_t n_right, uint32_t warps, uint32_t shifts, uint32_t left_mats,
-                   uint32_t right_mats, uint32_t left_rows) {
-    return guarded([&] { run_ccn_n_to_m_shuffle_multirow_both_multimat_both<float, float>(
-                             left, right, out, msize(rows, cols), ssize(rows, cols), n_left, n_right, warps,
-                             shifts, left_mats, right_mats, left_rows); });
-}
-
 }

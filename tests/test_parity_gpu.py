@@ -322,3 +322,38 @@ def test_ffma_probe_reports_a_plausible_peak(xc):
     flops, ms = xc.ffma_peak_probe()
     assert 20e12 < flops < 90e12, flops                  # B200: 148 SM x 128 lanes x 2 x ~1.9 GHz
     assert ms > 0
+
+
+# ---- the reference's own CUDA kernels as a further witness --------------------------------------
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [
+    ("one_to_one", 16, 16, 1, 1), ("one_to_one", 64, 64, 1, 1), ("one_to_one", 24, 24, 1, 1),
+    ("one_to_many", 32, 32, 1, 24), ("one_to_many", 48, 48, 1, 9), ("n_to_mn", 24, 24, 3, 12),
+])
+def test_reference_cuda_kernels_agree(xc, oracle, mode, rows, cols, nl, nr):
+    """Where the reference's CUDA kernels were compiled for this GPU (oracle/Makefile, target
+    refcuda; optional), their results, this library's and the oracle's agree: three
+    implementations, two of them the reference's own.  The reference kernels accumulate in
+    float in their own order, so they are held to 2e-5 of the double oracle, like its CPU
+    float path.  Sizes are ones the reference's own benchmark runs these kernels on."""
+    import pyoracle
+    if not pyoracle.ReferenceCuda.available():
+        pytest.skip("oracle/_ref/libxcorr_refcuda.so not built")
+    rc = pyoracle.ReferenceCuda()
+    left, right = seeded_inputs(rows, cols, nl, nr, 77)
+    want = oracle_grouped(oracle, mode, left, right)
+    ours = gpu_run(xc, mode, left, right)
+    dl, dr = torch.from_numpy(left).cuda(), torch.from_numpy(right).cuda()
+    out = torch.full(ours.shape, float("nan"), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    if mode == "one_to_one":
+        rc.one_to_one(dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols)
+    elif mode == "one_to_many":
+        rc.one_to_many(dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols, nr)
+    else:
+        rc.n_to_mn(dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols, nl, nr)
+    torch.cuda.synchronize()
+    theirs = out.cpu().numpy()
+    assert not np.isnan(theirs).any()
+    assert rel_err(theirs, want) <= 2e-5
+    assert rel_err(ours, want) <= REL_TOL
+    assert rel_err(ours, theirs.astype(np.float64)) <= 2e-5
