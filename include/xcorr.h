@@ -209,6 +209,33 @@ XCORR_API uint64_t xcorr_num_results(int32_t mode, uint32_t n_left, uint32_t n_r
 XCORR_API int32_t xcorr_validate_input_size(int32_t mode, uint32_t rows, uint32_t cols,
                                             uint32_t n_left, uint32_t n_right);
 
+/* ---- FFT path ---------------------------------------------------------------------------
+ * The same four modes through cuFFT: zero padding to 2*rows x 2*cols on the device, one batched
+ * real-to-complex transform of all inputs, spectrum products left * conj(right), one batched
+ * complex-to-real transform of all pairs, unpacking.  Stands in for the reference's
+ * fft_original_alg_* / fft_reduced_transfer_* classes (one_to_one.hpp:888-1170,
+ * one_to_many.hpp:502-780, n_to_mn.hpp:720-1000), fft_better_hadamard_alg_n_to_m
+ * (n_to_m.hpp:647-800) and their kernels run_hadamard_original / run_hadamard_n_to_m_over_*
+ * (kernels.cuh, hadamard.cu) and run_scatter (scatter.cu).  Inputs, pair order and stream
+ * semantics as for the direct entry points.  Float rounding differs from the direct path
+ * (about 1e-6 of the largest result at the benchmark sizes).
+ * layout XCORR_FFT_NORMALIZED: `d_out` gets the direct path's result layout,
+ *   (2*rows-1) x (2*cols-1) per pair, scaled (fft_helpers.hpp:213-262 normalize_fft_results,
+ *   done on the host there).
+ * layout XCORR_FFT_RAW: `d_out` gets 2*rows x 2*cols per pair exactly as the inverse transform
+ *   leaves it -- shift (sy, sx) at row sy mod 2*rows, column sx mod 2*cols, times 4*rows*cols:
+ *   what the reference's fft classes hold in results() and write without --normalize.
+ * The workspace (xcorr_fft_workspace_bytes) is required.  cuFFT plans are created on first use
+ * of a (size, batch) and cached; xcorr_fft_release_plans() destroys them. */
+typedef enum xcorr_fft_layout { XCORR_FFT_NORMALIZED = 0, XCORR_FFT_RAW = 1 } xcorr_fft_layout;
+
+XCORR_API size_t xcorr_fft_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols,
+                                           uint32_t n_left, uint32_t n_right, int32_t layout);
+XCORR_API xcorr_status xcorr_fft_f32(int32_t mode, const float* d_left, const float* d_right, float* d_out,
+                                     uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                     int32_t layout, void* d_workspace, size_t workspace_bytes, void* stream);
+XCORR_API void xcorr_fft_release_plans(void);
+
 /* ---- host-buffer entry points -----------------------------------------------------------
  * The reference's whole computation step for one algorithm object: prepare (cudaMalloc),
  * transfer (H2D), run, finalize (D2H), free -- main.cpp:123-174, one_to_one.hpp:112-135 and

@@ -112,6 +112,11 @@ def lib() -> C.CDLL:
     L.xcorr_reset_launch_count.argtypes = []
     L.xcorr_reset_launch_count.restype = None
     L.xcorr_ffma_peak_probe.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_double), vp]
+    L.xcorr_fft_workspace_bytes.argtypes = [i32, u32, u32, u32, u32, i32]
+    L.xcorr_fft_workspace_bytes.restype = sz
+    L.xcorr_fft_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, i32, vp, sz, vp]
+    L.xcorr_fft_release_plans.argtypes = []
+    L.xcorr_fft_release_plans.restype = None
     _lib = L
     return L
 
@@ -157,6 +162,27 @@ def run_device(mode, d_left: int, d_right: int, d_out: int, rows: int, cols: int
     check(lib().xcorr_run_f32(_mode(mode), d_left, d_right, d_out, rows, cols, n_left, n_right,
                               C.byref(hints) if hints is not None else None,
                               d_workspace or None, workspace_bytes_, stream or None))
+
+
+FFT_LAYOUTS = {"normalized": 0, "raw": 1}
+
+
+def fft_workspace_bytes(mode, rows, cols, n_left, n_right, layout="normalized") -> int:
+    return int(lib().xcorr_fft_workspace_bytes(_mode(mode), rows, cols, n_left, n_right, FFT_LAYOUTS[layout]))
+
+
+def fft_out_shape(mode, rows, cols, n_left, n_right, layout="normalized"):
+    n = int(lib().xcorr_num_results(_mode(mode), n_left, n_right))
+    return (n, 2 * rows - 1, 2 * cols - 1) if layout == "normalized" else (n, 2 * rows, 2 * cols)
+
+
+def run_fft_device(mode, d_left: int, d_right: int, d_out: int, rows: int, cols: int, n_left: int,
+                   n_right: int, layout="normalized", d_workspace: int = 0, workspace_bytes_: int = 0,
+                   stream: int = 0) -> None:
+    """The cuFFT path on raw device addresses (asynchronous).  ``layout`` "normalized" gives the
+    direct path's result layout, "raw" the 2*rows x 2*cols unnormalised inverse transforms."""
+    check(lib().xcorr_fft_f32(_mode(mode), d_left, d_right, d_out, rows, cols, n_left, n_right,
+                              FFT_LAYOUTS[layout], d_workspace or None, workspace_bytes_, stream or None))
 
 
 def run_host(mode, left: np.ndarray, right: np.ndarray, hints: Hints | None = None, device: int = 0,

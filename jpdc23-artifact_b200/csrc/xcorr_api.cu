@@ -733,6 +733,48 @@ xcorr_status xcorr_n_to_m_f32(const float* d_left, const float* d_right, float* 
                       d_workspace, workspace_bytes, stream);
 }
 
+size_t xcorr_fft_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                 int32_t layout) {
+    PairMap pm{};
+    if (check_sizes(mode, rows, cols, n_left, n_right, &pm) != XCORR_OK) return 0;
+    if (layout != XCORR_FFT_NORMALIZED && layout != XCORR_FFT_RAW) return 0;
+    return fft_workspace_layout(pm, (int)rows, (int)cols, n_right, layout == XCORR_FFT_RAW).total;
+}
+
+xcorr_status xcorr_fft_f32(int32_t mode, const float* d_left, const float* d_right, float* d_out,
+                           uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                           int32_t layout, void* d_workspace, size_t workspace_bytes, void* stream) {
+    if (!d_left || !d_right || !d_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+    PairMap pm{};
+    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+    if (st != XCORR_OK) return st;
+    if (layout != XCORR_FFT_NORMALIZED && layout != XCORR_FFT_RAW)
+        return fail(XCORR_ERR_INVALID_HINT, "layout must be XCORR_FFT_NORMALIZED or XCORR_FFT_RAW");
+    const FftLayout lay = fft_workspace_layout(pm, (int)rows, (int)cols, n_right, layout == XCORR_FFT_RAW);
+    if (!d_workspace || workspace_bytes < lay.total)
+        return fail(XCORR_ERR_WORKSPACE, "the FFT path needs xcorr_fft_workspace_bytes() bytes of workspace");
+    if (reinterpret_cast<uintptr_t>(d_workspace) % 256 != 0)
+        return fail(XCORR_ERR_WORKSPACE, "the FFT workspace must be 256-byte aligned");
+    DeviceInfo dev;
+    int device = 0;
+    if ((st = current_device_info(&dev, &device)) != XCORR_OK) return st;
+    std::string err;
+    int launches = 0;
+    const int rc = fft_run(d_left, d_right, d_out, (int)rows, (int)cols, pm, n_right, layout == XCORR_FFT_RAW,
+                           d_workspace, device, dev.sm_count, static_cast<cudaStream_t>(stream), &err, &launches);
+    t_launch_count += (uint64_t)launches;
+    if (rc != 0) return fail(XCORR_ERR_CUDA, err);
+    char buf[256];
+    std::snprintf(buf, sizeof buf, "kernel=fft transform=%ux%u inputs=%llu pairs=%llu product=%s layout=%s workspace=%zu",
+                  2 * rows, 2 * cols, (unsigned long long)pm.n_left + n_right, (unsigned long long)pm.n_left * pm.m,
+                  lay.product_in_place ? "in-place" : "separate", layout == XCORR_FFT_RAW ? "raw" : "normalized",
+                  lay.total);
+    t_last_launch = buf;
+    return XCORR_OK;
+}
+
+void xcorr_fft_release_plans(void) { fft_release_plans(); }
+
 size_t xcorr_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                              const xcorr_hints* hints) {
     PairMap pm{};

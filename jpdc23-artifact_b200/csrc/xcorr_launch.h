@@ -1,6 +1,7 @@
 // Launcher declarations: the only way the C-ABI layer reaches device code.
 #pragma once
 #include <cuda_runtime.h>
+#include <string>
 #include "xcorr_plan.h"
 
 namespace xcorr {
@@ -20,5 +21,20 @@ cudaError_t launch_ffma_probe(float* sink, int iters, int blocks, cudaStream_t s
 // address on the current device (looked up once per device).
 size_t noalloc_scratch_bytes();
 cudaError_t noalloc_scratch_address(float** ptr);
+
+// FFT path (xcorr_fft.cu).  Workspace layout in bytes: padded real inputs, spectra of all
+// inputs, spectrum products (absent when they overwrite the right spectra: every mode but
+// n_to_m), raw inverse transforms (absent when the caller wants the raw result in `out`).
+struct FftLayout {
+    size_t padded_off, spectra_off, product_off, raw_off, total;
+    int product_in_place;
+};
+FftLayout fft_workspace_layout(const PairMap& pm, int H, int W, unsigned n_right, int raw_result);
+// Enqueues the whole path on `stream`.  0 = ok, 1 = CUDA error, 2 = cuFFT error (*err says which);
+// *launches is increased by the number of own kernels launched.
+int fft_run(const float* left, const float* right, float* out, int H, int W, const PairMap& pm, unsigned n_right,
+            int raw_result, void* workspace, int device, int sm_count, cudaStream_t stream, std::string* err,
+            int* launches);
+void fft_release_plans();
 
 }  // namespace xcorr

@@ -357,3 +357,75 @@ def test_reference_cuda_kernels_agree(xc, oracle, mode, rows, cols, nl, nr):
     assert rel_err(theirs, want) <= 2e-5
     assert rel_err(ours, want) <= REL_TOL
     assert rel_err(ours, theirs.astype(np.float64)) <= 2e-5
+
+
+# ---- FFT path ---------------------------------------------------------------------------------
+def fft_run(xc, mode, left, right, layout="normalized"):
+    left = np.ascontiguousarray(left, np.float32)
+    right = np.ascontiguousarray(right, np.float32)
+    nl, rows, cols = left.shape
+    nr = right.shape[0]
+    dl, dr = torch.from_numpy(left).cuda(), torch.from_numpy(right).cuda()
+    out = torch.full(xc.fft_out_shape(mode, rows, cols, nl, nr, layout), float("nan"), dtype=torch.float32,
+                     device="cuda")
+    wsb = xc.fft_workspace_bytes(mode, rows, cols, nl, nr, layout)
+    ws = torch.empty(wsb + 256, dtype=torch.uint8, device="cuda")
+    base = (ws.data_ptr() + 255) // 256 * 256
+    xc.run_fft_device(mode, dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols, nl, nr, layout, base, wsb,
+                      torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [
+    ("one_to_one", 16, 16, 1, 1), ("one_to_one", 256, 256, 1, 1), ("one_to_one", 19, 23, 1, 1),
+    ("one_to_one", 1, 1, 1, 1), ("one_to_one", 3, 40, 1, 1),
+    ("one_to_many", 64, 64, 1, 33), ("one_to_many", 17, 12, 1, 5),
+    ("n_to_mn", 48, 48, 4, 24), ("n_to_mn", 9, 14, 3, 6),
+    ("n_to_m", 32, 32, 5, 7), ("n_to_m", 11, 6, 2, 3),
+])
+def test_fft_path_matches_the_oracle(xc, oracle, mode, rows, cols, nl, nr):
+    """The cuFFT path in the direct path's result layout against the double oracle (same
+    tolerance), and against the direct path itself."""
+    left, right = seeded_inputs(rows, cols, nl, nr, 500 + rows)
+    want = oracle_grouped(oracle, mode, left, right)
+    got = fft_run(xc, mode, left, right)
+    assert got.shape == want.shape
+    assert not np.isnan(got).any()
+    assert rel_err(got, want) <= REL_TOL, xc.last_launch()
+    assert xc.last_launch().startswith("kernel=fft")
+    direct = gpu_run(xc, mode, left, right)
+    assert rel_err(got, direct.astype(np.float64)) <= 2e-5
+
+
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [("one_to_one", 10, 10, 1, 1), ("one_to_many", 8, 12, 1, 4),
+                                                  ("n_to_m", 6, 5, 2, 3)])
+def test_fft_raw_layout_is_the_reference_result_layout(xc, oracle, mode, rows, cols, nl, nr):
+    """Raw layout: 2H x 2W per pair, shift (sy, sx) at (sy mod 2H, sx mod 2W), times 4HW, the row
+    and column at H / W unused -- what normalize_fft_results (fft_helpers.hpp:213-262) expects."""
+    left, right = seeded_inputs(rows, cols, nl, nr, 41)
+    want = oracle_grouped(oracle, mode, left, right)
+    raw = fft_run(xc, mode, left, right, layout="raw")
+    assert raw.shape == (want.shape[0], 2 * rows, 2 * cols)
+    norm = np.empty_like(want)
+    H, W = rows, cols
+    for oy in range(2 * H - 1):
+        for ox in range(2 * W - 1):
+            norm[:, oy, ox] = raw[:, (oy - (H - 1)) % (2 * H), (ox - (W - 1)) % (2 * W)] / (4.0 * H * W)
+    assert rel_err(norm, want) <= REL_TOL
+    # the quadrant arithmetic of the reference: top-left quadrant of raw -> centre of the result
+    assert abs(raw[0, 0, 0] / (4.0 * H * W) - want[0, H - 1, W - 1]) <= REL_TOL * np.abs(want).max()
+
+
+def test_fft_path_argument_errors(xc):
+    left, right = seeded_inputs(8, 8, 1, 1, 3)
+    dl, dr = torch.from_numpy(left).cuda(), torch.from_numpy(right).cuda()
+    out = torch.empty((1, 15, 15), dtype=torch.float32, device="cuda")
+    with pytest.raises(xc.XcorrError) as e:
+        xc.run_fft_device("one_to_one", dl.data_ptr(), dr.data_ptr(), out.data_ptr(), 8, 8, 1, 1)
+    assert e.value.status == 4                               # no workspace
+    with pytest.raises(xc.XcorrError) as e:
+        xc.run_fft_device("one_to_many", dl.data_ptr(), dr.data_ptr(), out.data_ptr(), 8, 8, 2, 1)
+    assert e.value.status == 2
+    assert xc.fft_workspace_bytes("one_to_one", 8, 8, 1, 1) > 0
+    assert xc.fft_workspace_bytes("one_to_one", 8, 8, 1, 1, "raw") < xc.fft_workspace_bytes("one_to_one", 8, 8, 1, 1)
