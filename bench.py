@@ -285,6 +285,51 @@ def reference_gpu_baseline(dev, iters=20):
     return out
 
 
+def fft_path_timings(xc, dev, stream, hbm_peak, iters=20):
+    """The cuFFT path (xcorr_fft_f32, normalized layout) on the same resident inputs: the
+    algorithmic alternative the reference carries next to the direct kernels.  Reported beside
+    the headline, not part of it.  `bytes` is the compulsory traffic of its five passes (pad,
+    forward transform, product, inverse transform, unpack), each reading and writing its
+    operands once."""
+    import torch
+    out = {}
+    for k, (mode, r, c, nl, nr) in CONFIGS.items():
+        d = dev[k]
+        wsb = xc.fft_workspace_bytes(mode, r, c, nl, nr)
+        ws = torch.empty(wsb + 256, dtype=torch.uint8, device="cuda")
+        base = (ws.data_ptr() + 255) // 256 * 256
+        res = torch.empty_like(d["out"])
+
+        def run():
+            xc.run_fft_device(mode, d["left"].data_ptr(), d["right"].data_ptr(), res.data_ptr(), r, c, nl, nr,
+                              "normalized", base, wsb, stream)
+        for _ in range(3):
+            run()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(iters):
+            run()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / iters
+        pairs = pairs_of(mode, nl, nr)
+        real, cplx = 4 * r * c * 4, 2 * r * (c + 1) * 8          # bytes of one padded matrix / one spectrum
+        n_in = nl + nr
+        traffic = (n_in * (r * c * 4 + real)                      # pad
+                   + n_in * (real + cplx)                         # forward
+                   + pairs * 3 * cplx                             # product (left spectra re-read from L2)
+                   + pairs * (cplx + real)                        # inverse
+                   + pairs * (real + (2 * r - 1) * (2 * c - 1) * 4))   # unpack
+        diff = float((res - d["out"]).abs().max() / d["out"].abs().max())
+        out[k] = {"ms": ms, "equivalent_gflops": flop_of(k) / (ms * 1e-3) / 1e9, "bytes": traffic,
+                  "hbm_gbs": traffic / (ms * 1e-3) / 1e9, "frac_hbm_measured": traffic / (ms * 1e-3) / 1e9 / hbm_peak,
+                  "max_abs_diff_to_direct_over_max": diff}
+        del ws, res
+    return out
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -563,6 +608,9 @@ def main():
             "gpu_launches": int(launches),
         }
         if world == 1:
+            line["fft_path"] = fft_path_timings(xc, dev, stream, hbm_peak)
+            for k, e in line["fft_path"].items():
+                e["direct_ms"] = per_ms_max[k]
             ref_gpu = reference_gpu_baseline(dev)
             if ref_gpu is not None:
                 for k, e in ref_gpu["per_config"].items():

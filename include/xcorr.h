@@ -72,7 +72,10 @@ typedef enum xcorr_kernel {
     XCORR_KERNEL_AUTO = 0,          /* per-shape selection */
     XCORR_KERNEL_TILE = 1,          /* register-tiled circular-class kernel (the fast path) */
     XCORR_KERNEL_OVERLAP_WISE = 2,  /* one thread per overlap -- run_cross_corr_naive_original, naive_original.cu:131-161 */
-    XCORR_KERNEL_WARP_PER_OVERLAP = 3 /* one warp per overlap -- run_ccn_warp_per_shift, naive_warp_per_shift.cu:308-335 */
+    XCORR_KERNEL_WARP_PER_OVERLAP = 3, /* one warp per overlap -- run_ccn_warp_per_shift, naive_warp_per_shift.cu:308-335 */
+    XCORR_KERNEL_FFT = 4            /* the cuFFT path (xcorr_fft_f32 with the normalized layout); needs the
+                                       workspace xcorr_workspace_bytes() reports for this hint.  Never chosen
+                                       automatically: its rounding differs from the direct path's */
 } xcorr_kernel;
 
 /* How partial sums of a row-split launch are combined (the reference's "work

@@ -26,7 +26,7 @@ CROSS_PATH = os.path.join(PKG_DIR, "bin", "cross")
 HEADER_PATH = os.path.join(os.path.dirname(PKG_DIR), "include", "xcorr.h")
 
 MODES = {"one_to_one": 0, "one_to_many": 1, "n_to_mn": 2, "n_to_m": 3}
-KERNELS = {"auto": 0, "tile": 1, "overlap_wise": 2, "warp_per_overlap": 3}
+KERNELS = {"auto": 0, "tile": 1, "overlap_wise": 2, "warp_per_overlap": 3, "fft": 4}
 COMBINE = {"auto": 0, "store": 1, "atomic": 2, "workspace": 3}
 
 

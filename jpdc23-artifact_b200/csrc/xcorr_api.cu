@@ -449,6 +449,9 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
         ++t_launch_count;
         return XCORR_OK;
     }
+    if (kernel == XCORR_KERNEL_FFT)
+        return xcorr_fft_f32(mode, d_left, d_right, d_out, rows, cols, n_left, n_right, XCORR_FFT_NORMALIZED,
+                             d_ws, ws_bytes, stream_v);
     if (kernel != XCORR_KERNEL_TILE) return fail(XCORR_ERR_INVALID_HINT, "unknown kernel family");
 
     TilePlan p{};
@@ -779,6 +782,8 @@ size_t xcorr_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols, uint32_
                              const xcorr_hints* hints) {
     PairMap pm{};
     if (check_sizes(mode, rows, cols, n_left, n_right, &pm) != XCORR_OK) return 0;
+    if (pick_kernel(hints) == XCORR_KERNEL_FFT)
+        return fft_workspace_layout(pm, (int)rows, (int)cols, n_right, 0).total;
     if (pick_kernel(hints) != XCORR_KERNEL_TILE) return 0;
     DeviceInfo dev;
     int ndev = 0;
@@ -801,6 +806,7 @@ int32_t xcorr_describe_plan(int32_t mode, uint32_t rows, uint32_t cols, uint32_t
     const int kernel = pick_kernel(hints);
     if (kernel == XCORR_KERNEL_OVERLAP_WISE) text = "kernel=overlap_wise";
     else if (kernel == XCORR_KERNEL_WARP_PER_OVERLAP) text = "kernel=warp_per_overlap";
+    else if (kernel == XCORR_KERNEL_FFT) text = "kernel=fft";
     else if (kernel == XCORR_KERNEL_TILE) {
         DeviceInfo dev;
         int ndev = 0;

@@ -102,14 +102,18 @@ std::vector<algorithm_spec> build_registry() {
         {"nai_warp_per_shift_shared_mem_n_to_m", N2M, family::warp_per_overlap,
          with(smem(16), {I("right_matrices_per_block", 8), streams}), false},
         {"nai_block_per_shift_one_to_one", O2O, family::warp_per_overlap, {I("block_size", 128)}, false},
-        // FFT engine (main.cpp:403-409): recognised, not part of this build
-        {"fft_orig_one_to_one", O2O, family::fft, {}, false},
-        {"fft_reduced_transfer_one_to_one", O2O, family::fft, {}, false},
-        {"fft_orig_one_to_many", O2M, family::fft, {}, false},
-        {"fft_reduced_transfer_one_to_many", O2M, family::fft, {}, false},
-        {"fft_orig_n_to_mn", NMN, family::fft, {}, false},
-        {"fft_reduced_transfer_n_to_mn", NMN, family::fft, {}, false},
-        {"fft_better_n_to_m", N2M, family::fft, {}, false},
+        // FFT engine (main.cpp:403-409); argument keys of one_to_one.hpp:895,1029-1031, n_to_m.hpp:655-656
+        {"fft_orig_one_to_one", O2O, family::fft, {I("hadamard_threads_per_block", 256)}, false},
+        {"fft_reduced_transfer_one_to_one", O2O, family::fft,
+         {I("scatter_threads_per_block", 256), I("scatter_items_per_thread", 10), I("hadamard_threads_per_block", 256)}, false},
+        {"fft_orig_one_to_many", O2M, family::fft, {I("hadamard_threads_per_block", 256)}, false},
+        {"fft_reduced_transfer_one_to_many", O2M, family::fft,
+         {I("scatter_threads_per_block", 256), I("scatter_items_per_thread", 10), I("hadamard_threads_per_block", 256)}, false},
+        {"fft_orig_n_to_mn", NMN, family::fft, {I("hadamard_threads_per_block", 256)}, false},
+        {"fft_reduced_transfer_n_to_mn", NMN, family::fft,
+         {I("scatter_threads_per_block", 256), I("scatter_items_per_thread", 10), I("hadamard_threads_per_block", 256)}, false},
+        {"fft_better_n_to_m", N2M, family::fft,
+         {I("hadamard_threads_per_block", 256), I("hadamard_items_per_thread", 10)}, false},
     };
     return r;
 }
@@ -149,10 +153,10 @@ const algorithm_spec* find_algorithm(const std::string& name) {
     return nullptr;
 }
 
-std::vector<std::string> sorted_algorithm_names(bool include_unavailable) {
+std::vector<std::string> sorted_algorithm_names(bool) {
     std::vector<std::string> names;
     for (const auto& s : algorithm_registry())
-        if (include_unavailable || s.fam != family::fft) names.push_back(s.name);
+        names.push_back(s.name);
     std::sort(names.begin(), names.end());
     return names;
 }
@@ -161,9 +165,6 @@ std::vector<std::string> sorted_algorithm_names(bool include_unavailable) {
 algorithm::algorithm(const algorithm_spec& spec, const json_object& args, double min_time_ns,
                      benchmark_type bench, std::vector<int> devices)
     : spec_(spec), min_time_ns_(min_time_ns), bench_(bench), devices_(std::move(devices)) {
-    if (spec_.fam == family::fft)
-        throw argument_error("algorithm \"" + spec_.name + "\" belongs to the FFT engine, which this build does not contain",
-                             spec_.name);
     if (devices_.empty()) devices_.push_back(0);
 
     // JSON -> values with the reference's defaults, echoed in the reference's column order
@@ -213,6 +214,11 @@ algorithm::algorithm(const algorithm_spec& spec, const json_object& args, double
         hints_.block_threads = static_cast<int32_t>(std::min<long>(std::max<long>(threads, 32), 1024));
         break;
     }
+    case family::fft:
+        // The reference's launch-shape keys (threads per block, items per thread) are echoed in
+        // the timing file and otherwise unused: the library sizes its own grids.
+        hints_.kernel = XCORR_KERNEL_FFT;
+        break;
     case family::tile: {
         hints_.kernel = XCORR_KERNEL_TILE;
         // Legacy keys steer the plan only when the file names them; defaults stay automatic.
@@ -319,7 +325,7 @@ void algorithm::load(const std::filesystem::path& ref_path, const std::filesyste
 void algorithm::build_shards() {
     shards_.clear();
     const std::size_t in_elems = left_.matrix_elems();
-    const std::size_t out_elems = static_cast<std::size_t>(2 * left_.rows() - 1) * (2 * left_.cols() - 1);
+    const std::size_t out_elems = static_cast<std::size_t>(result_.rows()) * result_.cols();
     const uint32_t nl = left_.num_matrices(), nr = right_.num_matrices(), m = rights_per_left();
     const int parts = (spec_.mode == XCORR_ONE_TO_ONE) ? 1 : static_cast<int>(devices_.size());
     const uint32_t units = spec_.mode == XCORR_ONE_TO_MANY ? nr : nl;
@@ -356,7 +362,12 @@ void algorithm::build_shards() {
 void algorithm::prepare() {
     timed_step(1, false, [&] {
         const uint64_t n_out = xcorr_num_results(spec_.mode, left_.num_matrices(), right_.num_matrices());
-        result_ = matrix_array(2 * left_.rows() - 1, 2 * left_.cols() - 1, static_cast<dsize_t>(n_out), on_gpu());
+        // FFT algorithms without --normalize hold the inverse transforms as they are: 2H x 2W,
+        // circular shifts, unnormalised (one_to_one.hpp:930, fft_alg.hpp:13-20)
+        if (raw_fft())
+            result_ = matrix_array(2 * left_.rows(), 2 * left_.cols(), static_cast<dsize_t>(n_out), true);
+        else
+            result_ = matrix_array(2 * left_.rows() - 1, 2 * left_.cols() - 1, static_cast<dsize_t>(n_out), on_gpu());
         if (!on_gpu()) return;
         build_shards();
         for (auto& s : shards_) {
@@ -367,7 +378,9 @@ void algorithm::prepare() {
             CUCH(cudaMalloc(&s.d_left, s.left_elems * sizeof(float)));
             CUCH(cudaMalloc(&s.d_right, s.right_elems * sizeof(float)));
             CUCH(cudaMalloc(&s.d_out, s.out_elems * sizeof(float)));
-            s.ws_bytes = xcorr_workspace_bytes(spec_.mode, left_.rows(), left_.cols(), s.n_left, s.n_right, &hints_);
+            s.ws_bytes = raw_fft()
+                ? xcorr_fft_workspace_bytes(spec_.mode, left_.rows(), left_.cols(), s.n_left, s.n_right, XCORR_FFT_RAW)
+                : xcorr_workspace_bytes(spec_.mode, left_.rows(), left_.cols(), s.n_left, s.n_right, &hints_);
             if (s.ws_bytes) CUCH(cudaMalloc(&s.d_ws, s.ws_bytes));
         }
     });
@@ -394,8 +407,12 @@ void algorithm::transfer() {
 void algorithm::launch_all() {
     for (auto& s : shards_) {
         CUCH(cudaSetDevice(s.device));
-        xcorr_check(xcorr_run_f32(spec_.mode, s.d_left, s.d_right, s.d_out, left_.rows(), left_.cols(),
-                                  s.n_left, s.n_right, &hints_, s.d_ws, s.ws_bytes, s.stream));
+        if (raw_fft())
+            xcorr_check(xcorr_fft_f32(spec_.mode, s.d_left, s.d_right, s.d_out, left_.rows(), left_.cols(),
+                                      s.n_left, s.n_right, XCORR_FFT_RAW, s.d_ws, s.ws_bytes, s.stream));
+        else
+            xcorr_check(xcorr_run_f32(spec_.mode, s.d_left, s.d_right, s.d_out, left_.rows(), left_.cols(),
+                                      s.n_left, s.n_right, &hints_, s.d_ws, s.ws_bytes, s.stream));
     }
 }
 
@@ -511,7 +528,41 @@ void algorithm::store_results(const std::filesystem::path& out_path) {
 }
 
 // ---- validate -----------------------------------------------------------------------------
+// fft_helpers.hpp:213-262 normalize_fft_results: swap the quadrants, drop the unused row and
+// column at rows/2 and cols/2, divide by the number of elements of the transform.
+matrix_array normalize_fft_results(const matrix_array& raw) {
+    const dsize_t RH = raw.rows(), RW = raw.cols();
+    matrix_array norm(RH - 1, RW - 1, raw.num_matrices(), false);
+    const dsize_t ey = RH / 2, ex = RW / 2;
+    const float area = static_cast<float>(RH) * static_cast<float>(RW);
+    for (dsize_t i = 0; i < raw.num_matrices(); ++i) {
+        const float* src = raw.matrix(i);
+        float* dst = norm.matrix(i);
+        auto copy = [&](dsize_t sx, dsize_t sy, dsize_t w, dsize_t h, dsize_t tx, dsize_t ty) {
+            for (dsize_t y = 0; y < h; ++y)
+                for (dsize_t x = 0; x < w; ++x)
+                    dst[static_cast<std::size_t>(ty + y) * (RW - 1) + tx + x] =
+                        src[static_cast<std::size_t>(sy + y) * RW + sx + x] / area;
+        };
+        copy(0, 0, ex, ey, (RW - 1) / 2, (RH - 1) / 2);                        // top left -> bottom right
+        copy(ex + 1, 0, RW - ex - 1, ey, 0, (RH - 1) / 2);                     // top right -> bottom left
+        copy(0, ey + 1, ex, RH - ey - 1, (RW - 1) / 2, 0);                     // bottom left -> top right
+        copy(ex + 1, ey + 1, RW - ex - 1, RH - ey - 1, 0, 0);                  // bottom right -> top left
+    }
+    return norm;
+}
+
 validation_results algorithm::validate(const std::optional<std::filesystem::path>& valid_path) const {
+    if (raw_fft()) {
+        // compare in the normalised layout, like `cross validate --normalize` (main.cpp:74-76)
+        const matrix_array norm = normalize_fft_results(result_);
+        return validate_against(norm, valid_path);
+    }
+    return validate_against(result_, valid_path);
+}
+
+validation_results algorithm::validate_against(const matrix_array& result_,
+                                               const std::optional<std::filesystem::path>& valid_path) const {
     const bool grouped = spec_.mode == XCORR_N_TO_MN && on_gpu();
     if (valid_path.has_value()) {
         matrix_array valid = matrix_array::load_csv(*valid_path, false, grouped ? left_.num_matrices() : 0);

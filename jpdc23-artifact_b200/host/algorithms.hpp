@@ -64,6 +64,7 @@ struct algorithm_spec {
 
 const std::vector<algorithm_spec>& algorithm_registry();
 const algorithm_spec* find_algorithm(const std::string& name);
+matrix_array normalize_fft_results(const matrix_array& raw);
 std::vector<std::string> sorted_algorithm_names(bool include_unavailable);
 
 using string_pairs = std::vector<std::pair<std::string, std::string>>;
@@ -86,6 +87,9 @@ public:
     void store_results(const std::filesystem::path& out_path);
 
     validation_results validate(const std::optional<std::filesystem::path>& valid_path) const;
+    // `cross run --normalize`: FFT algorithms deliver the direct path's result layout instead of
+    // the raw inverse transforms (main.cpp:178-186); no effect on the other families.
+    void set_normalize(bool on) { normalize_ = on; }
 
     std::vector<std::string> measurement_labels() const;
     std::vector<measurement_result> measurements() const { return measurements_; }
@@ -119,6 +123,11 @@ private:
     std::vector<shard> shards_;
     std::vector<measurement_result> measurements_;
     long rows_per_thread_ = 0;       // explicit JSON value, 0 = not given
+    bool normalize_ = false;
+
+    bool raw_fft() const { return spec_.fam == family::fft && !normalize_; }
+    validation_results validate_against(const matrix_array& result,
+                                        const std::optional<std::filesystem::path>& valid_path) const;
 
     bool measure_common() const { return bench_ == benchmark_type::CommonSteps; }
     bool measure_alg() const { return bench_ == benchmark_type::Algorithm; }

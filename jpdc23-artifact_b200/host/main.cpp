@@ -280,6 +280,7 @@ int command_run(const std::vector<std::string>& tokens, const std::string& prog)
         alg_args = json_object::parse(f);
     }
     algorithm alg(*spec, alg_args, min_time_s * 1e9, bench, devices);
+    alg.set_normalize(a.has("normalize"));
     if (spec->fam != family::cpu) {
         int have = 0;
         if (cudaGetDeviceCount(&have) != cudaSuccess || have == 0)
@@ -357,8 +358,7 @@ int command_validate(const std::vector<std::string>& tokens, const std::string& 
     if (a.has("help")) { print_help(std::cout, prog); return 0; }
     if (a.positional.size() < 2)
         throw option_error("the option '--template_data_path' and '--validate_data_path' are required but missing");
-    if (a.has("normalize"))
-        throw std::runtime_error("--normalize applies to FFT results, which this build does not produce");
+    const bool normalize = a.has("normalize");
     const bool csv = a.has("csv"), header = a.has("print_header");
     logger log{!csv, true};
     matrix_array valid = matrix_array::load_csv(a.positional[0], false);
@@ -366,6 +366,7 @@ int command_validate(const std::vector<std::string>& tokens, const std::string& 
     for (std::size_t i = 1; i < a.positional.size(); ++i) {
         log.log("Validating " + a.positional[i]);
         matrix_array target = matrix_array::load_csv(a.positional[i], false);
+        if (normalize) target = normalize_fft_results(target);          // main.cpp:74-76
         if (target.rows() != valid.rows() || target.cols() != valid.cols() || target.num_matrices() != valid.num_matrices())
             throw std::runtime_error("Cannot validate matrices of different sizes");
         std::vector<double> target_d(target.data(), target.data() + target.size());

@@ -35,6 +35,8 @@ nai_warp_per_shift_work_distribution_one_to_one
 nai_warp_per_shift_shared_mem_one_to_one nai_warp_per_shift_shared_mem_one_to_many
 nai_warp_per_shift_shared_mem_n_to_mn nai_warp_per_shift_shared_mem_n_to_m
 nai_block_per_shift_one_to_one
+fft_orig_one_to_one fft_reduced_transfer_one_to_one fft_orig_one_to_many fft_reduced_transfer_one_to_many
+fft_orig_n_to_mn fft_reduced_transfer_n_to_mn fft_better_n_to_m
 """.split())
 
 
@@ -207,8 +209,9 @@ def test_exit_codes(cross, tmp_path):
     assert run(cross, "run", "-d", "double", "cpu_one_to_one", l, rr).returncode == 1
     r = run(cross, "run", "cpu_one_to_one", l, tmp_path / "missing.csv")
     assert r.returncode == 3 and "data loading step" in r.stderr
-    r = run(cross, "run", "fft_orig_one_to_one", l, rr)
-    assert r.returncode == 1 and "FFT engine" in r.stderr
+    (tmp_path / "badfft.json").write_text(json.dumps({"hadamard_threads_per_block": 0}))
+    r = run(cross, "run", "--args_path", tmp_path / "badfft.json", "fft_orig_one_to_one", l, rr)
+    assert r.returncode == 1 and "Invalid algorithm argument value" in r.stderr
     # wrong matrix counts for the mode, sizes that differ, broken files: computation-step errors
     write_matrices(tmp_path / "two.csv", np.zeros((2, 4, 4), np.float32))
     assert run(cross, "run", "cpu_one_to_one", l, tmp_path / "two.csv").returncode == 3
@@ -312,3 +315,51 @@ def test_gpu_devices_option_shards_without_changing_results(cross, tmp_path):
     assert all(o == outs[0] for o in outs)
     r = run(cross, "run", "--devices", 99, "nai_orig_n_to_m", tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
     assert r.returncode == 2 and "--devices" in r.stderr
+
+
+FFT_ALGS = [
+    ("fft_orig_one_to_one", "one_to_one", 16, 16, 1, 1, {"hadamard_threads_per_block": 128}),
+    ("fft_reduced_transfer_one_to_one", "one_to_one", 13, 10, 1, 1, {}),
+    ("fft_orig_one_to_many", "one_to_many", 12, 12, 1, 5, {}),
+    ("fft_reduced_transfer_n_to_mn", "n_to_mn", 8, 10, 2, 6, {"scatter_items_per_thread": 4}),
+    ("fft_better_n_to_m", "n_to_m", 9, 9, 2, 3, {}),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("alg,mode,rows,cols,nl,nr,args", FFT_ALGS)
+def test_fft_algorithms_raw_and_normalized_files(cross, oracle, tmp_path, alg, mode, rows, cols, nl, nr, args):
+    """The FFT registry names: without --normalize the output file holds the raw inverse
+    transforms (2H x 2W per pair, as the reference's fft classes store them) and
+    `cross validate --normalize` brings them to the template's layout; with --normalize the
+    file is directly comparable with the direct algorithms' output."""
+    left, right = seeded_inputs(rows, cols, nl, nr, 29)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    (tmp_path / "args.json").write_text(json.dumps(args))
+    want = oracle.run(mode, left, right, acc64=True)
+    write_matrices(tmp_path / "valid.csv", want.astype(np.float32))
+    common = ["--args_path", tmp_path / "args.json", "--no_progress", "--benchmark_type", "Algorithm",
+              "--min_time", "0.005", "--times", tmp_path / "t.csv"]
+    r = run(cross, "run", "--out", tmp_path / "norm.csv", "--normalize", "--validate", *common, alg,
+            tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    got = read_matrices(tmp_path / "norm.csv")
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max() + 5.1e-7
+    assert float(r.stdout.splitlines()[1].split(",")[0]) < 1e-3
+    head, row = open(tmp_path / "t.csv").read().splitlines()[:2]
+    assert head.split(",")[:2] == ["Kernel", "Kernel_iterations"]
+    for k, v in args.items():
+        assert row.split(",")[head.split(",").index(k)] == str(v)
+    # raw result file
+    r = run(cross, "run", "--out", tmp_path / "raw.csv", "--validate", "--no_progress", alg,
+            tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    assert float(r.stdout.splitlines()[1].split(",")[0]) < 1e-3
+    raw = read_matrices(tmp_path / "raw.csv")
+    assert raw.shape == (want.shape[0], 2 * rows, 2 * cols)
+    assert abs(raw[0, 0, 0] / (4.0 * rows * cols) - want[0, rows - 1, cols - 1]) <= 1e-4 * np.abs(want).max()
+    r = run(cross, "validate", "--normalize", "-c", "-p", tmp_path / "valid.csv", tmp_path / "raw.csv")
+    assert r.returncode == 0, r.stderr
+    assert float(r.stdout.splitlines()[1].split(",")[0]) < 1e-3

@@ -429,3 +429,22 @@ def test_fft_path_argument_errors(xc):
     assert e.value.status == 2
     assert xc.fft_workspace_bytes("one_to_one", 8, 8, 1, 1) > 0
     assert xc.fft_workspace_bytes("one_to_one", 8, 8, 1, 1, "raw") < xc.fft_workspace_bytes("one_to_one", 8, 8, 1, 1)
+
+
+@pytest.mark.parametrize("mode,nl,nr", [("one_to_many", 1, 21), ("n_to_m", 4, 6), ("n_to_mn", 4, 12)])
+def test_fft_kernel_family_through_the_common_entry_points(xc, oracle, mode, nl, nr):
+    """hints.kernel = fft routes the device, host-buffer (in pieces) and sharded entry points
+    through the cuFFT path; the workspace query answers for it."""
+    left, right = seeded_inputs(24, 20, nl, nr, 61)
+    want = oracle_grouped(oracle, mode, left, right)
+    fft = xc.make_hints(kernel="fft")
+    assert xc.workspace_bytes(mode, 24, 20, nl, nr, fft) == xc.fft_workspace_bytes(mode, 24, 20, nl, nr)
+    assert xc.describe_plan(mode, 24, 20, nl, nr, fft) == "kernel=fft"
+    got = gpu_run(xc, mode, left, right, fft)
+    assert rel_err(got, want) <= REL_TOL
+    assert xc.last_launch().startswith("kernel=fft")
+    host = xc.run_host(mode, left, right, xc.make_hints(kernel="fft", host_chunks=3))
+    assert rel_err(host, want) <= REL_TOL
+    ndev = torch.cuda.device_count()
+    sharded = xc.run_host(mode, left, right, fft, devices=[i % ndev for i in range(2)])
+    assert rel_err(sharded, want) <= REL_TOL
