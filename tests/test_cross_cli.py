@@ -196,6 +196,48 @@ def test_validate_option_and_command(cross, oracle, tmp_path):
     assert abs(float(lines[2].split(",")[0]) - 1e-3) < 1e-4
 
 
+def write_binary(path, a):
+    a = np.ascontiguousarray(a, "<f4")
+    n, rows, cols = a.shape
+    with open(path, "wb") as f:
+        f.write(b"XCORRMAT" + np.array([cols, rows, n], "<u4").tobytes() + a.tobytes())
+
+
+def read_binary(path):
+    raw = open(path, "rb").read()
+    assert raw[:8] == b"XCORRMAT"
+    cols, rows, n = np.frombuffer(raw[8:20], "<u4")
+    return np.frombuffer(raw[20:], "<f4").reshape(n, rows, cols)
+
+
+def test_binary_matrix_files(cross, oracle, tmp_path):
+    """Paths ending in .bin are binary matrix files (header + float32 data), for inputs, results
+    and validation templates alike; n_to_mn keeps the file order t*n + l in both formats."""
+    left, right = seeded_inputs(6, 9, 2, 6, 17)
+    write_binary(tmp_path / "l.bin", left)
+    write_binary(tmp_path / "r.bin", right)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    r = run(cross, "run", "-o", tmp_path / "o.bin", "cpu_n_to_mn", tmp_path / "l.bin", tmp_path / "r.bin", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    got = read_binary(tmp_path / "o.bin")
+    want = oracle.run("n_to_mn", left, right)
+    assert got.shape == want.shape and np.array_equal(got, want)          # same float arithmetic, no text rounding
+    # mixed formats: text in, binary template
+    r = run(cross, "run", "--validate", tmp_path / "o.bin", "--no_progress", "cpu_n_to_mn", tmp_path / "l.csv",
+            tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    assert float(r.stdout.splitlines()[1].split(",")[0]) < 1e-5           # text inputs carry full precision here
+    r = run(cross, "validate", "-c", "-p", tmp_path / "o.bin", tmp_path / "o.bin")
+    assert r.returncode == 0 and float(r.stdout.splitlines()[1].split(",")[0]) == 0.0
+    # broken files: loading-step errors
+    (tmp_path / "bad.bin").write_bytes(b"NOTAMATRIXFILE")
+    assert run(cross, "run", "cpu_one_to_one", tmp_path / "bad.bin", tmp_path / "bad.bin").returncode == 3
+    (tmp_path / "short.bin").write_bytes(open(tmp_path / "l.bin", "rb").read()[:-8])
+    r = run(cross, "run", "cpu_n_to_mn", tmp_path / "short.bin", tmp_path / "r.bin")
+    assert r.returncode == 3 and "file ends inside matrix" in r.stderr
+
+
 def test_exit_codes(cross, tmp_path):
     left, right = seeded_inputs(4, 4, 1, 1, 1)
     write_matrices(tmp_path / "l.csv", left)
