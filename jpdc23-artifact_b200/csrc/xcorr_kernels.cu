@@ -239,13 +239,15 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
 #pragma unroll
             for (int j = 0; j < kTX; ++j) acc[t][j] = 0.f;
 
-        // Rows r0 .. r1-1, then TY more trips that only write: trip r1 + t writes class t's
-        // final sums.  Keeping the end-of-slice writes in the row loop leaves one copy of the
-        // flush code in the kernel (instruction-cache footprint).
+        // The final sums of the slice are written either by kEndTrips = TY extra trips of the row
+        // loop (one copy of the flush code in the kernel; what the 168-register builds of
+        // TY >= 3 run fastest with) or by a rolled loop behind it (TY <= 2: with the extra trips
+        // the compiler moved all 32 accumulators at every trip of the row loop).  Measured on B200.
+        constexpr int kEndTrips = TY >= 3 ? TY : 0;
         uint32_t rrow = rmat_addr;
 #pragma unroll 1
-        for (int ry = r0; ry < r1 + TY; ++ry, rrow += (uint32_t)Wp * 4) {
-            const bool at_end = ry >= r1;
+        for (int ry = r0; ry < r1 + kEndTrips; ++ry, rrow += (uint32_t)Wp * 4) {
+            const bool at_end = kEndTrips > 0 && ry >= r1;
             // A class that starts wrapping at this row: its unwrapped-in-y part is complete.
             // The wrap rows of the warp's SL * TY classes are consecutive (one range check for
             // the warp); those of a lane's classes differ, so at most one of them matches.
@@ -286,6 +288,26 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
                 lofs[t] += (uint32_t)p.LS * 4;
                 if (lofs[t] == stage_bytes) lofs[t] = 0;
             }
+        }
+
+        // TY <= 2: a rolled loop over the classes (the class's sums picked by compares, not by
+        // indexing) keeps this at one more copy of the flush code.
+#pragma unroll 1
+        for (int te = 0; te < (kEndTrips > 0 ? 0 : TY); ++te) {
+            float vals[kTX];
+#pragma unroll
+            for (int j = 0; j < kTX; ++j) vals[j] = 0.f;
+#pragma unroll
+            for (int t = 0; t < TY; ++t) {
+                if (t == te) {
+#pragma unroll
+                    for (int j = 0; j < kTX; ++j) vals[j] = acc[t][j];
+                }
+            }
+            const int cyt = cy0 + p.SL * te;
+            const int sy = r1 > Hp - cyt ? cyt - Hp : cyt;
+            const bool has = lane_live && sy > -H && sy < H;
+            warp_flush(flush_scratch, vals, has, dst + (size_t)(sy + H - 1) * OW, cx0, W, Wp, pass, combine, lane);
         }
     }
 }
