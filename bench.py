@@ -390,6 +390,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the FFT-path and reference-GPU-kernel legs (short profiling runs)")
     ap.add_argument("--cpu-seconds", type=float, default=6.0)
     ap.add_argument("--only", default="", help="comma-separated subset of C1..C5 (profiling runs; "
                     "the default line always covers all five)")
@@ -607,7 +609,7 @@ def main():
                     "result_probe": checksum},
             "gpu_launches": int(launches),
         }
-        if world == 1:
+        if world == 1 and not args.no_extras:
             line["fft_path"] = fft_path_timings(xc, dev, stream, hbm_peak)
             for k, e in line["fft_path"].items():
                 e["direct_ms"] = per_ms_max[k]

@@ -33,28 +33,30 @@ namespace {
 
 constexpr int kThreads = 256;
 
-// ---- zero padding: (n, H, W) -> (n, 2H, 2W), data in the top-left corner (scatter.cu) -------
+// ---- zero padding: (n, H, W) -> (n, 2H, 2W), data in the top-left corner (scatter.cu).
+//      One warp per padded row at a time; a unit is 4 consecutive floats (VEC) or one.
 template<bool VEC>
 __global__ void __launch_bounds__(kThreads) fft_pad_kernel(const float* __restrict__ in, float* __restrict__ out,
-                                                           int H, int W, unsigned long long units) {
-    // one unit = 4 consecutive output floats (VEC) or one float
-    const int W2 = 2 * W;
-    const unsigned long long per_row = VEC ? (unsigned)(W2 / 4) : (unsigned)W2;
-    for (unsigned long long u = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; u < units;
-         u += (unsigned long long)gridDim.x * blockDim.x) {
-        const unsigned long long row = u / per_row;          // padded row over all matrices
-        const int xu = (int)(u - row * per_row);
-        const unsigned long long mat = row / (unsigned)(2 * H);
-        const int y = (int)(row - mat * (unsigned)(2 * H));
-        if (VEC) {
-            const int x = xu * 4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (y < H && x < W) v = __ldg(reinterpret_cast<const float4*>(in + (mat * H + y) * W + x));
-            reinterpret_cast<float4*>(out)[u] = v;
-        } else {
-            float v = 0.f;
-            if (y < H && xu < W) v = __ldg(in + (mat * H + y) * W + xu);
-            out[u] = v;
+                                                           int H, int W, unsigned long long rows_total) {
+    const unsigned per_row = VEC ? (unsigned)(2 * W / 4) : (unsigned)(2 * W);
+    const unsigned lane = threadIdx.x & 31;
+    const unsigned long long warps = (unsigned long long)gridDim.x * (kThreads / 32);
+    for (unsigned long long r = (unsigned long long)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); r < rows_total;
+         r += warps) {
+        const unsigned long long mat = r / (unsigned)(2 * H);
+        const int y = (int)(r - mat * (unsigned)(2 * H));
+        const float* src = in + (mat * H + y) * W;           // only read when y < H
+        float* dst = out + r * (2ull * W);
+        for (unsigned u = lane; u < per_row; u += 32) {
+            if (VEC) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (y < H && (int)(u * 4) < W) v = __ldg(reinterpret_cast<const float4*>(src + u * 4));
+                reinterpret_cast<float4*>(dst)[u] = v;
+            } else {
+                float v = 0.f;
+                if (y < H && (int)u < W) v = __ldg(src + u);
+                dst[u] = v;
+            }
         }
     }
 }
@@ -85,20 +87,27 @@ __global__ void __launch_bounds__(kThreads) fft_product_kernel(const float4* __r
 }
 
 // ---- unpack: raw (pairs, 2H, 2W) -> (pairs, 2H-1, 2W-1), shift (sy, sx) read from row
-//      sy mod 2H, column sx mod 2W, scaled by 1 / (4HW)  (fft_helpers.hpp:199-262) ------------
+//      sy mod 2H, column sx mod 2W, scaled by 1 / (4HW)  (fft_helpers.hpp:199-262).
+//      One warp per output row at a time (one division per row, none per element): the two
+//      halves of a row are two contiguous runs of the raw row.
 __global__ void __launch_bounds__(kThreads) fft_unpack_kernel(const float* __restrict__ raw, float* __restrict__ out,
-                                                              int H, int W, float scale, unsigned long long total) {
+                                                              int H, int W, float scale, unsigned long long rows_total) {
     const unsigned OW = 2 * W - 1, OH = 2 * H - 1;
-    for (unsigned long long o = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; o < total;
-         o += (unsigned long long)gridDim.x * blockDim.x) {
-        const unsigned long long orow = o / OW;
-        const unsigned ox = (unsigned)(o - orow * OW);
-        const unsigned long long pair = orow / OH;
-        const unsigned oy = (unsigned)(orow - pair * OH);
-        const int sy = (int)oy - (H - 1), sx = (int)ox - (W - 1);
+    const unsigned lane = threadIdx.x & 31;
+    const unsigned long long warps = (unsigned long long)gridDim.x * (kThreads / 32);
+    for (unsigned long long r = (unsigned long long)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); r < rows_total;
+         r += warps) {
+        const unsigned long long pair = r / OH;
+        const unsigned oy = (unsigned)(r - pair * OH);
+        const int sy = (int)oy - (H - 1);
         const unsigned ry = sy < 0 ? sy + 2 * H : sy;
-        const unsigned rx = sx < 0 ? sx + 2 * W : sx;
-        out[o] = __ldg(raw + (pair * (2ull * H) + ry) * (2ull * W) + rx) * scale;
+        const float* src = raw + (pair * (2ull * H) + ry) * (2ull * W);
+        float* dst = out + r * OW;
+        // ox < W-1: sx = ox-(W-1) < 0 -> column ox + W + 1; ox >= W-1: column ox - (W-1)
+        for (unsigned ox = lane; ox < OW; ox += 32) {
+            const unsigned rx = ox < (unsigned)(W - 1) ? ox + W + 1 : ox - (W - 1);
+            dst[ox] = __ldg(src + rx) * scale;
+        }
     }
 }
 
@@ -205,9 +214,10 @@ int fft_run(const float* left, const float* right, float* out, int H, int W, con
         const float* src = side == 0 ? left : right;
         const size_t n = side == 0 ? pm.n_left : n_right;
         float* dst = padded + (side == 0 ? 0 : (size_t)pm.n_left * real_mat);
-        const unsigned long long units = n * real_mat / (vec ? 4 : 1);
-        if (vec) fft_pad_kernel<true><<<grid_for(units, sm_count), kThreads, 0, stream>>>(src, dst, H, W, units);
-        else     fft_pad_kernel<false><<<grid_for(units, sm_count), kThreads, 0, stream>>>(src, dst, H, W, units);
+        const unsigned long long rows_total = (unsigned long long)n * 2ull * H;
+        const unsigned grid = grid_for(rows_total * 32, sm_count);
+        if (vec) fft_pad_kernel<true><<<grid, kThreads, 0, stream>>>(src, dst, H, W, rows_total);
+        else     fft_pad_kernel<false><<<grid, kThreads, 0, stream>>>(src, dst, H, W, rows_total);
         if (cuda_check(cudaGetLastError(), "fft_pad_kernel")) return 1;
     }
     *launches += 2;
@@ -238,9 +248,9 @@ int fft_run(const float* left, const float* right, float* out, int H, int W, con
 
     // 5. unpack to the direct path's layout
     if (!raw_result) {
-        const unsigned long long total = (unsigned long long)pairs * (2ull * H - 1) * (2ull * W - 1);
-        fft_unpack_kernel<<<grid_for(total, sm_count), kThreads, 0, stream>>>(raw, out, H, W,
-                                                                             1.0f / (4.0f * (float)H * (float)W), total);
+        const unsigned long long rows_total = (unsigned long long)pairs * (2ull * H - 1);
+        fft_unpack_kernel<<<grid_for(rows_total * 32, sm_count), kThreads, 0, stream>>>(
+            raw, out, H, W, 1.0f / (4.0f * (float)H * (float)W), rows_total);
         if (cuda_check(cudaGetLastError(), "fft_unpack_kernel")) return 1;
         *launches += 1;
     }
