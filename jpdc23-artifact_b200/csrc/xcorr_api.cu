@@ -300,7 +300,11 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const double rs = (double)H / S;
                     const double macs_per_block = (double)p.threads * rs * p.Wp * TY * kTX;
                     const double busiest = std::ceil(tasks * S / dev.sm_count);
-                    const double t_rate = busiest * (macs_per_block / rate * (rs + 0.25) / rs + t_stage);
+                    // issue slots of the output flushes (about 110 instructions each: SL * TY wrap
+                    // flushes and TY final ones per pass) relative to the FFMA of a warp's slice
+                    const double flush_share = 2.0 * (std::min<double>(p.SL * TY, rs) + TY) * 110.0 /
+                                               (rs * p.Wp * TY * kTX);
+                    const double t_rate = busiest * (macs_per_block / rate * ((rs + 0.25) / rs + flush_share) + t_stage);
                     // A lone warp is bound by latency, not by the SM's FFMA rate: per right row its
                     // FFMAs one per clock plus ~150 cycles of row overhead per pass and ~40 per
                     // chunk visit, ~500 cycles per output flush (SL * TY wrap flushes and TY final
