@@ -353,8 +353,11 @@ def test_gpu_devices_option_shards_without_changing_results(cross, tmp_path):
         r = run(cross, "run", "--devices", nd, "-o", tmp_path / f"o{nd}.csv",
                 "nai_shuffle_multirow_both_multimat_both_n_to_m", tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
         assert r.returncode == 0, r.stderr
-        outs.append(open(tmp_path / f"o{nd}.csv").read())
-    assert all(o == outs[0] for o in outs)
+        outs.append(read_matrices(tmp_path / f"o{nd}.csv"))
+    # automatic plans depend on the shard's matrix counts, so sums may be taken in another order
+    for o in outs:
+        assert o.shape == outs[0].shape
+        assert np.abs(o - outs[0]).max() <= 2e-6 * np.abs(outs[0]).max() + 1.1e-6
     r = run(cross, "run", "--devices", 99, "nai_orig_n_to_m", tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
     assert r.returncode == 2 and "--devices" in r.stderr
 
