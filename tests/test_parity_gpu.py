@@ -448,3 +448,27 @@ def test_fft_kernel_family_through_the_common_entry_points(xc, oracle, mode, nl,
     ndev = torch.cuda.device_count()
     sharded = xc.run_host(mode, left, right, fft, devices=[i % ndev for i in range(2)])
     assert rel_err(sharded, want) <= REL_TOL
+
+
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [("one_to_one", 512, 512, 1, 1), ("one_to_one", 300, 700, 1, 1),
+                                                  ("one_to_many", 128, 128, 1, 64), ("n_to_m", 96, 80, 6, 10)])
+def test_direct_and_fft_paths_agree_at_sizes_beyond_the_oracle(xc, mode, rows, cols, nl, nr):
+    """Sizes the CPU oracle would take minutes for: the direct kernels and the cuFFT path are two
+    independent computations of the same definition (different algorithm, different summation
+    order) and must agree to float rounding; plus the sums the definition fixes in closed form."""
+    left, right = seeded_inputs(rows, cols, nl, nr, 900 + rows)
+    direct = gpu_run(xc, mode, left, right).astype(np.float64)
+    fft = fft_run(xc, mode, left, right).astype(np.float64)
+    assert not np.isnan(direct).any() and not np.isnan(fft).any()
+    scale = np.abs(direct).max()
+    assert np.abs(direct - fft).max() <= 2e-5 * scale, xc.last_launch()
+    # sum over all shifts of one pair = (sum of left) * (sum of right); centre = plain dot product
+    l64, r64 = left.astype(np.float64), right.astype(np.float64)
+    pairs = [(0, 0)] if mode == "one_to_one" else [(0, 0), (0, nr - 1)] if mode == "one_to_many" else \
+            [(0, 0), (nl - 1, nr - 1)]
+    for l, r in pairs:
+        idx = r if mode != "n_to_m" else l * nr + r
+        want_sum = l64[l].sum() * r64[r].sum()
+        assert abs(direct[idx].sum() - want_sum) <= 1e-6 * abs(want_sum)
+        want_centre = (l64[l] * r64[r]).sum()
+        assert abs(direct[idx, rows - 1, cols - 1] - want_centre) <= 1e-5 * scale
