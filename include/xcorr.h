@@ -295,6 +295,13 @@ XCORR_API const char* xcorr_status_string(int32_t status);
 XCORR_API uint64_t xcorr_launch_count(void);
 XCORR_API void xcorr_reset_launch_count(void);
 
+/* Health of the current device as this library sees it: synchronises the device, then returns
+ * XCORR_ERR_CUDA if an earlier launch failed, XCORR_ERR_TIMEOUT if any bounded device-side
+ * wait of the library's kernels gave up since the library was loaded (the results of such a
+ * launch are invalid; the count is in xcorr_last_error_string()), else XCORR_OK.  Stands in
+ * for the CUCH(cudaDeviceSynchronize()); CUCH(cudaGetLastError()) pair of main.cpp:267-270. */
+XCORR_API xcorr_status xcorr_check_device(void);
+
 /* Measured FP32 FFMA throughput of the current device in FLOP/s: a dependency-free
  * register-only FFMA kernel on every SM, timed with CUDA events on `stream`
  * (synchronises).  The denominator for "fraction of FFMA peak". */

@@ -115,6 +115,7 @@ def lib() -> C.CDLL:
     L.xcorr_fft_workspace_bytes.argtypes = [i32, u32, u32, u32, u32, i32]
     L.xcorr_fft_workspace_bytes.restype = sz
     L.xcorr_fft_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, i32, vp, sz, vp]
+    L.xcorr_check_device.argtypes = []
     L.xcorr_fft_release_plans.argtypes = []
     L.xcorr_fft_release_plans.restype = None
     _lib = L
@@ -162,6 +163,11 @@ def run_device(mode, d_left: int, d_right: int, d_out: int, rows: int, cols: int
     check(lib().xcorr_run_f32(_mode(mode), d_left, d_right, d_out, rows, cols, n_left, n_right,
                               C.byref(hints) if hints is not None else None,
                               d_workspace or None, workspace_bytes_, stream or None))
+
+
+def check_device() -> None:
+    """Synchronise and raise if a launch failed or a bounded device-side wait gave up."""
+    check(lib().xcorr_check_device())
 
 
 FFT_LAYOUTS = {"normalized": 0, "raw": 1}

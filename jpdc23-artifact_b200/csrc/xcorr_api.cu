@@ -782,6 +782,17 @@ xcorr_status xcorr_fft_f32(int32_t mode, const float* d_left, const float* d_rig
 
 void xcorr_fft_release_plans(void) { fft_release_plans(); }
 
+xcorr_status xcorr_check_device(void) {
+    XC_CUDA(cudaDeviceSynchronize());
+    XC_CUDA(cudaGetLastError());
+    unsigned timeouts = 0;
+    XC_CUDA(tile_stage_timeouts(&timeouts));
+    if (timeouts != 0)
+        return fail(XCORR_ERR_TIMEOUT, std::to_string(timeouts) + " bounded staging wait(s) of tile_kernel gave up; "
+                    "results of those launches are invalid");
+    return XCORR_OK;
+}
+
 size_t xcorr_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                              const xcorr_hints* hints) {
     PairMap pm{};

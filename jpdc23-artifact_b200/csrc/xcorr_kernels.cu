@@ -64,6 +64,41 @@ __device__ __forceinline__ void stage_wait() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
+// ---- bulk staging (TMA, non-tensor form): whole rows / whole row blocks of a matrix go
+// global -> shared as one cp.async.bulk each, completion counted in bytes on an mbarrier.
+// Used when rows need no column padding (cols a multiple of 16) and the operands are 16-byte
+// aligned; everything else takes the 16-byte cp.async path above.
+// Waits on the mbarrier are bounded: after kStageWaitLimit polls the block counts a timeout in
+// g_stage_timeouts (read by the host through tile_stage_timeouts()), polls once more with the
+// same bound so that its own copies can land, and carries on to its end without hanging.
+__device__ unsigned g_stage_timeouts = 0;
+constexpr unsigned kStageWaitLimit = 1u << 22;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const float* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
+    unsigned ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        for (unsigned it = 0; it < kStageWaitLimit; ++it)
+            if (mbar_poll(bar, parity)) return;
+        if (attempt == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_stage_timeouts, 1u);
+    }
+}
+
 // Load the N4*4 floats at `addr` into w[FIRST ...].
 template<int FIRST, int N4, int LEN>
 __device__ __forceinline__ void window_load(float (&w)[LEN], uint32_t addr) {
@@ -359,6 +394,14 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         reinterpret_cast<char*>(sR + (size_t)p.ML * p.RMS) + (size_t)warp * kFlushBytesPerWarp);
     int* queue = reinterpret_cast<int*>(reinterpret_cast<char*>(sR + (size_t)p.ML * p.RMS) +
                                         (size_t)(nthr >> 5) * kFlushBytesPerWarp);
+    // bulk staging: rows without column padding, 16-byte aligned operands
+    const bool bulk = a.vec_ok && W == Wp;
+    const uint32_t stage_bar = (uint32_t)__cvta_generic_to_shared(queue) + 8;
+    uint32_t stage_parity = 0;
+    if (bulk) {
+        if (tid == 0) mbar_init(stage_bar);
+        __syncthreads();
+    }
 
     while (u < uend) {
         int r0, r1, bx, by, rg, l, combine, q_first = 0, q_count = 0;
@@ -392,6 +435,58 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
 
         // ---- stage the left rows: staged row i holds left row (rowbase + i) mod Hp, zeros
         //      where the padded matrix is zero.
+        if (bulk) {
+            const float* gL = a.left + (size_t)l * H * W;
+            const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);
+            const int rs = r1 - r0;
+            const uint32_t row_bytes = (uint32_t)W * 4, mat_bytes = (uint32_t)(rs * W) * 4;
+            if (warp == 0) {
+                // one lane announces the bytes, all lanes of the warp issue the copies: staged
+                // left rows first, then one copy per right matrix (its rows r0..r1-1 are contiguous)
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                uint32_t bytes = 0;
+                for (int i = lane; i < nstage + p.ML; i += 32) {
+                    if (i < nstage) {
+                        int row = rowbase + i;
+                        if (row >= Hp) row -= Hp;
+                        if (row < H) bytes += row_bytes;
+                    } else if ((unsigned)rg * p.ML + (i - nstage) < a.pm.m) {
+                        bytes += mat_bytes;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
+                if (lane == 0) mbar_expect(stage_bar, bytes);
+                __syncwarp();
+                for (int i = lane; i < nstage + p.ML; i += 32) {
+                    if (i < nstage) {
+                        int row = rowbase + i;
+                        if (row >= Hp) row -= Hp;
+                        if (row < H) bulk_copy(sL_addr + (uint32_t)(i * p.LS) * 4, gL + (size_t)row * W, row_bytes, stage_bar);
+                    } else {
+                        const int mm = i - nstage;
+                        const unsigned j = (unsigned)rg * p.ML + mm;
+                        if (j < a.pm.m) {
+                            const size_t rmat = (size_t)l * a.pm.right_stride + j;
+                            bulk_copy(sR_addr + (uint32_t)(mm * p.RMS) * 4, a.right + (rmat * H + r0) * W, mat_bytes, stage_bar);
+                        }
+                    }
+                }
+            }
+            // rows and matrices of the zero padding: plain stores, one warp per row / matrix
+            const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int i = warp; i < nstage; i += nthr >> 5) {
+                int row = rowbase + i;
+                if (row >= Hp) row -= Hp;
+                if (row >= H)
+                    for (int x = lane * 4; x < Wp; x += 128) *reinterpret_cast<float4*>(sL + (size_t)i * p.LS + x) = zero4;
+            }
+            for (int mm = warp; mm < p.ML; mm += nthr >> 5)
+                if ((unsigned)rg * p.ML + mm >= a.pm.m)
+                    for (int x = lane * 4; x < rs * Wp; x += 128) *reinterpret_cast<float4*>(sR + (size_t)mm * p.RMS + x) = zero4;
+            mbar_wait_bounded(stage_bar, stage_parity);
+            stage_parity ^= 1u;
+        } else {
         {
             const float* gL = a.left + (size_t)l * H * W;
             const int units = p.LS >> 2;             // float4 per staged row (last one is padding)
@@ -447,6 +542,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             }
         }
         stage_wait();
+        }
         if (p.schedule == kSchedWarpQueue && tid == 0) *queue = 0;
         __syncthreads();
 
@@ -679,6 +775,10 @@ cudaError_t launch_warp_per_overlap(const float* left, const float* right, float
 // all calls (calls that overlap on one GPU would race on it).
 constexpr size_t kNoAllocScratchFloats = (size_t)8 << 20;            // 32 MiB
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+cudaError_t tile_stage_timeouts(unsigned* count) {
+    return cudaMemcpyFromSymbol(count, g_stage_timeouts, sizeof(unsigned));
+}
 
 size_t noalloc_scratch_bytes() { return kNoAllocScratchFloats * sizeof(float); }
 

@@ -15,6 +15,9 @@ cudaError_t launch_overlap_wise(const float* left, const float* right, float* ou
 cudaError_t launch_warp_per_overlap(const float* left, const float* right, float* out, int H, int W,
                                     PairMap pm, unsigned long long npairs, int block_threads,
                                     int sm_count, dim3* grid_out, dim3* block_out, cudaStream_t stream);
+// Number of bounded staging waits of the tile kernel that gave up on the current device since
+// the library was loaded (0 in every healthy run); synchronises with the device.
+cudaError_t tile_stage_timeouts(unsigned* count);
 cudaError_t launch_ffma_probe(float* sink, int iters, int blocks, cudaStream_t stream);
 
 // Built-in scratch of the entry point that allocates nothing: size, and the array's device

@@ -472,3 +472,31 @@ def test_direct_and_fft_paths_agree_at_sizes_beyond_the_oracle(xc, mode, rows, c
         assert abs(direct[idx].sum() - want_sum) <= 1e-6 * abs(want_sum)
         want_centre = (l64[l] * r64[r]).sum()
         assert abs(direct[idx, rows - 1, cols - 1] - want_centre) <= 1e-5 * scale
+
+
+def test_bulk_and_element_staging_give_identical_results(xc):
+    """Rows without column padding (cols a multiple of 16) on 16-byte aligned operands are staged
+    with bulk copies counted on an mbarrier; operands off that alignment take the element-wise
+    path.  Same arithmetic, so the results are bit-identical."""
+    rows, cols, nr = 48, 32, 21
+    left, right = seeded_inputs(rows, cols, 1, nr, 314)
+    hints = xc.make_hints(kernel="tile", overlap_rows=2, class_lanes=4, warps_x=2, warps_y=2, row_slices=1, schedule=1)
+    stream = torch.cuda.current_stream().cuda_stream
+    outs = []
+    for shift in (0, 1):                      # element offset of the operands: 0 -> aligned, 1 -> 4 bytes off
+        bl = torch.zeros(left.size + 8, dtype=torch.float32, device="cuda")
+        br = torch.zeros(right.size + 8, dtype=torch.float32, device="cuda")
+        bl[shift:shift + left.size] = torch.from_numpy(left.ravel()).cuda()
+        br[shift:shift + right.size] = torch.from_numpy(right.ravel()).cuda()
+        out = torch.full(xc.out_shape("one_to_many", rows, cols, 1, nr), float("nan"), dtype=torch.float32, device="cuda")
+        xc.run_device("one_to_many", bl.data_ptr() + 4 * shift, br.data_ptr() + 4 * shift, out.data_ptr(), rows, cols,
+                      1, nr, hints, 0, 0, stream)
+        torch.cuda.synchronize()
+        outs.append(out.cpu().numpy())
+    assert not np.isnan(outs[0]).any()
+    assert np.array_equal(outs[0], outs[1])
+
+
+def test_device_health_after_all_launches(xc):
+    """No launch failed and no bounded device-side wait (bulk staging) gave up in this process."""
+    xc.check_device()
