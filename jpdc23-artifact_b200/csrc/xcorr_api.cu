@@ -172,7 +172,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
 
     const double out_bytes = (double)pm.n_left * pm.m * (2.0 * H - 1) * (2.0 * W - 1) * 4.0;
     // measured: 2, 3 and 4 y classes per thread run the inner loop about equally fast
-    static const double ty_eff[5] = {0.0, 0.55, 0.95, 1.0, 1.0};
+    static const double ty_eff[5] = {0.0, 0.55, 0.98, 1.0, 1.0};
 
     for (int TY = 1; TY <= kMaxTY; ++TY) {
         if (want_ty && TY != want_ty) continue;
@@ -250,7 +250,10 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 const int warps_blk = p.threads / 32;
                 const double block_prior = warps_blk >= 12 ? 1.0 : warps_blk >= 8 ? 0.93 : warps_blk >= 4 ? 0.87 : 0.8;
                 const double lanes_prior = p.ML >= 8 ? 1.0 : p.ML == 4 ? 0.96 : p.ML == 2 ? 0.92 : 0.9;
-                const double rate = sm_rate * occ_eff * smem_eff * block_prior * lanes_prior;
+                // blocks of more than 384 threads run the 128-register build, which spills for
+                // TY = 4 (and a little for TY = 3): measured 28 against 47 TFLOP/s on 64 x 64 x 512
+                const double build_eff = p.threads > kSmallBlockThreads ? (TY == 4 ? 0.6 : TY == 3 ? 0.9 : 1.0) : 1.0;
+                const double rate = sm_rate * occ_eff * smem_eff * block_prior * lanes_prior * build_eff;
                 // filling the staging buffers: bytes over ~64 B/clk from L2 plus a latency
                 // chain, paid once per block (per segment / phase)
                 const double t_stage = ((double)p.smem_bytes / 64.0 + 2000.0) / 1.9e9;
@@ -282,17 +285,26 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const double macs_per_row = (double)p.threads * p.Wp * TY * kTX;
                     // every block: its rows, plus a fixed cost per segment (staging, flush)
                     const double segments = rows_per_block / H + 1.0;
+                    const double sk_flush_share = segments * 2.0 * (std::min<double>(p.SL * TY, rows_per_block) + TY) *
+                                                  110.0 / (rows_per_block * p.Wp * TY * kTX);
+                    // measured on 48 x 48 x 2048: with several segments per block the 3-class tile
+                    // loses 6 % to the 2-class one (0.476 against 0.447 ms), unlike in static plans
+                    const double sk_tile_prior = TY >= 3 ? 0.94 : 1.0;
                     const double t_rate = std::ceil(G / dev.sm_count) * ((rows_per_block + 0.25 * segments) *
-                                          macs_per_row / rate + segments * t_stage);
+                                          macs_per_row / (rate * sk_tile_prior) * (1.0 + sk_flush_share) + segments * t_stage);
                     // the lone-warp latency bound of the static branch, per segment
                     const double sk_flushes = 2.0 * (std::min<double>(p.SL * TY, rows_per_block) + TY) * segments;
                     const double sk_row_cycles = 300.0 + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
                     const double t_serial = (rows_per_block * sk_row_cycles + sk_flushes * 500.0 +
                                              4000.0 * segments) / 1.9e9;
-                    const double split_share = std::min(1.0, 2.0 * G / tasks);   // outputs added atomically
+                    // every block boundary splits one task; a split task is added atomically twice
+                    // (measured on B200 with the coalesced flush: ~3.4 TB/s of atomic traffic, the
+                    // memset of the output ~5 TB/s)
+                    const double split_share = std::min(1.0, G / tasks);
                     // more than two parts of a task do not commute: last bits then vary run to run
-                    const double order_penalty = tasks >= G ? 1.0 : 1.03;
-                    t = (std::max(t_rate, t_serial) + 5e-6 + out_bytes / 3e12 + split_share * 2.3 * out_bytes / 0.4e12) *
+                    // (a price put on reproducibility: such a plan must win by a clear margin)
+                    const double order_penalty = rows_per_block >= H ? 1.0 : 1.06;
+                    t = (std::max(t_rate, t_serial) + 5e-6 + out_bytes / 5e12 + split_share * 2.0 * out_bytes / 3.4e12) *
                         order_penalty;
                     comb = kAtomic;
                 } else {

@@ -328,6 +328,7 @@ def test_ffma_probe_reports_a_plausible_peak(xc):
 @pytest.mark.parametrize("mode,rows,cols,nl,nr", [
     ("one_to_one", 16, 16, 1, 1), ("one_to_one", 64, 64, 1, 1), ("one_to_one", 24, 24, 1, 1),
     ("one_to_many", 32, 32, 1, 24), ("one_to_many", 48, 48, 1, 9), ("n_to_mn", 24, 24, 3, 12),
+    ("n_to_m", 32, 32, 8, 8), ("n_to_m", 16, 16, 4, 12),
 ])
 def test_reference_cuda_kernels_agree(xc, oracle, mode, rows, cols, nl, nr):
     """Where the reference's CUDA kernels were compiled for this GPU (oracle/Makefile, target
@@ -339,6 +340,8 @@ def test_reference_cuda_kernels_agree(xc, oracle, mode, rows, cols, nl, nr):
     if not pyoracle.ReferenceCuda.available():
         pytest.skip("oracle/_ref/libxcorr_refcuda.so not built")
     rc = pyoracle.ReferenceCuda()
+    if mode == "n_to_m" and rc.n2m is None:
+        pytest.skip("oracle/_ref/libxcorr_refcuda_n2m.so not built")
     left, right = seeded_inputs(rows, cols, nl, nr, 77)
     want = oracle_grouped(oracle, mode, left, right)
     ours = gpu_run(xc, mode, left, right)
@@ -349,6 +352,8 @@ def test_reference_cuda_kernels_agree(xc, oracle, mode, rows, cols, nl, nr):
         rc.one_to_one(dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols)
     elif mode == "one_to_many":
         rc.one_to_many(dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols, nr)
+    elif mode == "n_to_m":
+        rc.n_to_m(dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols, nl, nr)
     else:
         rc.n_to_mn(dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols, nl, nr)
     torch.cuda.synchronize()
