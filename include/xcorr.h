@@ -107,10 +107,14 @@ typedef struct xcorr_hints {
                                   1 static: one block per block task (and row slice);
                                   2 stream-K: the (block task, right row) units of all tasks are cut evenly
                                     over one resident wave of blocks; a block works on whole tasks (plain
-                                    stores) and at most two partial ones (atomic adds onto the zeroed
-                                    output).  A task that ends up in more than two parts makes the last
-                                    bits of a result vary between runs, as with the reference's atomicAdd
-                                    "work distribution" kernels;
+                                    stores) and at most two partial ones, which it adds atomically onto
+                                    the zeroed output.  Two parts of a task commute; a task in more than
+                                    two parts makes the last bits of a result vary between runs, as with
+                                    the reference's atomicAdd "work distribution" kernels.  With
+                                    combine = workspace the parts go to partial images instead and the
+                                    block that finishes a task's last part sums them in the fixed order of
+                                    their rows: bit-reproducible for any number of parts, a few percent
+                                    slower;
                                   3 warp queue: the warp tasks (one 16-wide x tile and one y group of one
                                     matrix group, all rows) are cut evenly over one resident wave of
                                     blocks whose warps take them from a shared counter: plain stores,

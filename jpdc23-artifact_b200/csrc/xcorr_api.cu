@@ -136,6 +136,11 @@ void finish_plan(TilePlan& p, const PairMap& pm) {
                    (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;   // + the warp queue's counter
 }
 
+// Workspace of a stream-K plan with fix-up: `pieces` partial images, then one counter per task.
+size_t fixup_counters_offset(int pieces, unsigned long long total_out) {
+    return ((size_t)pieces * total_out * sizeof(float) + 255) / 256 * 256;
+}
+
 // Per-shape plan of the tile kernel: micro-tile height, lane split, block shape and how the
 // right rows are divided -- none (one block per task, plain stores), S equal slices per task
 // (partials combined by atomics or through the workspace) or stream-K (the (task, row)
@@ -161,9 +166,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
     const int want_sched = h ? h->schedule : 0;
     if (want_sched < 0 || want_sched > 3)
         return fail(XCORR_ERR_INVALID_HINT, "schedule must be 0 (auto), 1 (static), 2 (stream-K) or 3 (warp queue)");
-    if (want_sched == kSchedStreamK &&
-        (want_s > 1 || want_combine == XCORR_COMBINE_STORE || want_combine == XCORR_COMBINE_WORKSPACE))
-        return fail(XCORR_ERR_INVALID_HINT, "schedule=2 (stream-K) excludes row_slices > 1 and combine=store/workspace");
+    if (want_sched == kSchedStreamK && (want_s > 1 || want_combine == XCORR_COMBINE_STORE))
+        return fail(XCORR_ERR_INVALID_HINT, "schedule=2 (stream-K) excludes row_slices > 1 and combine=store");
     if (want_sched == kSchedWarpQueue &&
         (want_s > 1 || want_combine == XCORR_COMBINE_ATOMIC || want_combine == XCORR_COMBINE_WORKSPACE))
         return fail(XCORR_ERR_INVALID_HINT, "schedule=3 (warp queue) writes with plain stores: no row_slices, no atomic/workspace");
@@ -188,7 +192,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
             std::vector<Cand> cands;
             const bool static_ok = want_sched == 0 || want_sched == kSchedStatic;
             const bool streamk_ok = (want_sched == 0 || want_sched == kSchedStreamK) && want_s <= 1 &&
-                                    want_combine != XCORR_COMBINE_STORE && want_combine != XCORR_COMBINE_WORKSPACE;
+                                    want_combine != XCORR_COMBINE_STORE &&
+                                    !(want_sched == 0 && want_combine == XCORR_COMBINE_WORKSPACE);
             // The warp queue is only taken on request: measured on B200 it loses to the static
             // schedule on every benchmark shape, because a warp task cannot be shared and a warp
             // is bound to one of the SM's four schedulers, so its balance is no finer than the
@@ -259,6 +264,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 const double t_stage = ((double)p.smem_bytes / 64.0 + 2000.0) / 1.9e9;
                 double t;
                 int comb;
+                int sk_parts = 0;
                 unsigned grid;
                 if (c.sched == kSchedWarpQueue) {
                     const double per_group = (double)p.NGY * p.NTX;
@@ -304,9 +310,34 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     // more than two parts of a task do not commute: last bits then vary run to run
                     // (a price put on reproducibility: such a plan must win by a clear margin)
                     const double order_penalty = rows_per_block >= H ? 1.0 : 1.06;
-                    t = (std::max(t_rate, t_serial) + 5e-6 + out_bytes / 5e12 + split_share * 2.0 * out_bytes / 3.4e12) *
-                        order_penalty;
-                    comb = kAtomic;
+                    // most parts any task is cut into: a task of H rows over ranges of at least rpb rows
+                    const double rpb = std::floor(units / G);
+                    const int parts = (int)((H - 1) / std::max(1.0, rpb)) + 2;
+                    // Only on request (combine = workspace): measured on B200 the sum of the parts by
+                    // the last block to finish a task sits at the end of that block's work and costs
+                    // more than zeroing the output and adding atomically (64 x 64 x 512: 0.387 against
+                    // 0.366 ms; 48 x 48 x 2048: 0.483 against 0.448 ms).  What it buys is results that
+                    // are bit-reproducible however many parts a task is cut into.
+                    const bool fixup = want_combine == XCORR_COMBINE_WORKSPACE &&
+                                       (double)parts * out_bytes + tasks * 4.0 + 64.0 <= (double)max_workspace_bytes;
+                    if (fixup) {
+                        // parts go to partial images with plain stores and are summed in a fixed order by
+                        // the block that finishes the task last: two more writes and two reads of a cut
+                        // task's results, mostly from L2, under the other blocks' arithmetic
+                        // ... and the sum itself is latency-bound: a warp takes two result rows per
+                        // round of ~600 cycles per four parts; a block finishes about G/tasks tasks
+                        const double fix_rows = (double)p.ML * p.WY * p.SL * TY * 2.0;
+                        const double t_fix = std::min(1.0, tasks / G) * std::max(1.0, G / tasks) *
+                                             std::ceil(fix_rows / (2.0 * warps_blk)) * std::ceil(parts / 4.0) * 600.0 / 1.9e9;
+                        t = std::max(t_rate, t_serial) + 3e-6 + split_share * 4.0 * out_bytes / 5e12 + t_fix;
+                        comb = kFixup;
+                        sk_parts = parts;
+                    } else {
+                        t = (std::max(t_rate, t_serial) + 5e-6 + out_bytes / 5e12 + split_share * 2.0 * out_bytes / 3.4e12) *
+                            order_penalty;
+                        comb = kAtomic;
+                        sk_parts = 0;
+                    }
                 } else {
                     const int S = c.S;
                     const double rs = (double)H / S;
@@ -338,6 +369,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     best_time = t;
                     best = p;
                     best.combine = comb;
+                    best.pieces = sk_parts;
                     best.grid = grid;
                     best.tasks = (unsigned)tasks;
                 }
@@ -349,7 +381,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
 
     const unsigned long long total_out = (unsigned long long)pm.n_left * pm.m *
                                          (2ull * H - 1) * (2ull * W - 1);
-    best.workspace_bytes = best.combine == kWorkspace ? (size_t)best.S * total_out * sizeof(float) : 0;
+    best.workspace_bytes = best.combine == kWorkspace ? (size_t)best.S * total_out * sizeof(float) :
+                           best.combine == kFixup ? fixup_counters_offset(best.pieces, total_out) + (size_t)best.tasks * 4 : 0;
     *out = best;
     return XCORR_OK;
 }
@@ -424,7 +457,7 @@ std::string describe_plan(const TilePlan& p) {
                   p.CX, p.CY, p.RG, p.S,
                   p.schedule == kSchedStatic ? "static" : p.schedule == kSchedStreamK ? "stream-k" : "warp-queue",
                   p.tasks, p.nstage,
-                  p.combine == kStore ? "store" : p.combine == kAtomic ? "atomic" : "workspace",
+                  p.combine == kStore ? "store" : p.combine == kAtomic ? "atomic" : p.combine == kFixup ? "fixup" : "workspace",
                   p.workspace_bytes);
     return buf;
 }
@@ -473,7 +506,7 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
     TilePlan p{};
     st = plan_tile(pm, H, W, hints, dev, &p);
     if (st != XCORR_OK) return st;
-    if (p.combine == kWorkspace) {
+    if (p.combine == kWorkspace || p.combine == kFixup) {
         const bool explicit_ws = hints && hints->combine == XCORR_COMBINE_WORKSPACE;
         if (!d_ws || ws_bytes < p.workspace_bytes) {
             if (explicit_ws)
@@ -487,7 +520,12 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
     }
     TileArgs a{};
     a.left = d_left; a.right = d_right; a.out = d_out;
-    a.ws = p.combine == kWorkspace ? static_cast<float*>(d_ws) : nullptr;
+    a.ws = (p.combine == kWorkspace || p.combine == kFixup) ? static_cast<float*>(d_ws) : nullptr;
+    a.counters = nullptr;
+    if (p.combine == kFixup) {
+        a.counters = reinterpret_cast<unsigned*>(static_cast<char*>(d_ws) + fixup_counters_offset(p.pieces, total_out));
+        XC_CUDA(cudaMemsetAsync(a.counters, 0, (size_t)p.tasks * sizeof(unsigned), stream));
+    }
     a.p = p; a.pm = pm; a.total_out = total_out;
     a.vec_ok = (W % 4 == 0) && reinterpret_cast<uintptr_t>(d_left) % 16 == 0 &&
                reinterpret_cast<uintptr_t>(d_right) % 16 == 0;

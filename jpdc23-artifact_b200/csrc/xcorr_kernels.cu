@@ -347,6 +347,107 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
     }
 }
 
+// Stream-K with fix-up: sum the parts of one block task, in the order of their rows, into the
+// output.  Part k of the task covers right rows [e_k, e_k+1) (the cuts of the blocks' ranges);
+// it has written the unwrapped-in-y row of class c iff e_k < Hp - c and the wrapped one iff
+// e_k+1 > Hp - c, both x variants each.  One warp per pair of output rows of the task, lanes over
+// their columns; the parts are read with L2 loads (other SMs wrote them during this launch),
+// up to four parts of up to eight elements in flight per lane: the sum is latency-bound.
+struct FixupTask {            // passed by value: a reference to the kernel's parameters would
+    const float* ws;          // force a copy of them onto the stack of every thread
+    float* out;
+    unsigned long long total_out;
+    int H, W, Hp, Wp, ML, WX;
+    unsigned tasks, m;
+    unsigned task_id, first_block;
+    int l, rg, by, bx, n_parts, cls_per_block;
+};
+
+__device__ __noinline__ void fixup_finalize(const FixupTask f) {
+    const int H = f.H, W = f.W, Hp = f.Hp, Wp = f.Wp;
+    const int l = f.l, rg = f.rg, by = f.by, bx = f.bx, n_parts = f.n_parts, cls_per_block = f.cls_per_block;
+    const unsigned first_block = f.first_block;
+    const int OW = 2 * W - 1, OH = 2 * H - 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const unsigned long long total = (unsigned long long)f.tasks * H;
+    const unsigned long long task_u = (unsigned long long)f.task_id * H;
+    const int cya = by * cls_per_block;
+    const int xw = f.WX * kTX;                    // x classes of the block
+    constexpr int kRows = 2, kSlots = 4, kParts = 4, kCuts = 9;
+    const int rows_total = f.ML * cls_per_block * 2;
+    // row cuts of the first parts, once (64-bit divisions); tasks in more parts recompute them
+    int cut[kCuts];
+#pragma unroll
+    for (int k = 0; k < kCuts; ++k)
+        cut[k] = k == 0 ? 0 : k >= n_parts ? H : (int)(total * (first_block + k) / gridDim.x - task_u);
+    for (int rbase = warp * kRows; rbase < rows_total; rbase += nwarps * kRows) {
+        size_t row_off[kRows];
+        int k_lo[kRows], k_hi[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int rid = rbase + r;
+            k_lo[r] = 0; k_hi[r] = -1; row_off[r] = 0;
+            if (rid >= rows_total) continue;
+            const int mm = rid / (cls_per_block * 2);
+            const int rem = rid - mm * cls_per_block * 2;
+            const int c = cya + (rem >> 1);
+            const int wrapped = rem & 1;
+            const unsigned j = (unsigned)rg * f.ML + mm;
+            const int sy = wrapped ? c - Hp : c;
+            if (j >= f.m || c >= Hp || sy <= -H || sy >= H) continue;
+            int lo = n_parts, hi = -1;            // parts that wrote this row: a run lo .. hi
+            if (n_parts < kCuts) {
+#pragma unroll
+                for (int k = 0; k < kCuts - 1; ++k)
+                    if (k < n_parts && (wrapped ? cut[k + 1] > Hp - c : cut[k] < Hp - c)) { lo = min(lo, k); hi = max(hi, k); }
+            } else {
+                for (int k = 0; k < n_parts; ++k) {
+                    const long long e0 = k == 0 ? 0 : (long long)(total * (first_block + k) / gridDim.x - task_u);
+                    const long long e1 = k == n_parts - 1 ? H : (long long)(total * (first_block + k + 1) / gridDim.x - task_u);
+                    if (wrapped ? e1 > Hp - c : e0 < Hp - c) { lo = min(lo, k); hi = max(hi, k); }
+                }
+            }
+            k_lo[r] = lo; k_hi[r] = hi;
+            row_off[r] = ((size_t)l * f.m + j) * (size_t)OH * OW + (size_t)(sy + H - 1) * OW;
+        }
+        for (int x0 = 0; x0 < 2 * xw; x0 += 32 * kSlots) {
+            int col[kSlots];
+#pragma unroll
+            for (int sl = 0; sl < kSlots; ++sl) {
+                const int xi = x0 + sl * 32 + lane;
+                const int xv = xi >= xw;
+                const int cx = bx * xw + (xv ? xi - xw : xi);
+                const int cc = xv ? cx - Wp + W - 1 : cx + W - 1;
+                col[sl] = (xi < 2 * xw && cx < Wp && (xv ? cc >= 0 : cx < W)) ? cc : -1;
+            }
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                float sum[kSlots];
+#pragma unroll
+                for (int sl = 0; sl < kSlots; ++sl) sum[sl] = 0.f;
+                for (int kb = k_lo[r]; kb <= k_hi[r]; kb += kParts) {
+                    float v[kParts][kSlots];
+#pragma unroll
+                    for (int kk = 0; kk < kParts; ++kk)
+#pragma unroll
+                        for (int sl = 0; sl < kSlots; ++sl)
+                            v[kk][sl] = (kb + kk <= k_hi[r] && col[sl] >= 0)
+                                ? __ldcg(f.ws + (size_t)(kb + kk) * f.total_out + row_off[r] + col[sl]) : 0.f;
+#pragma unroll
+                    for (int kk = 0; kk < kParts; ++kk)
+#pragma unroll
+                        for (int sl = 0; sl < kSlots; ++sl) sum[sl] += v[kk][sl];
+                }
+                if (k_hi[r] >= k_lo[r]) {
+#pragma unroll
+                    for (int sl = 0; sl < kSlots; ++sl)
+                        if (col[sl] >= 0) f.out[row_off[r] + col[sl]] = sum[sl];
+                }
+            }
+        }
+    }
+}
+
 // BOUND = 384: blocks of up to 12 warps, up to 168 registers per thread (nothing of the hot
 // loop spills for TY = 4); BOUND = 512: blocks of 13..16 warps at 128 registers.
 template<int TY, int BOUND>
@@ -405,6 +506,8 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
 
     while (u < uend) {
         int r0, r1, bx, by, rg, l, combine, q_first = 0, q_count = 0;
+        unsigned task_id = 0, first_block = 0;
+        int n_parts = 1, part = 0;
         if (p.schedule == kSchedWarpQueue) {
             const unsigned group = (unsigned)(u / (unsigned)tasks_per_group);
             q_first = (int)(u - (unsigned long long)group * tasks_per_group);
@@ -416,6 +519,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             combine = kStore;
         } else {
             unsigned task = (unsigned)(u / (unsigned)H);
+            task_id = task;
             r0 = (int)(u - (unsigned long long)task * H);
             r1 = (int)min((unsigned long long)H, r0 + (uend - u));
             u += (unsigned)(r1 - r0);
@@ -425,6 +529,15 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             l = task / p.RG;
             // a whole task is written with plain stores, a part of one is added to the zeroed output
             combine = p.schedule == kSchedStreamK ? ((r0 == 0 && r1 == H) ? (int)kStore : (int)kAtomic) : p.combine;
+            if (p.schedule == kSchedStreamK && p.combine == kFixup && combine == kAtomic) {
+                // which blocks share this task: block b owns units [total*b/G, total*(b+1)/G)
+                const unsigned long long total = (unsigned long long)p.tasks * H;
+                const unsigned long long t0 = (unsigned long long)task_id * H;
+                first_block = (unsigned)(((t0 + 1) * gridDim.x - 1) / total);
+                n_parts = (int)(((t0 + H) * gridDim.x - 1) / total) - (int)first_block + 1;
+                part = (int)blockIdx.x - (int)first_block;
+                combine = kFixup;
+            }
         }
 
         // y classes the staged left rows must serve: the block's groups, or all in queue mode
@@ -569,15 +682,32 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             const int cx0 = tile_x * kTX;
             const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
             const size_t out_mat = (size_t)l * a.pm.m + jright;
-            float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out : a.out)
+            float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out :
+                          combine == kFixup ? a.ws + (size_t)part * a.total_out : a.out)
                          + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
-            tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live, combine,
-                            flush_scratch, lane, cls_per_block);
+            tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live,
+                            combine == kFixup ? (int)kStore : combine, flush_scratch, lane, cls_per_block);
             if (p.schedule == kSchedWarpQueue) {
                 if (lane == 0) item = atomicAdd(queue, 1);
                 item = __shfl_sync(0xffffffffu, item, 0);
             } else {
                 item = 1;
+            }
+        }
+        if (combine == kFixup) {
+            // this part is written: count it; whoever counts the task's last part sums them
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) *queue = atomicAdd(a.counters + task_id, 1u) + 1u == (unsigned)n_parts ? 1 : 0;
+            __syncthreads();
+            if (*queue) {
+                __threadfence();
+                FixupTask f;
+                f.ws = a.ws; f.out = a.out; f.total_out = a.total_out;
+                f.H = H; f.W = W; f.Hp = Hp; f.Wp = Wp; f.ML = p.ML; f.WX = p.WX;
+                f.tasks = p.tasks; f.m = a.pm.m; f.task_id = task_id; f.first_block = first_block;
+                f.l = l; f.rg = rg; f.by = by; f.bx = bx; f.n_parts = n_parts; f.cls_per_block = cls_per_block;
+                fixup_finalize(f);
             }
         }
         __syncthreads();                          // the next segment reuses the staging buffers

@@ -27,7 +27,9 @@ constexpr int kSmemLimit = 227 * 1024;
 // per-warp staging area of the output flush: 32 rows of kTX + 1 floats and 32 row addresses
 constexpr int kFlushBytesPerWarp = 32 * (kTX + 1) * 4 + 32 * 8;
 
-enum Combine : int { kStore = 1, kAtomic = 2, kWorkspace = 3 };
+// kFixup (stream-K only): a part of a task is stored to its own partial image; the block that
+// finishes a task's last outstanding part sums the parts in their fixed order into the output.
+enum Combine : int { kStore = 1, kAtomic = 2, kWorkspace = 3, kFixup = 4 };
 enum Schedule : int { kSchedStatic = 1, kSchedStreamK = 2, kSchedWarpQueue = 3 };
 
 // How the pairs of a mode are enumerated: left l in [0, n_left) meets rights
@@ -61,6 +63,7 @@ struct TilePlan {
     int RMS;           // floats between the staged right matrices of one block
     int threads;
     int combine;       // Combine
+    int pieces;        // kFixup: most parts any task is cut into (partial images in the workspace)
     unsigned grid;
     size_t smem_bytes;
     size_t workspace_bytes;
@@ -71,7 +74,8 @@ struct TileArgs {
     const float* left;
     const float* right;
     float* out;
-    float* ws;         // partial images, S * total_out floats (kWorkspace) or nullptr
+    float* ws;         // partial images: S (kWorkspace) or p.pieces (kFixup) * total_out floats, or nullptr
+    unsigned* counters;  // kFixup: one zeroed counter per block task (finished parts)
     TilePlan p;
     PairMap pm;
     int vec_ok;        // rows may be fetched with 16-byte loads

@@ -86,9 +86,12 @@ def test_workspace_planning_without_a_device(xc):
     big = xc.workspace_bytes("one_to_one", 256, 256, 1, 1)
     out_bytes = 511 * 511 * 4
     assert big > 0 and big % out_bytes == 0 and 8 <= big // out_bytes <= 64
-    # many independent pairs fill the GPU without a row split or with two slices: no workspace
+    # many independent pairs fill the GPU without a row split, or with atomics: no workspace
     assert xc.workspace_bytes("one_to_many", 64, 64, 1, 512) == 0
     assert xc.workspace_bytes("n_to_m", 32, 32, 32, 64) == 0
+    # stream-K with partial images on request: two or three result-sized images and the counters
+    sk = xc.workspace_bytes("one_to_many", 64, 64, 1, 512, xc.make_hints(kernel="tile", schedule=2, combine="workspace"))
+    assert 2 * 512 * 127 * 127 * 4 <= sk <= 3 * 512 * 127 * 127 * 4 + 65536
     # explicit hints
     h = xc.make_hints(kernel="tile", combine="workspace", row_slices=4)
     assert xc.workspace_bytes("one_to_one", 16, 16, 1, 1, h) == 4 * 31 * 31 * 4

@@ -108,6 +108,10 @@ TILE_VARIANTS = [
     dict(schedule=2, overlap_rows=2, class_lanes=8, warps_x=1, warps_y=2),
     dict(schedule=2, overlap_rows=4, class_lanes=2, warps_x=2, warps_y=1),
     dict(schedule=1),
+    dict(schedule=2, combine="atomic"),
+    dict(schedule=2, combine="workspace", overlap_rows=2, class_lanes=4, warps_x=1, warps_y=2),
+    dict(schedule=2, combine="workspace", overlap_rows=3, class_lanes=2, warps_x=2, warps_y=2),
+    dict(schedule=2, combine="workspace", overlap_rows=1, class_lanes=8, warps_x=1, warps_y=1),
     dict(schedule=3),
     dict(schedule=3, overlap_rows=2, class_lanes=4, warps_x=3, warps_y=1),
     dict(schedule=3, overlap_rows=4, class_lanes=16, warps_x=16, warps_y=1),
@@ -150,6 +154,34 @@ def test_workspace_plans_are_bit_reproducible(xc):
     assert np.array_equal(c[0], c[4])
 
 
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [("one_to_many", 64, 64, 1, 40), ("n_to_m", 32, 32, 6, 10),
+                                                  ("n_to_mn", 48, 48, 3, 36), ("one_to_one", 96, 80, 1, 1)])
+def test_stream_k_with_fixup_is_exact_and_reproducible(xc, oracle, mode, rows, cols, nl, nr):
+    """Stream-K with partial images: a task cut into two, three or more parts is summed in the
+    fixed order of its rows by whichever block finishes last, so runs agree bit for bit, and a
+    forced small tile (many parts per task) still matches the oracle."""
+    left, right = seeded_inputs(rows, cols, nl, nr, 808)
+    want = oracle_grouped(oracle, mode, left, right)
+    for hints in (dict(schedule=2, combine="workspace"),
+                  dict(schedule=2, combine="workspace", overlap_rows=1, class_lanes=4, warps_x=1, warps_y=1),
+                  dict(schedule=2, combine="workspace", overlap_rows=2, class_lanes=8)):
+        h = xc.make_hints(kernel="tile", **hints)
+        try:
+            a = gpu_run(xc, mode, left, right, h)
+        except xc.XcorrError as e:
+            assert e.status == 6 and hints != dict(schedule=2, combine="workspace")   # forced tile too big for the shape
+            continue
+        assert "combine=fixup" in xc.last_launch(), xc.last_launch()
+        b = gpu_run(xc, mode, left, right, h)
+        assert not np.isnan(a).any(), xc.last_launch()
+        assert rel_err(a, want) <= REL_TOL, xc.last_launch()
+        assert np.array_equal(a, b), xc.last_launch()
+    # without a workspace the same hint-free stream-K plan falls back to atomic adds
+    c = gpu_run(xc, mode, left, right, xc.make_hints(kernel="tile", schedule=2), with_workspace=False)
+    assert "combine=atomic" in xc.last_launch()
+    assert rel_err(c, want) <= REL_TOL
+
+
 def test_missing_workspace_is_reported_or_replaced(xc, oracle):
     left, right = seeded_inputs(32, 32, 1, 1, 8)
     explicit = xc.make_hints(kernel="tile", combine="workspace", row_slices=4)
@@ -168,7 +200,7 @@ def test_invalid_hints_are_rejected(xc):
     for bad in (dict(overlap_rows=5), dict(class_lanes=3), dict(warps_x=5, warps_y=4), dict(row_slices=9),
                 dict(kernel=9), dict(kernel="overlap_wise", block_threads=100),
                 dict(combine="store", row_slices=2), dict(schedule=4), dict(schedule=2, row_slices=2),
-                dict(schedule=2, combine="workspace")):
+                dict(schedule=2, combine="store")):
         with pytest.raises(xc.XcorrError) as e:
             gpu_run(xc, "one_to_one", left, right, xc.make_hints(**bad))
         assert e.value.status == 3, bad
