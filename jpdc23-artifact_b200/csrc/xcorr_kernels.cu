@@ -450,7 +450,10 @@ __device__ __noinline__ void fixup_finalize(const FixupTask f) {
 
 // BOUND = 384: blocks of up to 12 warps, up to 168 registers per thread (nothing of the hot
 // loop spills for TY = 4); BOUND = 512: blocks of 13..16 warps at 128 registers.
-template<int TY, int BOUND>
+// FIXUP: the build that can write parts of a cut stream-K task to partial images and sum them
+// (combine = kFixup); kept apart because its extra code cost the other plans 1-2 % when it sat
+// in the same kernel.
+template<int TY, int BOUND, bool FIXUP>
 __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     extern __shared__ __align__(16) float smem[];
     const TilePlan& p = a.p;
@@ -529,7 +532,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             l = task / p.RG;
             // a whole task is written with plain stores, a part of one is added to the zeroed output
             combine = p.schedule == kSchedStreamK ? ((r0 == 0 && r1 == H) ? (int)kStore : (int)kAtomic) : p.combine;
-            if (p.schedule == kSchedStreamK && p.combine == kFixup && combine == kAtomic) {
+            if (FIXUP && p.schedule == kSchedStreamK && p.combine == kFixup && combine == kAtomic) {
                 // which blocks share this task: block b owns units [total*b/G, total*(b+1)/G)
                 const unsigned long long total = (unsigned long long)p.tasks * H;
                 const unsigned long long t0 = (unsigned long long)task_id * H;
@@ -683,10 +686,10 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
             const size_t out_mat = (size_t)l * a.pm.m + jright;
             float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out :
-                          combine == kFixup ? a.ws + (size_t)part * a.total_out : a.out)
+                          (FIXUP && combine == kFixup) ? a.ws + (size_t)part * a.total_out : a.out)
                          + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
             tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live,
-                            combine == kFixup ? (int)kStore : combine, flush_scratch, lane, cls_per_block);
+                            (FIXUP && combine == kFixup) ? (int)kStore : combine, flush_scratch, lane, cls_per_block);
             if (p.schedule == kSchedWarpQueue) {
                 if (lane == 0) item = atomicAdd(queue, 1);
                 item = __shfl_sync(0xffffffffu, item, 0);
@@ -694,7 +697,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 item = 1;
             }
         }
-        if (combine == kFixup) {
+        if (FIXUP && combine == kFixup) {
             // this part is written: count it; whoever counts the task's last part sums them
             __threadfence();
             __syncthreads();
@@ -828,12 +831,12 @@ __global__ void __launch_bounds__(1024) ffma_probe_kernel(float* sink, float b, 
 // ------------------------------------------------------------------------------------------
 template<int TY, int BOUND>
 static cudaError_t launch_tile_variant(const TileArgs& a, cudaStream_t stream) {
+    auto kernel = a.p.combine == kFixup ? tile_kernel<TY, BOUND, true> : tile_kernel<TY, BOUND, false>;
     if (a.p.smem_bytes > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(tile_kernel<TY, BOUND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)a.p.smem_bytes);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.p.smem_bytes);
         if (e != cudaSuccess) return e;
     }
-    tile_kernel<TY, BOUND><<<a.p.grid, a.p.threads, a.p.smem_bytes, stream>>>(a);
+    kernel<<<a.p.grid, a.p.threads, a.p.smem_bytes, stream>>>(a);
     return cudaGetLastError();
 }
 
