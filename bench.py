@@ -535,6 +535,8 @@ def main():
     checksum = float(host[last][2].reshape(-1)[0])   # a device result read on the host
     barrier()
 
+    xc.check_device()          # no failed launch, no bounded device-side wait that gave up
+
     # ---- FFMA peak of this GPU, measured now
     ffma_flops, _ = xc.ffma_peak_probe(stream)
 

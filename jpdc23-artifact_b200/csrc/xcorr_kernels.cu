@@ -1,10 +1,13 @@
 // Device code of the direct 2-D cross-correlation library (sm_100a).
 //
 // Three kernel families:
-//   tile_kernel<TY>        register-tiled circular-class kernel; the fast path for every
+//   tile_kernel<TY, BOUND, FIXUP>
+//                          register-tiled circular-class kernel; the fast path for every
 //                          mode.  Stands in for the reference's warp-shuffle families
 //                          (naive_shuffle*.cu): grouped-overlap, multi-matrix-right/both
-//                          and, with row slices, the split-row ("work distribution") ones.
+//                          and, with row slices or stream-K, the split-row ("work
+//                          distribution") ones.  Operands are staged with bulk copies
+//                          (cp.async.bulk + mbarrier) or 16-byte cp.async.
 //   overlap_wise_kernel    one thread per overlap (naive_original.cu:37-102).
 //   warp_per_overlap_kernel one warp per overlap (naive_warp_per_shift.cu:192-244).
 // plus the fixed-order reduction of workspace partials and the FFMA peak probe.

@@ -316,10 +316,10 @@ int command_run(const std::vector<std::string>& tokens, const std::string& prog)
             if (ret != 0) return ret;
         }
         if (spec->fam != family::cpu) {
-            cudaError_t e = cudaDeviceSynchronize();
-            if (e == cudaSuccess) e = cudaGetLastError();
-            if (e != cudaSuccess) {
-                std::cerr << "Exception somewhere in CUDA code: " << cudaGetErrorString(e)
+            // CUCH(cudaDeviceSynchronize()); CUCH(cudaGetLastError()) of main.cpp:267-270, plus the
+            // library's own device-side waits
+            if (xcorr_check_device() != XCORR_OK) {
+                std::cerr << "Exception somewhere in CUDA code: " << xcorr_last_error_string()
                           << "\nLast kernel launch arguments:\n" << xcorr_last_launch_string() << std::endl;
                 return 3;
             }
