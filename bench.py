@@ -330,6 +330,118 @@ def fft_path_timings(xc, dev, stream, hbm_peak, iters=20):
     return out
 
 
+# The reference's own benchmark grid (benchmark/benchmark.yml: groups one_to_one, one_to_many,
+# n_to_mn, n_to_m and their "saturated" variants), as rows x cols x left x right.
+GRID = {
+    "one_to_one": ["16x16x1x1", "24x24x1x1", "32x32x1x1", "48x48x1x1", "64x64x1x1", "96x96x1x1", "128x128x1x1",
+                   "192x192x1x1", "256x256x1x1"],
+    "one_to_many": ["16x16x1x2", "16x16x1x8", "16x16x1x32", "32x32x1x2", "32x32x1x8", "32x32x1x32", "64x64x1x2",
+                    "64x64x1x8", "64x64x1x32", "128x128x1x2", "128x128x1x8", "128x128x1x32", "256x256x1x2",
+                    "256x256x1x8", "256x256x1x32", "16x16x1x4000", "32x32x1x4000", "64x64x1x4000",
+                    "128x128x1x4000", "256x256x1x4000"],
+    "n_to_mn": ["16x16x2x8", "16x16x4x16", "16x16x8x32", "32x32x2x8", "32x32x4x16", "32x32x8x32", "64x64x2x8",
+                "64x64x4x16", "64x64x8x32", "128x128x2x8", "128x128x4x16", "128x128x8x32", "256x256x2x8",
+                "256x256x4x16", "256x256x8x32", "16x16x100x4000", "32x32x100x4000", "64x64x100x4000",
+                "128x128x100x4000", "256x256x100x4000"],
+    "n_to_m": ["16x16x2x2", "16x16x8x8", "16x16x32x32", "32x32x2x2", "32x32x8x8", "32x32x32x32", "64x64x2x2",
+               "64x64x8x8", "64x64x32x32", "128x128x2x2", "128x128x8x8", "128x128x32x32", "256x256x2x2",
+               "256x256x8x8", "256x256x32x32", "16x16x128x128", "32x32x128x128", "64x64x128x128",
+               "128x128x128x128"],
+}
+
+
+def run_grid(args):
+    """`bench.py --grid`: every size of the reference's benchmark file on one GPU -- the direct
+    kernels (automatic plan), the cuFFT path and, where oracle/_ref holds them, the reference's
+    own best CUDA kernels -- resident inputs, CUDA events, one JSON line.  Sizes above
+    --grid-max-tflop of arithmetic are skipped (the reference kernels above a fifth of that)."""
+    import torch
+    xc = load_package()
+    xc.lib()
+    torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import pyoracle
+    rc = pyoracle.ReferenceCuda() if pyoracle.ReferenceCuda.available() else None
+    side = [torch.cuda.Stream() for _ in range(8)]
+    legacy = torch.cuda.default_stream()
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+
+    def timed(fn, flop, on=None):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(on)
+        fn()
+        b.record(on)
+        torch.cuda.synchronize()
+        once = max(a.elapsed_time(b), 1e-3)
+        n = int(min(200, max(3, 30.0 / once)))
+        a.record(on)
+        for _ in range(n):
+            fn()
+        b.record(on)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    rows_out = []
+    for mode, sizes in GRID.items():
+        for size in sizes:
+            r, c, nl, nr = (int(v) for v in size.split("x"))
+            pairs = pairs_of(mode, nl, nr)
+            flop = 2.0 * pairs * r * r * c * c
+            entry = {"mode": mode, "size": size, "gflop": flop / 1e9}
+            if flop > args.grid_max_tflop * 1e12:
+                entry["skipped"] = "above --grid-max-tflop"
+                rows_out.append(entry)
+                continue
+            left = torch.rand((nl, r, c), device="cuda", generator=gen)
+            right = torch.rand((nr, r, c), device="cuda", generator=gen)
+            out = torch.empty(xc.out_shape(mode, r, c, nl, nr), dtype=torch.float32, device="cuda")
+            L, R, O = left.data_ptr(), right.data_ptr(), out.data_ptr()
+            wsb = xc.workspace_bytes(mode, r, c, nl, nr)
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device="cuda")
+            ms = timed(lambda: xc.run_device(mode, L, R, O, r, c, nl, nr, None, ws.data_ptr() if wsb else 0, wsb, stream), flop)
+            entry.update(direct_ms=ms, direct_gflops=flop / ms / 1e6, plan=xc.last_launch().split(" plan{")[0])
+            direct = out.clone()
+            fwsb = xc.fft_workspace_bytes(mode, r, c, nl, nr)
+            fws = torch.empty(fwsb + 256, dtype=torch.uint8, device="cuda")
+            fbase = (fws.data_ptr() + 255) // 256 * 256
+            fms = timed(lambda: xc.run_fft_device(mode, L, R, O, r, c, nl, nr, "normalized", fbase, fwsb, stream), flop)
+            entry.update(fft_ms=fms, fft_vs_direct=float((out - direct).abs().max() / direct.abs().max()))
+            del fws
+            if rc is not None and flop <= 0.2 * args.grid_max_tflop * 1e12 and not (mode == "n_to_m" and rc.n2m is None):
+                def ref():
+                    if mode == "one_to_one":
+                        rc.one_to_one(L, R, O, r, c)
+                    elif mode == "one_to_many":
+                        rc.one_to_many(L, R, O, r, c, nr)
+                    elif mode == "n_to_m":
+                        rc.n_to_m(L, R, O, r, c, nl, nr)
+                    else:
+                        start = torch.cuda.Event()
+                        start.record(legacy)
+                        for s_ in side:
+                            s_.wait_event(start)
+                        rc.n_to_mn(L, R, O, r, c, nl, nr, streams=[s_.cuda_stream for s_ in side])
+                        for s_ in side:
+                            e = torch.cuda.Event()
+                            e.record(s_)
+                            legacy.wait_event(e)
+                torch.cuda.synchronize()
+                rms = timed(ref, flop, legacy)
+                entry.update(reference_ms=rms, speedup=rms / ms,
+                             reference_vs_direct=float((out - direct).abs().max() / direct.abs().max()))
+            rows_out.append(entry)
+            del left, right, out, direct, ws
+            torch.cuda.empty_cache()
+    xc.check_device()
+    print(json.dumps({"grid": rows_out, "reference_args": {"one_to_one": "4_8_8", "one_to_many": "4_4_4_4",
+                                                            "n_to_mn": "4_4_4_4", "n_to_m": "4_4_4_4_4"}}))
+    return 0
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -393,6 +505,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the FFT-path and reference-GPU-kernel legs (short profiling runs)")
     ap.add_argument("--cpu-seconds", type=float, default=6.0)
+    ap.add_argument("--grid", action="store_true",
+                    help="run the sizes of the reference's benchmark file instead of the headline step")
+    ap.add_argument("--grid-max-tflop", type=float, default=40.0)
     ap.add_argument("--only", default="", help="comma-separated subset of C1..C5 (profiling runs; "
                     "the default line always covers all five)")
     ap.add_argument("--hints", default="", help='JSON {"C3": {"overlap_rows": 4, ...}}: force plan hints of '
@@ -407,6 +522,8 @@ def main():
             raise SystemExit("--only selected no configuration")
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.grid:
+        return run_grid(args)
 
     import torch
     import torch.distributed as dist
