@@ -114,3 +114,28 @@ def test_argument_errors_come_back_as_status_codes(xc):
     assert lib.xcorr_run_host_sharded_f32(1, p, p, p, 4, 4, 1, 2, None, None, 0) == 7
     assert lib.xcorr_n_to_mn_reorder_f32(None, p, 1, 1, 1, 1) == 1
     assert lib.xcorr_ffma_peak_probe(None, None, None) == 1
+
+
+def test_plans_exist_and_fit_for_a_sweep_of_shapes(xc):
+    """The planner needs no device: for a sweep of modes, sizes and counts every automatic plan
+    exists, fits one SM's shared memory, has a non-empty grid, and the workspace query agrees
+    with the plan text."""
+    import re
+    rng = np.random.default_rng(7)
+    shapes = [(1, 1), (2, 3), (5, 5), (16, 16), (17, 33), (31, 64), (48, 48), (64, 64), (100, 9), (96, 128),
+              (200, 200), (256, 256), (300, 40), (512, 512)]
+    for rows, cols in shapes:
+        for mode, nl, nr in (("one_to_one", 1, 1), ("one_to_many", 1, int(rng.integers(1, 600))),
+                             ("n_to_mn", 3, 3 * int(rng.integers(1, 40))), ("n_to_m", int(rng.integers(1, 20)), int(rng.integers(1, 70)))):
+            text = xc.describe_plan(mode, rows, cols, nl, nr)
+            m = re.search(r"grid=\((\d+),1,1\) block=\((\d+),1,1\) smem=(\d+) plan\{H=(\d+) W=(\d+) Hp=(\d+) Wp=(\d+) SL=(\d+) "
+                          r"ML=(\d+) WX=(\d+) WY=(\d+) .* S=(\d+) schedule=([a-z-]+) tasks=(\d+) nstage=(\d+) "
+                          r"combine=([a-z]+) workspace=(\d+)\}", text)
+            assert m, text
+            grid, block, smem, H, W, Hp, Wp, SL, ML, WX, WY, S = (int(v) for v in m.groups()[:12])
+            sched, tasks, nstage, comb, ws = m.group(13), int(m.group(14)), int(m.group(15)), m.group(16), int(m.group(17))
+            assert (H, W) == (rows, cols) and Hp >= H and Wp >= W and Wp % 16 == 0 and SL * ML == 32, text
+            assert 1 <= grid and 32 <= block <= 512 and block == 32 * WX * WY and smem <= 227 * 1024, text
+            assert tasks >= 1 and nstage >= 1 and (S == 1 or sched == "static"), text
+            assert ws == xc.workspace_bytes(mode, rows, cols, nl, nr), text
+            assert (ws > 0) == (comb in ("workspace", "fixup")), text
