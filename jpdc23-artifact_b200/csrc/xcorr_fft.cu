@@ -41,21 +41,34 @@ __global__ void __launch_bounds__(kThreads) fft_pad_kernel(const float* __restri
     const unsigned per_row = VEC ? (unsigned)(2 * W / 4) : (unsigned)(2 * W);
     const unsigned lane = threadIdx.x & 31;
     const unsigned long long warps = (unsigned long long)gridDim.x * (kThreads / 32);
-    for (unsigned long long r = (unsigned long long)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); r < rows_total;
-         r += warps) {
-        const unsigned long long mat = r / (unsigned)(2 * H);
-        const int y = (int)(r - mat * (unsigned)(2 * H));
-        const float* src = in + (mat * H + y) * W;           // only read when y < H
-        float* dst = out + r * (2ull * W);
+    // four rows per trip, all loads before the stores: the kernel is bound by memory latency
+    // times the loads in flight, not by arithmetic
+    constexpr int kRows = 4;
+    for (unsigned long long r0 = ((unsigned long long)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * kRows;
+         r0 < rows_total; r0 += warps * kRows) {
         for (unsigned u = lane; u < per_row; u += 32) {
-            if (VEC) {
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (y < H && (int)(u * 4) < W) v = __ldg(reinterpret_cast<const float4*>(src + u * 4));
-                reinterpret_cast<float4*>(dst)[u] = v;
-            } else {
-                float v = 0.f;
-                if (y < H && (int)u < W) v = __ldg(src + u);
-                dst[u] = v;
+            float4 v4[kRows];
+            float v1[kRows];
+#pragma unroll
+            for (int i = 0; i < kRows; ++i) {
+                const unsigned long long r = r0 + i;
+                const unsigned long long mat = r / (unsigned)(2 * H);
+                const int y = (int)(r - mat * (unsigned)(2 * H));
+                const float* src = in + (mat * H + y) * W;       // only read when y < H
+                v4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                v1[i] = 0.f;
+                if (r < rows_total && y < H) {
+                    if (VEC) { if ((int)(u * 4) < W) v4[i] = __ldg(reinterpret_cast<const float4*>(src + u * 4)); }
+                    else if ((int)u < W) v1[i] = __ldg(src + u);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kRows; ++i) {
+                const unsigned long long r = r0 + i;
+                if (r >= rows_total) continue;
+                float* dst = out + r * (2ull * W);
+                if (VEC) reinterpret_cast<float4*>(dst)[u] = v4[i];
+                else dst[u] = v1[i];
             }
         }
     }
@@ -95,18 +108,38 @@ __global__ void __launch_bounds__(kThreads) fft_unpack_kernel(const float* __res
     const unsigned OW = 2 * W - 1, OH = 2 * H - 1;
     const unsigned lane = threadIdx.x & 31;
     const unsigned long long warps = (unsigned long long)gridDim.x * (kThreads / 32);
-    for (unsigned long long r = (unsigned long long)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); r < rows_total;
-         r += warps) {
-        const unsigned long long pair = r / OH;
-        const unsigned oy = (unsigned)(r - pair * OH);
-        const int sy = (int)oy - (H - 1);
-        const unsigned ry = sy < 0 ? sy + 2 * H : sy;
-        const float* src = raw + (pair * (2ull * H) + ry) * (2ull * W);
-        float* dst = out + r * OW;
+    constexpr int kRows = 2, kCols = 4;               // 8 loads in flight per lane
+    for (unsigned long long r0 = ((unsigned long long)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * kRows;
+         r0 < rows_total; r0 += warps * kRows) {
+        const float* src[kRows];
+#pragma unroll
+        for (int i = 0; i < kRows; ++i) {
+            const unsigned long long r = min(r0 + i, rows_total - 1);
+            const unsigned long long pair = r / OH;
+            const unsigned oy = (unsigned)(r - pair * OH);
+            const int sy = (int)oy - (H - 1);
+            const unsigned ry = sy < 0 ? sy + 2 * H : sy;
+            src[i] = raw + (pair * (2ull * H) + ry) * (2ull * W);
+        }
         // ox < W-1: sx = ox-(W-1) < 0 -> column ox + W + 1; ox >= W-1: column ox - (W-1)
-        for (unsigned ox = lane; ox < OW; ox += 32) {
-            const unsigned rx = ox < (unsigned)(W - 1) ? ox + W + 1 : ox - (W - 1);
-            dst[ox] = __ldg(src + rx) * scale;
+        for (unsigned x0 = lane; x0 < OW; x0 += 32 * kCols) {
+            float v[kRows][kCols];
+#pragma unroll
+            for (int i = 0; i < kRows; ++i)
+#pragma unroll
+                for (int j = 0; j < kCols; ++j) {
+                    const unsigned ox = x0 + 32 * j;
+                    const unsigned rx = ox < (unsigned)(W - 1) ? ox + W + 1 : ox - (W - 1);
+                    v[i][j] = ox < OW ? __ldg(src[i] + rx) : 0.f;
+                }
+#pragma unroll
+            for (int i = 0; i < kRows; ++i) {
+                if (r0 + i >= rows_total) continue;
+                float* dst = out + (r0 + i) * OW;
+#pragma unroll
+                for (int j = 0; j < kCols; ++j)
+                    if (x0 + 32 * j < OW) dst[x0 + 32 * j] = v[i][j] * scale;
+            }
         }
     }
 }
