@@ -215,6 +215,11 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const int s_lo = want_s ? want_s : 1;
                     const int s_hi = want_s ? want_s : std::min(H, 64);
                     for (int S = s_lo; S <= s_hi; ++S) cands.push_back({shape.first, shape.second, S, kSchedStatic});
+                    // wide matrices: a staged left row is several KB, so only short runs of rows
+                    // fit in shared memory -- finer slices, in steps of about 1.5x up to one row each
+                    if (!want_s)
+                        for (int S = 96; S / 3 * 2 < H; S = S * 3 / 2)
+                            if (std::min(S, H) > 64) cands.push_back({shape.first, shape.second, std::min(S, H), kSchedStatic});
                 }
                 if (streamk_ok) cands.push_back({shape.first, shape.second, 1, kSchedStreamK});
             }
@@ -357,7 +362,12 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const double row_cycles = 300.0 + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
                     const double t_serial = (rs * row_cycles + flushes * 500.0 + 4000.0) / 1.9e9;
                     comb = want_combine;
-                    if (comb == XCORR_COMBINE_AUTO) comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
+                    if (comb == XCORR_COMBINE_AUTO) {
+                        comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
+                        // partial images beyond a few GB (very fine slices of a large result): atomics
+                        if (comb == kWorkspace && (double)S * out_bytes > std::min((double)max_workspace_bytes, 4.0 * (1ull << 30)))
+                            comb = kAtomic;
+                    }
                     // a memset or a second kernel in front of / behind the main one costs a few us
                     double t_combine = 0.0;
                     if (comb == kAtomic) t_combine = 5e-6 + out_bytes / 3e12 + S * out_bytes / 0.4e12;
@@ -505,6 +515,18 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
 
     TilePlan p{};
     st = plan_tile(pm, H, W, hints, dev, &p);
+    if (st == XCORR_ERR_UNSUPPORTED && (!hints || hints->kernel == XCORR_KERNEL_AUTO)) {
+        // no tile plan fits in shared memory (rows of many thousands of columns): the automatic
+        // choice falls back to the overlap-wise kernel, which needs none -- slow, but every size
+        // the reference accepts is computed
+        dim3 g, b;
+        XC_CUDA(launch_overlap_wise(d_left, d_right, d_out, H, W, pm, npairs, 256, &g, &b, stream));
+        std::snprintf(buf, sizeof buf, "kernel=overlap_wise grid=(%u,%u,%u) block=(%u,%u,1) smem=0 (no tile plan fits)",
+                      g.x, g.y, g.z, b.x, b.y);
+        t_last_launch = buf;
+        ++t_launch_count;
+        return XCORR_OK;
+    }
     if (st != XCORR_OK) return st;
     if (p.combine == kWorkspace || p.combine == kFixup) {
         const bool explicit_ws = hints && hints->combine == XCORR_COMBINE_WORKSPACE;
@@ -881,8 +903,13 @@ int32_t xcorr_describe_plan(int32_t mode, uint32_t rows, uint32_t cols, uint32_t
         }
         TilePlan p{};
         st = plan_tile(pm, (int)rows, (int)cols, hints, dev, &p);
-        if (st != XCORR_OK) return st;
-        text = describe_plan(p);
+        if (st == XCORR_ERR_UNSUPPORTED && (!hints || hints->kernel == XCORR_KERNEL_AUTO)) {
+            text = "kernel=overlap_wise (no tile plan fits)";
+            st = XCORR_OK;
+        } else {
+            if (st != XCORR_OK) return st;
+            text = describe_plan(p);
+        }
     } else {
         return fail(XCORR_ERR_INVALID_HINT, "unknown kernel family");
     }

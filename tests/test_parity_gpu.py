@@ -488,7 +488,9 @@ def test_fft_kernel_family_through_the_common_entry_points(xc, oracle, mode, nl,
 
 
 @pytest.mark.parametrize("mode,rows,cols,nl,nr", [("one_to_one", 512, 512, 1, 1), ("one_to_one", 300, 700, 1, 1),
-                                                  ("one_to_many", 128, 128, 1, 64), ("n_to_m", 96, 80, 6, 10)])
+                                                  ("one_to_many", 128, 128, 1, 64), ("n_to_m", 96, 80, 6, 10),
+                                                  ("one_to_one", 1024, 1024, 1, 1), ("one_to_one", 5, 3000, 1, 1),
+                                                  ("one_to_many", 200, 8, 1, 50), ("n_to_mn", 33, 47, 5, 40)])
 def test_direct_and_fft_paths_agree_at_sizes_beyond_the_oracle(xc, mode, rows, cols, nl, nr):
     """Sizes the CPU oracle would take minutes for: the direct kernels and the cuFFT path are two
     independent computations of the same definition (different algorithm, different summation
