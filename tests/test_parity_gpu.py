@@ -539,3 +539,20 @@ def test_bulk_and_element_staging_give_identical_results(xc):
 def test_device_health_after_all_launches(xc):
     """No launch failed and no bounded device-side wait (bulk staging) gave up in this process."""
     xc.check_device()
+
+
+def test_rows_too_wide_for_the_tile_kernel_fall_back(xc, oracle):
+    """A staged left row of 6000 columns leaves no tile plan that fits one SM's shared memory:
+    the automatic choice runs the overlap-wise kernel instead (slow, any size); asking for the
+    tile kernel explicitly reports the shape as unsupported."""
+    left, right = seeded_inputs(6, 6000, 1, 1, 99)
+    want = oracle.run("one_to_one", left, right, acc64=True, threads=os.cpu_count() or 1)
+    got = gpu_run(xc, "one_to_one", left, right)
+    assert "overlap_wise" in xc.last_launch() and "no tile plan fits" in xc.last_launch()
+    assert rel_err(got, want) <= REL_TOL
+    assert xc.describe_plan("one_to_one", 6, 6000, 1, 1).startswith("kernel=overlap_wise")
+    with pytest.raises(xc.XcorrError) as e:
+        gpu_run(xc, "one_to_one", left, right, xc.make_hints(kernel="tile"))
+    assert e.value.status == 6
+    fft = fft_run(xc, "one_to_one", left, right)
+    assert rel_err(fft, want) <= REL_TOL
