@@ -123,7 +123,12 @@ typedef struct xcorr_hints {
                                   matrices are cut into so that the input copy, the kernel and the result
                                   copy of successive pieces overlap.  0 auto (by result size, 1..8);
                                   1 one piece (copy in, run, copy out) */
-    int32_t reserved[6];
+    int32_t reproducible;      /* TILE: 1 = only plans whose results are bit-identical from run to run (no
+                                  sum of more than two atomically added parts); 0 = the fastest plan, which
+                                  for small inputs may add many parts atomically, like the reference's
+                                  "work distribution" kernels.  The environment variable
+                                  XCORR_REPRODUCIBLE=1 sets it for every call of the process */
+    int32_t reserved[5];
 } xcorr_hints;
 
 /* ---- device-pointer entry points ------------------------------------------------------

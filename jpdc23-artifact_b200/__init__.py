@@ -42,12 +42,12 @@ class Hints(C.Structure):
         ("kernel", C.c_int32), ("combine", C.c_int32), ("overlap_rows", C.c_int32),
         ("class_lanes", C.c_int32), ("warps_x", C.c_int32), ("warps_y", C.c_int32),
         ("row_slices", C.c_int32), ("block_threads", C.c_int32), ("schedule", C.c_int32),
-        ("host_chunks", C.c_int32), ("reserved", C.c_int32 * 6),
+        ("host_chunks", C.c_int32), ("reproducible", C.c_int32), ("reserved", C.c_int32 * 5),
     ]
 
 
 def make_hints(kernel="auto", combine="auto", overlap_rows=0, class_lanes=0, warps_x=0, warps_y=0,
-               row_slices=0, block_threads=0, schedule=0, host_chunks=0) -> Hints:
+               row_slices=0, block_threads=0, schedule=0, host_chunks=0, reproducible=0) -> Hints:
     h = Hints()
     h.kernel = KERNELS[kernel] if isinstance(kernel, str) else int(kernel)
     h.combine = COMBINE[combine] if isinstance(combine, str) else int(combine)
@@ -55,6 +55,7 @@ def make_hints(kernel="auto", combine="auto", overlap_rows=0, class_lanes=0, war
     h.warps_x, h.warps_y, h.row_slices, h.block_threads = warps_x, warps_y, row_slices, block_threads
     h.schedule = schedule
     h.host_chunks = host_chunks
+    h.reproducible = reproducible
     return h
 
 

@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -174,6 +175,11 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
     if (want_combine == XCORR_COMBINE_STORE && want_s > 1)
         return fail(XCORR_ERR_INVALID_HINT, "combine=store needs row_slices=1");
 
+    static const bool env_reproducible = [] {
+        const char* e = std::getenv("XCORR_REPRODUCIBLE");
+        return e && e[0] == '1';
+    }();
+    const bool reproducible = env_reproducible || (h && h->reproducible == 1);
     const double out_bytes = (double)pm.n_left * pm.m * (2.0 * H - 1) * (2.0 * W - 1) * 4.0;
     // measured: 2, 3 and 4 y classes per thread run the inner loop about equally fast
     static const double ty_eff[5] = {0.0, 0.55, 0.98, 1.0, 1.0};
@@ -338,6 +344,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                         comb = kFixup;
                         sk_parts = parts;
                     } else {
+                        if (reproducible && parts > 2) continue;      // three or more atomic addends per result
                         t = (std::max(t_rate, t_serial) + 5e-6 + out_bytes / 5e12 + split_share * 2.0 * out_bytes / 3.4e12) *
                             order_penalty;
                         comb = kAtomic;
@@ -368,6 +375,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                         if (comb == kWorkspace && (double)S * out_bytes > std::min((double)max_workspace_bytes, 4.0 * (1ull << 30)))
                             comb = kAtomic;
                     }
+                    if (reproducible && comb == kAtomic && S > 2) continue;
                     // a memset or a second kernel in front of / behind the main one costs a few us
                     double t_combine = 0.0;
                     if (comb == kAtomic) t_combine = 5e-6 + out_bytes / 3e12 + S * out_bytes / 0.4e12;
@@ -426,7 +434,7 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
     k.n_left = pm.n_left; k.m = pm.m; k.right_stride = pm.right_stride; k.H = H; k.W = W;
     if (h) {
         k.hint[0] = h->overlap_rows; k.hint[1] = h->class_lanes; k.hint[2] = h->warps_x; k.hint[3] = h->warps_y;
-        k.hint[4] = h->row_slices;   k.hint[5] = h->combine;     k.hint[6] = h->schedule;
+        k.hint[4] = h->row_slices;   k.hint[5] = h->combine;     k.hint[6] = h->schedule + 16 * (h->reproducible == 1);
     }
     k.sm_count = dev.sm_count; k.smem_optin = dev.smem_optin; k.max_ws = max_workspace_bytes;
     {
@@ -534,6 +542,9 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
             if (explicit_ws)
                 return fail(XCORR_ERR_WORKSPACE, "combine=workspace needs xcorr_workspace_bytes() bytes of workspace");
             // automatic plan without (enough) workspace: fall back to atomics
+            if (hints && hints->reproducible == 1 && p.S > 2)
+                return fail(XCORR_ERR_WORKSPACE, "the reproducible plan of this shape sums partial images: "
+                            "it needs xcorr_workspace_bytes() bytes of workspace");
             p.combine = kAtomic;
             p.workspace_bytes = 0;
         } else if (reinterpret_cast<uintptr_t>(d_ws) % 16 != 0) {

@@ -235,6 +235,7 @@ algorithm::algorithm(const algorithm_spec& spec, const json_object& args, double
         hints_.warps_x = static_cast<int32_t>(args.value("warps_x", 0L));
         hints_.warps_y = static_cast<int32_t>(args.value("warps_y", 0L));
         hints_.row_slices = static_cast<int32_t>(args.value("row_slices", 0L));
+        hints_.reproducible = static_cast<int32_t>(args.value("reproducible", 0L));
         const std::string comb = args.value("combine", std::string("auto"));
         if (comb == "auto") hints_.combine = XCORR_COMBINE_AUTO;
         else if (comb == "store") hints_.combine = XCORR_COMBINE_STORE;

@@ -556,3 +556,19 @@ def test_rows_too_wide_for_the_tile_kernel_fall_back(xc, oracle):
     assert e.value.status == 6
     fft = fft_run(xc, "one_to_one", left, right)
     assert rel_err(fft, want) <= REL_TOL
+
+
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [("one_to_one", 16, 16, 1, 1), ("one_to_one", 64, 64, 1, 1),
+                                                  ("one_to_many", 32, 32, 1, 9), ("n_to_m", 24, 16, 3, 4),
+                                                  ("n_to_mn", 48, 48, 4, 64)])
+def test_reproducible_hint_gives_bit_identical_runs(xc, oracle, mode, rows, cols, nl, nr):
+    """hints.reproducible = 1 keeps the planner to plans without sums of three or more atomic
+    addends: repeated runs agree bit for bit (and still match the oracle)."""
+    left, right = seeded_inputs(rows, cols, nl, nr, 4242)
+    h = xc.make_hints(reproducible=1)
+    a = gpu_run(xc, mode, left, right, h)
+    plan = xc.last_launch()
+    assert "combine=store" in plan or "combine=workspace" in plan or "combine=fixup" in plan or "schedule=stream-k" in plan
+    for _ in range(3):
+        assert np.array_equal(a, gpu_run(xc, mode, left, right, h)), plan
+    assert rel_err(a, oracle_grouped(oracle, mode, left, right)) <= REL_TOL
