@@ -369,7 +369,7 @@ void algorithm::prepare() {
             result_ = matrix_array(2 * left_.rows(), 2 * left_.cols(), static_cast<dsize_t>(n_out), true);
         else
             result_ = matrix_array(2 * left_.rows() - 1, 2 * left_.cols() - 1, static_cast<dsize_t>(n_out), on_gpu());
-        if (!on_gpu()) return;
+        if (!on_gpu() || pipelined()) return;
         build_shards();
         for (auto& s : shards_) {
             CUCH(cudaSetDevice(s.device));
@@ -389,7 +389,7 @@ void algorithm::prepare() {
 
 void algorithm::transfer() {
     timed_step(2, true, [&] {
-        if (!on_gpu()) return;
+        if (!on_gpu() || pipelined()) return;
         for (auto& s : shards_) {
             CUCH(cudaSetDevice(s.device));
             CUCH(cudaMemcpyAsync(s.d_left, left_.data() + s.left_offset, s.left_elems * sizeof(float),
@@ -441,7 +441,17 @@ void algorithm::run_cpu() {
 
 void algorithm::run() {
     auto once = [&] {
-        if (on_gpu()) launch_all(); else run_cpu();
+        if (pipelined()) {
+            std::vector<int32_t> devs(devices_.begin(), devices_.end());
+            xcorr_check(xcorr_run_host_sharded_f32(spec_.mode, left_.data(), right_.data(), result_.data(),
+                                                   left_.rows(), left_.cols(), left_.num_matrices(),
+                                                   right_.num_matrices(), &hints_, devs.data(),
+                                                   static_cast<int32_t>(devs.size())));
+        } else if (on_gpu()) {
+            launch_all();
+        } else {
+            run_cpu();
+        }
     };
     if (measure_common()) {
         // CPU_ADAPTIVE_MEASURE(3, ..., gpu_sync = true, run_impl) -- cross_corr.hpp:50-54
@@ -490,7 +500,7 @@ void algorithm::run() {
 
 void algorithm::finalize() {
     timed_step(4, true, [&] {
-        if (!on_gpu()) return;
+        if (!on_gpu() || pipelined()) return;
         for (auto& s : shards_) {
             CUCH(cudaSetDevice(s.device));
             CUCH(cudaMemcpyAsync(result_.data() + s.out_offset, s.d_out, s.out_elems * sizeof(float),

@@ -90,6 +90,11 @@ public:
     // `cross run --normalize`: FFT algorithms deliver the direct path's result layout instead of
     // the raw inverse transforms (main.cpp:178-186); no effect on the other families.
     void set_normalize(bool on) { normalize_ = on; }
+    // `cross run --pipelined` (or XCORR_PIPELINED=1): the transfer / run / finalize steps become one
+    // call of the host-buffer entry point, which overlaps the copies of successive pieces of
+    // the result with the kernels; prepare and free then have nothing to do on the device.
+    // Not used in Algorithm mode (which times kernels alone) nor for raw FFT results.
+    void set_pipelined(bool on) { pipelined_ = on; }
 
     std::vector<std::string> measurement_labels() const;
     std::vector<measurement_result> measurements() const { return measurements_; }
@@ -124,6 +129,8 @@ private:
     std::vector<measurement_result> measurements_;
     long rows_per_thread_ = 0;       // explicit JSON value, 0 = not given
     bool normalize_ = false;
+    bool pipelined_ = false;
+    bool pipelined() const { return pipelined_ && on_gpu() && !measure_alg() && !raw_fft(); }
 
     bool raw_fft() const { return spec_.fam == family::fft && !normalize_; }
     validation_results validate_against(const matrix_array& result,

@@ -4,14 +4,15 @@
 //   cross [-h] list
 //   cross run [-d single] [-o out] [-t times] [-v [valid]] [-n] [-a] [-p]
 //             [-b None|Compute|CommonSteps|Algorithm] [-l outer_loops] [-m min_time_s]
-//             [--args_path json] [--devices N] <alg> <ref_path> <target_path>
+//             [--args_path json] [--devices N] [--pipelined] <alg> <ref_path> <target_path>
 //   cross validate [-n] [-c] [-p] <template_data_path> <validate_data_path...>
 //   cross input <alg_type> <rows> <columns> <left_matrices> <right_matrices>
 //
 // Exit codes: 0 ok; 1 bad options, unknown algorithm or bad algorithm argument (help is
 // printed); 2 any other exception; 3 an exception inside a computation step.
-// `--devices N` (or the environment variable XCORR_DEVICES) is the one addition: shard the
-// independent result matrices of the many-matrix modes over the first N GPUs.
+// Additions: `--devices N` (or the environment variable XCORR_DEVICES) shards the independent
+// result matrices of the many-matrix modes over the first N GPUs; `--pipelined` (or
+// XCORR_PIPELINED=1) runs transfer, kernels and copy-back as one overlapped call.
 #include <cuda_runtime.h>
 
 #include <cstdlib>
@@ -105,7 +106,7 @@ const std::vector<option_def> kRunOptions = {
     {"validate", 'v', true, true}, {"normalize", 'n', false, false}, {"append", 'a', false, false},
     {"no_progress", 'p', false, false}, {"benchmark_type", 'b', true, false},
     {"outer_loops", 'l', true, false}, {"min_time", 'm', true, false}, {"args_path", 0, true, false},
-    {"devices", 0, true, false}, {"help", 'h', false, false},
+    {"devices", 0, true, false}, {"pipelined", 0, false, false}, {"help", 'h', false, false},
 };
 const std::vector<option_def> kValidateOptions = {
     {"normalize", 'n', false, false}, {"csv", 'c', false, false}, {"print_header", 'p', false, false},
@@ -144,7 +145,8 @@ void print_help(std::ostream& out, const std::string& name) {
            "  -m [ --min_time ] arg (=1)            The minimum time to consider measurement statistically relevant, in\n"
            "                                        seconds\n"
            "  --args_path arg                       Path to the JSON file containing arguments for the algorithm\n"
-           "  --devices arg (=1)                    Number of GPUs to shard the many-matrix modes over\n";
+           "  --devices arg (=1)                    Number of GPUs to shard the many-matrix modes over\n"
+           "  --pipelined                           Transfer, run and copy back as one overlapped call (not in Algorithm mode)\n";
 }
 
 std::string join_sorted(const std::vector<std::string>& v) {
@@ -281,6 +283,10 @@ int command_run(const std::vector<std::string>& tokens, const std::string& prog)
     }
     algorithm alg(*spec, alg_args, min_time_s * 1e9, bench, devices);
     alg.set_normalize(a.has("normalize"));
+    {
+        const char* env = std::getenv("XCORR_PIPELINED");
+        alg.set_pipelined(a.has("pipelined") || (env && env[0] == '1'));
+    }
     if (spec->fam != family::cpu) {
         int have = 0;
         if (cudaGetDeviceCount(&have) != cudaSuccess || have == 0)

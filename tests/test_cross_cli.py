@@ -408,3 +408,30 @@ def test_fft_algorithms_raw_and_normalized_files(cross, oracle, tmp_path, alg, m
     r = run(cross, "validate", "--normalize", "-c", "-p", tmp_path / "valid.csv", tmp_path / "raw.csv")
     assert r.returncode == 0, r.stderr
     assert float(r.stdout.splitlines()[1].split(",")[0]) < 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("alg,mode,nl,nr", [("nai_shuffle_multirow_both_multimat_right_one_to_many", "one_to_many", 1, 40),
+                                            ("nai_shuffle_multirow_both_multimat_both_n_to_m", "n_to_m", 6, 7),
+                                            ("nai_shuffle_multirow_both_multimat_right_n_to_mn", "n_to_mn", 4, 12),
+                                            ("fft_orig_one_to_many", "one_to_many", 1, 9)])
+def test_pipelined_computation_steps(cross, oracle, tmp_path, alg, mode, nl, nr):
+    """--pipelined (or XCORR_PIPELINED=1): transfer, kernels and copy-back as one overlapped call
+    of the host-buffer entry point; same files, `Computation` timing in Compute mode."""
+    left, right = seeded_inputs(40, 48, nl, nr, 31)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    want = oracle.run(mode, left, right, acc64=True)
+    extra = ["--normalize"] if alg.startswith("fft") else []
+    r = run(cross, "run", "--pipelined", "-b", "Compute", "-m", "0.005", "-t", tmp_path / "t.csv", "-o", tmp_path / "o.csv",
+            *extra, alg, tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    got = read_matrices(tmp_path / "o.csv")
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max() + 5.1e-7
+    assert open(tmp_path / "t.csv").read().splitlines()[0].startswith("Computation,Computation_iterations")
+    env = dict(os.environ, XCORR_PIPELINED="1")
+    r = subprocess.run([cross, "run", "-o", str(tmp_path / "o2.csv"), *extra, alg, str(tmp_path / "l.csv"),
+                        str(tmp_path / "r.csv")], cwd=tmp_path, env=env, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert np.abs(read_matrices(tmp_path / "o2.csv") - want).max() <= 1e-5 * np.abs(want).max() + 5.1e-7
