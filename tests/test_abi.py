@@ -139,3 +139,27 @@ def test_plans_exist_and_fit_for_a_sweep_of_shapes(xc):
             assert tasks >= 1 and nstage >= 1 and (S == 1 or sched == "static"), text
             assert ws == xc.workspace_bytes(mode, rows, cols, nl, nr), text
             assert (ws > 0) == (comb in ("workspace", "fixup")), text
+
+
+def test_header_is_plain_c(xc, tmp_path):
+    """include/xcorr.h compiles as C99 with warnings on, and a C program links against the
+    library and calls a host-only entry point: the boundary is a C ABI, not a C++ one."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    src = tmp_path / "t.c"
+    src.write_text('#include <stdio.h>\n#include "xcorr.h"\n'
+                   'int main(void) { xcorr_hints h = {0}; unsigned first = 0, count = 0; (void)h;\n'
+                   '  xcorr_shard_range(10, 3, 1, &first, &count);\n'
+                   '  printf("%u %u %llu %s\\n", first, count, (unsigned long long)xcorr_num_results(XCORR_N_TO_M, 3, 4),\n'
+                   '         xcorr_status_string(XCORR_ERR_WORKSPACE)); return 0; }\n')
+    exe = tmp_path / "t"
+    inc = os.path.dirname(xc.HEADER_PATH)
+    libdir = os.path.dirname(xc.LIB_PATH)
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", f"-I{inc}", str(src), "-o", str(exe),
+                        f"-L{libdir}", "-lxcorr", f"-Wl,-rpath,{libdir}", "-Wl,-rpath,/usr/local/cuda/lib64"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.split()[:3] == ["3", "3", "12"], (r.stdout, r.stderr)
