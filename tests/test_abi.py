@@ -128,6 +128,11 @@ def test_plans_exist_and_fit_for_a_sweep_of_shapes(xc):
         for mode, nl, nr in (("one_to_one", 1, 1), ("one_to_many", 1, int(rng.integers(1, 600))),
                              ("n_to_mn", 3, 3 * int(rng.integers(1, 40))), ("n_to_m", int(rng.integers(1, 20)), int(rng.integers(1, 70)))):
             text = xc.describe_plan(mode, rows, cols, nl, nr)
+            if text == "kernel=warp_per_overlap":          # a handful of overlaps: one warp per overlap
+                assert nl * (nr if mode != "n_to_mn" else nr // nl) * (2 * rows - 1) * (2 * cols - 1) <= 1500 or \
+                    (mode == "n_to_mn" and nr * (2 * rows - 1) * (2 * cols - 1) <= 1500)
+                assert xc.workspace_bytes(mode, rows, cols, nl, nr) == 0
+                continue
             m = re.search(r"grid=\((\d+),1,1\) block=\((\d+),1,1\) smem=(\d+) plan\{H=(\d+) W=(\d+) Hp=(\d+) Wp=(\d+) SL=(\d+) "
                           r"ML=(\d+) WX=(\d+) WY=(\d+) .* S=(\d+) schedule=([a-z-]+) tasks=(\d+) nstage=(\d+) "
                           r"combine=([a-z]+) workspace=(\d+)\}", text)
