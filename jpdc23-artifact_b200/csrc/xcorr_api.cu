@@ -180,9 +180,23 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
         return e && e[0] == '1';
     }();
     const bool reproducible = env_reproducible || (h && h->reproducible == 1);
+    static const bool plan_debug = std::getenv("XCORR_PLAN_DEBUG") != nullptr;   // candidates and estimates to stderr
     const double out_bytes = (double)pm.n_left * pm.m * (2.0 * H - 1) * (2.0 * W - 1) * 4.0;
-    // measured: 2, 3 and 4 y classes per thread run the inner loop about equally fast
-    static const double ty_eff[5] = {0.0, 0.55, 0.98, 1.0, 1.0};
+    // Fitted to ~1500 timed plans over 19 shapes on B200: 1 and 2 y classes per thread run the
+    // inner loop about equally fast (the per-row cost below aside), 3 and 4 classes slower
+    // (register pressure; 64 x 64 x 512: 404 against 361 us).  Plans of 1 class win wherever their
+    // shorter warp tasks and fewer flushes per task matter: anything that does not fill the GPU
+    // many times over.
+    static const double ty_eff[5] = {0.0, 0.97, 0.98, 0.93, 0.85};
+    // issue slots one output flush costs, in FFMA-equivalents (fitted to measured plan timings)
+    const double kFlushSlots = 150.0;
+    // latency of a lone warp's row, besides its chunks (a 16 x 16 batch in one static block of 16
+    // rows: 14 us measured, against 10 us when the rows are spread over 16 blocks)
+    const double kRowBase = 550.0;
+    // issue slots of the per-row code of a warp (two passes: addresses, ranges, the first window),
+    // which weigh on narrow matrices and small tiles: 32 x 32, saturated, 1 class per thread runs
+    // 13..30 % slower than 2 classes; at 64 x 64 they are level
+    const double kRowSlots = 50.0;
 
     for (int TY = 1; TY <= kMaxTY; ++TY) {
         if (want_ty && TY != want_ty) continue;
@@ -238,7 +252,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 }
             }
 
-            const double sm_rate = 128.0 * 1.8e9 * 0.8 * ty_eff[TY];
+            const double sm_rate = 128.0 * 1.8e9 * 0.8;
             for (const Cand& c : cands) {
                 p.WX = c.WX; p.WY = c.WY; p.S = c.S; p.schedule = c.sched;
                 finish_plan(p, pm);
@@ -269,7 +283,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 // blocks of more than 384 threads run the 128-register build, which spills for
                 // TY = 4 (and a little for TY = 3): measured 28 against 47 TFLOP/s on 64 x 64 x 512
                 const double build_eff = p.threads > kSmallBlockThreads ? (TY == 4 ? 0.6 : TY == 3 ? 0.9 : 1.0) : 1.0;
-                const double rate = sm_rate * occ_eff * smem_eff * block_prior * lanes_prior * build_eff;
+                const double tile_eff = ty_eff[TY] / (1.0 + kRowSlots / ((double)p.Wp * TY * kTX));
+                const double rate = sm_rate * tile_eff * occ_eff * smem_eff * block_prior * lanes_prior * build_eff;
                 // filling the staging buffers: bytes over ~64 B/clk from L2 plus a latency
                 // chain, paid once per block (per segment / phase)
                 const double t_stage = ((double)p.smem_bytes / 64.0 + 2000.0) / 1.9e9;
@@ -303,15 +318,13 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     // every block: its rows, plus a fixed cost per segment (staging, flush)
                     const double segments = rows_per_block / H + 1.0;
                     const double sk_flush_share = segments * 2.0 * (std::min<double>(p.SL * TY, rows_per_block) + TY) *
-                                                  110.0 / (rows_per_block * p.Wp * TY * kTX);
-                    // measured on 48 x 48 x 2048: with several segments per block the 3-class tile
-                    // loses 6 % to the 2-class one (0.476 against 0.447 ms), unlike in static plans
-                    const double sk_tile_prior = TY >= 3 ? 0.94 : 1.0;
-                    const double t_rate = std::ceil(G / dev.sm_count) * ((rows_per_block + 0.25 * segments) *
-                                          macs_per_row / (rate * sk_tile_prior) * (1.0 + sk_flush_share) + segments * t_stage);
+                                                  kFlushSlots / (rows_per_block * p.Wp * TY * kTX);
+                    // (the staging of blocks resident together overlaps; their arithmetic shares the SM)
+                    const double t_rate = std::ceil(G / dev.sm_count) * (rows_per_block + 0.25 * segments) *
+                                          macs_per_row / rate * (1.0 + sk_flush_share) + segments * t_stage;
                     // the lone-warp latency bound of the static branch, per segment
                     const double sk_flushes = 2.0 * (std::min<double>(p.SL * TY, rows_per_block) + TY) * segments;
-                    const double sk_row_cycles = 300.0 + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
+                    const double sk_row_cycles = kRowBase + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
                     const double t_serial = (rows_per_block * sk_row_cycles + sk_flushes * 500.0 +
                                              4000.0 * segments) / 1.9e9;
                     // every block boundary splits one task; a split task is added atomically twice
@@ -319,8 +332,11 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     // memset of the output ~5 TB/s)
                     const double split_share = std::min(1.0, G / tasks);
                     // more than two parts of a task do not commute: last bits then vary run to run
-                    // (a price put on reproducibility: such a plan must win by a clear margin)
-                    const double order_penalty = rows_per_block >= H ? 1.0 : 1.06;
+                    // (a price put on reproducibility: such a plan must win by a clear margin).  Whole-task
+                    // plans still pay for zeroing and re-reading an output that is not in L2, which
+                    // the timings these constants were fitted to (same buffers replayed) do not show:
+                    // 64 x 64 x 512 from a cold cache, 0.373 ms against 0.367 ms of the static plan.
+                    const double order_penalty = rows_per_block >= H ? 1.03 : 1.06;
                     // most parts any task is cut into: a task of H rows over ranges of at least rpb rows
                     const double rpb = std::floor(units / G);
                     const int parts = (int)((H - 1) / std::max(1.0, rpb)) + 2;
@@ -355,18 +371,19 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const double rs = (double)H / S;
                     const double macs_per_block = (double)p.threads * rs * p.Wp * TY * kTX;
                     const double busiest = std::ceil(tasks * S / dev.sm_count);
-                    // issue slots of the output flushes (about 110 instructions each: SL * TY wrap
+                    // issue slots of the output flushes (kFlushSlots each: SL * TY wrap
                     // flushes and TY final ones per pass) relative to the FFMA of a warp's slice
-                    const double flush_share = 2.0 * (std::min<double>(p.SL * TY, rs) + TY) * 110.0 /
+                    const double flush_share = 2.0 * (std::min<double>(p.SL * TY, rs) + TY) * kFlushSlots /
                                                (rs * p.Wp * TY * kTX);
-                    const double t_rate = busiest * (macs_per_block / rate * ((rs + 0.25) / rs + flush_share) + t_stage);
+                    const double t_rate = busiest * macs_per_block / rate * ((rs + 0.25) / rs + flush_share) +
+                                          std::ceil(busiest / blocks_sm) * t_stage;
                     // A lone warp is bound by latency, not by the SM's FFMA rate: per right row its
                     // FFMAs one per clock plus ~150 cycles of row overhead per pass and ~40 per
                     // chunk visit, ~500 cycles per output flush (SL * TY wrap flushes and TY final
                     // ones per pass), ~4000 for the staging.  This decides the plan of tiny inputs
                     // (16 x 16: many small warps tasks with few flushes beat one full warp).
                     const double flushes = 2.0 * (std::min<double>(p.SL * TY, rs) + TY);
-                    const double row_cycles = 300.0 + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
+                    const double row_cycles = kRowBase + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
                     const double t_serial = (rs * row_cycles + flushes * 500.0 + 4000.0) / 1.9e9;
                     comb = want_combine;
                     if (comb == XCORR_COMBINE_AUTO) {
@@ -383,6 +400,9 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     t = std::max(t_rate, t_serial) + t_combine;
                     grid = (unsigned)(tasks * S);
                 }
+                if (plan_debug)
+                    std::fprintf(stderr, "plan TY=%d SL=%d WX=%d WY=%d S=%d sched=%d comb=%d grid=%u t=%.2f us\n", TY, SL, c.WX,
+                                 c.WY, c.S, c.sched, comb, grid, t * 1e6);
                 if (best_time < 0.0 || t < best_time * 0.9999) {
                     best_time = t;
                     best = p;
