@@ -264,6 +264,27 @@ XCORR_API xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, con
                                           uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                                           const xcorr_hints* hints, int32_t device);
 
+/* Several problems in one call.  The reference runs its algorithm objects one after the other,
+ * each through prepare / transfer / run / finalize (main.cpp:123-174; benchmark.py starts one
+ * process per input): a result copy that has to end before the next problem's input copy
+ * starts.  Here the problems of a batch share the three streams of the host-buffer path, so
+ * the input copy and the kernels of problem k+1 run under the result copy of problem k and
+ * the device -> host link stays busy from the first result to the last.  Every job is what
+ * one xcorr_run_host_f32 call takes; results are bit-identical to separate calls.  The
+ * call returns when every result is in its h_out; the first job that fails ends the batch
+ * with its status (results of earlier jobs are complete). */
+typedef struct xcorr_host_job {
+    int32_t mode;                 /* xcorr_mode */
+    uint32_t rows, cols;
+    uint32_t n_left, n_right;
+    const float* h_left;
+    const float* h_right;
+    float* h_out;
+    const xcorr_hints* hints;     /* NULL = automatic */
+} xcorr_host_job;
+
+XCORR_API xcorr_status xcorr_run_host_batch_f32(const xcorr_host_job* jobs, int32_t n_jobs, int32_t device);
+
 /* Same, with the independent result matrices sharded over `n_devices` GPUs of this
  * process (devices[i] are CUDA device indices; NULL = 0..n_devices-1): right matrices for
  * one_to_many, left matrices for n_to_m and n_to_mn (each with all / its own rights), the

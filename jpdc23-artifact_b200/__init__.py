@@ -46,6 +46,16 @@ class Hints(C.Structure):
     ]
 
 
+class HostJob(C.Structure):
+    """Mirror of ``xcorr_host_job`` (include/xcorr.h)."""
+    _fields_ = [
+        ("mode", C.c_int32), ("rows", C.c_uint32), ("cols", C.c_uint32),
+        ("n_left", C.c_uint32), ("n_right", C.c_uint32),
+        ("h_left", C.c_void_p), ("h_right", C.c_void_p), ("h_out", C.c_void_p),
+        ("hints", C.POINTER(Hints)),
+    ]
+
+
 def make_hints(kernel="auto", combine="auto", overlap_rows=0, class_lanes=0, warps_x=0, warps_y=0,
                row_slices=0, block_threads=0, schedule=0, host_chunks=0, reproducible=0) -> Hints:
     h = Hints()
@@ -96,6 +106,7 @@ def lib() -> C.CDLL:
     L.xcorr_validate_input_size.argtypes = [i32, u32, u32, u32, u32]
     L.xcorr_validate_input_size.restype = i32
     L.xcorr_run_host_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, hp, i32]
+    L.xcorr_run_host_batch_f32.argtypes = [C.POINTER(HostJob), i32, i32]
     L.xcorr_run_host_sharded_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, hp,
                                              C.POINTER(i32), i32]
     L.xcorr_shard_range.argtypes = [u32, i32, i32, C.POINTER(u32), C.POINTER(u32)]
@@ -221,6 +232,43 @@ def run_host(mode, left: np.ndarray, right: np.ndarray, hints: Hints | None = No
                                                out.ctypes.data, rows, cols, nl, nr, hp, arr,
                                                len(devices)))
     return out
+
+
+def run_host_batch(jobs, device: int = 0) -> list[np.ndarray]:
+    """Several problems in one call (``xcorr_run_host_batch_f32``): ``jobs`` is a list of
+    ``(mode, left, right)``, ``(mode, left, right, hints)`` or ``(mode, left, right, hints, out)``;
+    returns the results in order.  Arrays are used in place when they are contiguous float32
+    (so page-locked buffers stay page-locked)."""
+    n = len(jobs)
+    arr = (HostJob * max(n, 1))()
+    keep, outs = [], []
+    for k, job in enumerate(jobs):
+        mode, left, right = job[0], job[1], job[2]
+        hints = job[3] if len(job) > 3 else None
+        out = job[4] if len(job) > 4 else None
+        left = np.ascontiguousarray(left, np.float32)
+        right = np.ascontiguousarray(right, np.float32)
+        if left.ndim == 2:
+            left = left[None]
+        if right.ndim == 2:
+            right = right[None]
+        nl, rows, cols = left.shape
+        nr = right.shape[0]
+        if right.shape[1:] != (rows, cols):
+            raise ValueError("left and right matrices must have the same size")
+        shape = out_shape(mode, rows, cols, nl, nr)
+        if shape[0] == 0:
+            check(2)
+        if out is None:
+            out = np.empty(shape, np.float32)
+        arr[k].mode = _mode(mode)
+        arr[k].rows, arr[k].cols, arr[k].n_left, arr[k].n_right = rows, cols, nl, nr
+        arr[k].h_left, arr[k].h_right, arr[k].h_out = left.ctypes.data, right.ctypes.data, out.ctypes.data
+        arr[k].hints = C.pointer(hints) if hints is not None else None
+        keep.append((left, right, hints))
+        outs.append(out)
+    check(lib().xcorr_run_host_batch_f32(arr, n, device))
+    return outs
 
 
 def n_to_mn_reorder(a: np.ndarray, n_left: int, to_grouped: bool) -> np.ndarray:

@@ -664,9 +664,8 @@ struct HostCache {
     cudaStream_t stream = nullptr;       // kernels
     cudaStream_t copy_in = nullptr;      // host -> device
     cudaStream_t copy_out = nullptr;     // device -> host
-    cudaEvent_t in_done[kMaxHostChunks] = {};
-    cudaEvent_t run_done[kMaxHostChunks] = {};
-    bool events = false;
+    std::vector<cudaEvent_t> in_done;    // one pair of events per piece in flight
+    std::vector<cudaEvent_t> run_done;
 };
 HostCache g_host_cache[kMaxDevices];
 
@@ -698,14 +697,59 @@ int host_chunk_count(int32_t mode, const PairMap& pm, uint32_t units, size_t oby
     return (int)std::max<long long>(k, 1);
 }
 
-xcorr_status run_host(int32_t mode, const float* h_left, const float* h_right, float* h_out,
-                      uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
-                      const xcorr_hints* hints, int32_t device) {
-    if (!h_left || !h_right || !h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
-    if (hints && hints->host_chunks < 0) return fail(XCORR_ERR_INVALID_HINT, "host_chunks must be 0 (auto) or positive");
-    PairMap pm{};
-    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
-    if (st != XCORR_OK) return st;
+// One problem of a host-buffer call, with what the batch runner derives for it.
+struct HostJob {
+    int32_t mode;
+    const float* h_left; const float* h_right; float* h_out;
+    uint32_t rows, cols, n_left, n_right;
+    const xcorr_hints* hints;
+    PairMap pm;
+    size_t lbytes, rbytes, obytes;      // operand and result sizes
+    size_t loff, roff, ooff;            // where they sit in the device arenas (bytes)
+    uint32_t units;
+    int chunks;
+};
+
+size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+// Several problems in one call: all of them share the three streams, so the input copy and
+// the kernels of a problem run under the result copy of the one before it -- the device ->
+// host link, the slowest stage of this path, never idles between problems.  Every problem
+// keeps its own device buffers (one arena per operand) until the call returns.
+xcorr_status run_host_batch(HostJob* jobs, int n_jobs, int32_t device) {
+    if (n_jobs <= 0) return XCORR_OK;
+    size_t lsum = 0, rsum = 0, osum = 0, wsb = 0;
+    int pieces = 0;
+    xcorr_status st;
+    for (int j = 0; j < n_jobs; ++j) {
+        HostJob& J = jobs[j];
+        if (!J.h_left || !J.h_right || !J.h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+        if (J.hints && J.hints->host_chunks < 0) return fail(XCORR_ERR_INVALID_HINT, "host_chunks must be 0 (auto) or positive");
+        J.pm = PairMap{};
+        if ((st = check_sizes(J.mode, J.rows, J.cols, J.n_left, J.n_right, &J.pm)) != XCORR_OK) return st;
+        const size_t in_elems = (size_t)J.rows * J.cols;
+        const size_t out_elems = (size_t)(2 * J.rows - 1) * (2 * J.cols - 1);
+        J.lbytes = in_elems * J.n_left * sizeof(float);
+        J.rbytes = in_elems * J.n_right * sizeof(float);
+        J.obytes = out_elems * (size_t)J.pm.n_left * J.pm.m * sizeof(float);
+        J.loff = lsum; lsum += align256(J.lbytes);
+        J.roff = rsum; rsum += align256(J.rbytes);
+        J.ooff = osum; osum += align256(J.obytes);
+        // the units a piece is made of: right matrices (one_to_many) or left matrices with all
+        // (n_to_m) / their own (n_to_mn) right matrices
+        J.units = J.mode == XCORR_ONE_TO_MANY ? J.n_right : J.mode == XCORR_ONE_TO_ONE ? 1u : J.n_left;
+        J.chunks = host_chunk_count(J.mode, J.pm, J.units, J.obytes, J.hints);
+        pieces += J.chunks;
+        // workspace: the largest need among all pieces (their kernels run one after the other)
+        for (int i = 0; i < J.chunks; ++i) {
+            uint32_t first = 0, count = 0;
+            xcorr_shard_range(J.units, J.chunks, i, &first, &count);
+            if (count == 0) continue;
+            const uint32_t nl = J.mode == XCORR_ONE_TO_MANY || J.mode == XCORR_ONE_TO_ONE ? J.n_left : count;
+            const uint32_t nr = J.mode == XCORR_ONE_TO_MANY ? count : J.mode == XCORR_N_TO_MN ? count * J.pm.m : J.n_right;
+            wsb = std::max(wsb, xcorr_workspace_bytes(J.mode, J.rows, J.cols, nl, nr, J.hints));
+        }
+    }
     int ndev = 0;
     XC_CUDA(cudaGetDeviceCount(&ndev));
     if (device < 0 || device >= ndev || device >= kMaxDevices) return fail(XCORR_ERR_DEVICE, "no such CUDA device");
@@ -715,96 +759,97 @@ xcorr_status run_host(int32_t mode, const float* h_left, const float* h_right, f
     if (!c.stream) XC_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
     if (!c.copy_in) XC_CUDA(cudaStreamCreateWithFlags(&c.copy_in, cudaStreamNonBlocking));
     if (!c.copy_out) XC_CUDA(cudaStreamCreateWithFlags(&c.copy_out, cudaStreamNonBlocking));
-    if (!c.events) {
-        for (int i = 0; i < kMaxHostChunks; ++i) {
-            XC_CUDA(cudaEventCreateWithFlags(&c.in_done[i], cudaEventDisableTiming));
-            XC_CUDA(cudaEventCreateWithFlags(&c.run_done[i], cudaEventDisableTiming));
-        }
-        c.events = true;
+    while ((int)c.in_done.size() < pieces) {
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        XC_CUDA(cudaEventCreateWithFlags(&e0, cudaEventDisableTiming));
+        c.in_done.push_back(e0);
+        XC_CUDA(cudaEventCreateWithFlags(&e1, cudaEventDisableTiming));
+        c.run_done.push_back(e1);
     }
-    const size_t in_elems = (size_t)rows * cols;
-    const size_t out_elems = (size_t)(2 * rows - 1) * (2 * cols - 1);
-    const size_t lbytes = in_elems * n_left * sizeof(float);
-    const size_t rbytes = in_elems * n_right * sizeof(float);
-    const size_t obytes = out_elems * (size_t)pm.n_left * pm.m * sizeof(float);
-    if ((st = grow(&c.d_left, &c.left_bytes, lbytes)) != XCORR_OK) return st;
-    if ((st = grow(&c.d_right, &c.right_bytes, rbytes)) != XCORR_OK) return st;
-    if ((st = grow(&c.d_out, &c.out_bytes, obytes)) != XCORR_OK) return st;
-
-    // the units a piece is made of: right matrices (one_to_many) or left matrices with all
-    // (n_to_m) / their own (n_to_mn) right matrices
-    const uint32_t units = mode == XCORR_ONE_TO_MANY ? n_right : mode == XCORR_ONE_TO_ONE ? 1u : n_left;
-    const int chunks = host_chunk_count(mode, pm, units, obytes, hints);
-
-    // workspace: the largest need among the pieces (they run one after the other)
-    size_t wsb = 0;
-    for (int i = 0; i < chunks; ++i) {
-        uint32_t first = 0, count = 0;
-        xcorr_shard_range(units, chunks, i, &first, &count);
-        if (count == 0) continue;
-        const uint32_t nl = mode == XCORR_ONE_TO_MANY || mode == XCORR_ONE_TO_ONE ? n_left : count;
-        const uint32_t nr = mode == XCORR_ONE_TO_MANY ? count : mode == XCORR_N_TO_MN ? count * pm.m : n_right;
-        wsb = std::max(wsb, xcorr_workspace_bytes(mode, rows, cols, nl, nr, hints));
-    }
+    if ((st = grow(&c.d_left, &c.left_bytes, lsum)) != XCORR_OK) return st;
+    if ((st = grow(&c.d_right, &c.right_bytes, rsum)) != XCORR_OK) return st;
+    if ((st = grow(&c.d_out, &c.out_bytes, osum)) != XCORR_OK) return st;
     if ((st = grow(&c.d_ws, &c.ws_bytes, wsb)) != XCORR_OK) return st;
 
-    // the operand every piece needs goes first
-    if (mode == XCORR_ONE_TO_MANY || mode == XCORR_ONE_TO_ONE)
-        XC_CUDA(cudaMemcpyAsync(c.d_left, h_left, lbytes, cudaMemcpyHostToDevice, c.copy_in));
-    else if (mode == XCORR_N_TO_M)
-        XC_CUDA(cudaMemcpyAsync(c.d_right, h_right, rbytes, cudaMemcpyHostToDevice, c.copy_in));
-
     std::string plans;
-    for (int i = 0; i < chunks; ++i) {
-        uint32_t first = 0, count = 0;
-        xcorr_shard_range(units, chunks, i, &first, &count);
-        if (count == 0) continue;
-        const float* dl = c.d_left;
-        const float* dr = c.d_right;
-        float* dout = c.d_out;
-        float* hout = h_out;
-        uint32_t nl = n_left, nr = n_right;
-        size_t piece_out = obytes;
-        if (mode == XCORR_ONE_TO_ONE) {
-            XC_CUDA(cudaMemcpyAsync(c.d_right, h_right, rbytes, cudaMemcpyHostToDevice, c.copy_in));
-        } else if (mode == XCORR_ONE_TO_MANY) {
-            const size_t off = (size_t)first * in_elems;
-            XC_CUDA(cudaMemcpyAsync(c.d_right + off, h_right + off, (size_t)count * in_elems * sizeof(float),
-                                    cudaMemcpyHostToDevice, c.copy_in));
-            dr += off; nr = count;
-            dout += (size_t)first * out_elems; hout += (size_t)first * out_elems;
-            piece_out = (size_t)count * out_elems * sizeof(float);
-        } else {
-            const size_t loff = (size_t)first * in_elems;
-            XC_CUDA(cudaMemcpyAsync(c.d_left + loff, h_left + loff, (size_t)count * in_elems * sizeof(float),
-                                    cudaMemcpyHostToDevice, c.copy_in));
-            dl += loff; nl = count;
-            if (mode == XCORR_N_TO_MN) {
-                const size_t roff = (size_t)first * pm.m * in_elems;
-                XC_CUDA(cudaMemcpyAsync(c.d_right + roff, h_right + roff,
-                                        (size_t)count * pm.m * in_elems * sizeof(float),
+    int piece = 0;
+    for (int j = 0; j < n_jobs; ++j) {
+        const HostJob& J = jobs[j];
+        const int32_t mode = J.mode;
+        const PairMap& pm = J.pm;
+        const size_t in_elems = (size_t)J.rows * J.cols;
+        const size_t out_elems = (size_t)(2 * J.rows - 1) * (2 * J.cols - 1);
+        float* const job_left = c.d_left + J.loff / sizeof(float);
+        float* const job_right = c.d_right + J.roff / sizeof(float);
+        float* const job_out = c.d_out + J.ooff / sizeof(float);
+        // the operand every piece needs goes first
+        if (mode == XCORR_ONE_TO_MANY || mode == XCORR_ONE_TO_ONE)
+            XC_CUDA(cudaMemcpyAsync(job_left, J.h_left, J.lbytes, cudaMemcpyHostToDevice, c.copy_in));
+        else if (mode == XCORR_N_TO_M)
+            XC_CUDA(cudaMemcpyAsync(job_right, J.h_right, J.rbytes, cudaMemcpyHostToDevice, c.copy_in));
+        for (int i = 0; i < J.chunks; ++i, ++piece) {
+            uint32_t first = 0, count = 0;
+            xcorr_shard_range(J.units, J.chunks, i, &first, &count);
+            if (count == 0) continue;
+            const float* dl = job_left;
+            const float* dr = job_right;
+            float* dout = job_out;
+            float* hout = J.h_out;
+            uint32_t nl = J.n_left, nr = J.n_right;
+            size_t piece_out = J.obytes;
+            if (mode == XCORR_ONE_TO_ONE) {
+                XC_CUDA(cudaMemcpyAsync(job_right, J.h_right, J.rbytes, cudaMemcpyHostToDevice, c.copy_in));
+            } else if (mode == XCORR_ONE_TO_MANY) {
+                const size_t off = (size_t)first * in_elems;
+                XC_CUDA(cudaMemcpyAsync(job_right + off, J.h_right + off, (size_t)count * in_elems * sizeof(float),
                                         cudaMemcpyHostToDevice, c.copy_in));
-                dr += roff; nr = count * pm.m;
+                dr += off; nr = count;
+                dout += (size_t)first * out_elems; hout += (size_t)first * out_elems;
+                piece_out = (size_t)count * out_elems * sizeof(float);
+            } else {
+                const size_t loff = (size_t)first * in_elems;
+                XC_CUDA(cudaMemcpyAsync(job_left + loff, J.h_left + loff, (size_t)count * in_elems * sizeof(float),
+                                        cudaMemcpyHostToDevice, c.copy_in));
+                dl += loff; nl = count;
+                if (mode == XCORR_N_TO_MN) {
+                    const size_t roff = (size_t)first * pm.m * in_elems;
+                    XC_CUDA(cudaMemcpyAsync(job_right + roff, J.h_right + roff,
+                                            (size_t)count * pm.m * in_elems * sizeof(float),
+                                            cudaMemcpyHostToDevice, c.copy_in));
+                    dr += roff; nr = count * pm.m;
+                }
+                dout += (size_t)first * pm.m * out_elems; hout += (size_t)first * pm.m * out_elems;
+                piece_out = (size_t)count * pm.m * out_elems * sizeof(float);
             }
-            dout += (size_t)first * pm.m * out_elems; hout += (size_t)first * pm.m * out_elems;
-            piece_out = (size_t)count * pm.m * out_elems * sizeof(float);
+            XC_CUDA(cudaEventRecord(c.in_done[piece], c.copy_in));
+            XC_CUDA(cudaStreamWaitEvent(c.stream, c.in_done[piece], 0));
+            st = run_device(mode, dl, dr, dout, J.rows, J.cols, nl, nr, J.hints, c.d_ws, c.ws_bytes, c.stream);
+            if (st != XCORR_OK) {
+                // let what was queued finish before the buffers can be reused
+                cudaStreamSynchronize(c.copy_in); cudaStreamSynchronize(c.stream); cudaStreamSynchronize(c.copy_out);
+                return st;
+            }
+            if (i == 0) {
+                if (!plans.empty()) plans += "; ";
+                plans += (J.chunks > 1 ? "host_chunks=" + std::to_string(J.chunks) + " first{" + t_last_launch + "}" : t_last_launch);
+            }
+            XC_CUDA(cudaEventRecord(c.run_done[piece], c.stream));
+            XC_CUDA(cudaStreamWaitEvent(c.copy_out, c.run_done[piece], 0));
+            XC_CUDA(cudaMemcpyAsync(hout, dout, piece_out, cudaMemcpyDeviceToHost, c.copy_out));
         }
-        XC_CUDA(cudaEventRecord(c.in_done[i], c.copy_in));
-        XC_CUDA(cudaStreamWaitEvent(c.stream, c.in_done[i], 0));
-        st = run_device(mode, dl, dr, dout, rows, cols, nl, nr, hints, c.d_ws, c.ws_bytes, c.stream);
-        if (st != XCORR_OK) {
-            // let what was queued finish before the buffers can be reused
-            cudaStreamSynchronize(c.copy_in); cudaStreamSynchronize(c.stream); cudaStreamSynchronize(c.copy_out);
-            return st;
-        }
-        if (chunks > 1 && i == 0) plans = t_last_launch;
-        XC_CUDA(cudaEventRecord(c.run_done[i], c.stream));
-        XC_CUDA(cudaStreamWaitEvent(c.copy_out, c.run_done[i], 0));
-        XC_CUDA(cudaMemcpyAsync(hout, dout, piece_out, cudaMemcpyDeviceToHost, c.copy_out));
     }
     XC_CUDA(cudaStreamSynchronize(c.copy_out));
-    if (chunks > 1) t_last_launch = "host_chunks=" + std::to_string(chunks) + " first{" + plans + "}";
+    t_last_launch = n_jobs > 1 ? "host_batch=" + std::to_string(n_jobs) + " [" + plans + "]" : plans;
     return XCORR_OK;
+}
+
+xcorr_status run_host(int32_t mode, const float* h_left, const float* h_right, float* h_out,
+                      uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                      const xcorr_hints* hints, int32_t device) {
+    HostJob job{};
+    job.mode = mode; job.h_left = h_left; job.h_right = h_right; job.h_out = h_out;
+    job.rows = rows; job.cols = cols; job.n_left = n_left; job.n_right = n_right; job.hints = hints;
+    return run_host_batch(&job, 1, device);
 }
 
 }  // namespace
@@ -976,6 +1021,21 @@ xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, const float* 
     return run_host(mode, h_left, h_right, h_out, rows, cols, n_left, n_right, hints, device);
 }
 
+xcorr_status xcorr_run_host_batch_f32(const xcorr_host_job* jobs, int32_t n_jobs, int32_t device) {
+    if (n_jobs < 0) return fail(XCORR_ERR_INVALID_SIZE, "n_jobs must not be negative");
+    if (n_jobs == 0) return XCORR_OK;
+    if (!jobs) return fail(XCORR_ERR_NULL_POINTER, "jobs must not be NULL");
+    std::vector<HostJob> hj((size_t)n_jobs);
+    for (int j = 0; j < n_jobs; ++j) {
+        hj[j].mode = jobs[j].mode;
+        hj[j].h_left = jobs[j].h_left; hj[j].h_right = jobs[j].h_right; hj[j].h_out = jobs[j].h_out;
+        hj[j].rows = jobs[j].rows; hj[j].cols = jobs[j].cols;
+        hj[j].n_left = jobs[j].n_left; hj[j].n_right = jobs[j].n_right;
+        hj[j].hints = jobs[j].hints;
+    }
+    return run_host_batch(hj.data(), n_jobs, device);
+}
+
 void xcorr_shard_range(uint32_t units, int32_t parts, int32_t index, uint32_t* first, uint32_t* count) {
     if (parts <= 0 || index < 0 || index >= parts) {
         if (first) *first = 0;
@@ -1056,10 +1116,10 @@ void xcorr_release_host_cache(void) {
         if (c.stream) cudaStreamDestroy(c.stream);
         if (c.copy_in) cudaStreamDestroy(c.copy_in);
         if (c.copy_out) cudaStreamDestroy(c.copy_out);
-        if (c.events) {
-            for (int i = 0; i < kMaxHostChunks; ++i) { cudaEventDestroy(c.in_done[i]); cudaEventDestroy(c.run_done[i]); }
-            c.events = false;
-        }
+        for (cudaEvent_t e : c.in_done) cudaEventDestroy(e);
+        for (cudaEvent_t e : c.run_done) cudaEventDestroy(e);
+        c.in_done.clear();
+        c.run_done.clear();
         c.copy_in = c.copy_out = nullptr;
         c.d_left = c.d_right = c.d_out = nullptr;
         c.d_ws = nullptr;

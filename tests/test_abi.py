@@ -112,6 +112,15 @@ def test_argument_errors_come_back_as_status_codes(xc):
     assert lib.xcorr_run_host_f32(0, None, p, p, 4, 4, 1, 1, None, 0) == 1
     assert b"NULL" in lib.xcorr_last_error_string()
     assert lib.xcorr_run_host_sharded_f32(1, p, p, p, 4, 4, 1, 2, None, None, 0) == 7
+    assert lib.xcorr_run_host_batch_f32(None, 3, 0) == 1
+    assert lib.xcorr_run_host_batch_f32(None, -1, 0) == 2
+    assert lib.xcorr_run_host_batch_f32(None, 0, 0) == 0
+    job = (xc.HostJob * 1)()
+    job[0].mode, job[0].rows, job[0].cols, job[0].n_left, job[0].n_right = 2, 4, 4, 3, 10
+    job[0].h_left = job[0].h_right = job[0].h_out = p
+    assert lib.xcorr_run_host_batch_f32(job, 1, 0) == 2           # 10 rights do not divide over 3 lefts
+    job[0].h_out = None
+    assert lib.xcorr_run_host_batch_f32(job, 1, 0) == 1
     assert lib.xcorr_n_to_mn_reorder_f32(None, p, 1, 1, 1, 1) == 1
     assert lib.xcorr_ffma_peak_probe(None, None, None) == 1
 

@@ -338,6 +338,61 @@ def test_host_entry_point_in_pieces(xc, oracle, mode, nl, nr, chunks):
     assert e.value.status == 3
 
 
+def test_host_batch_equals_separate_calls(xc, oracle):
+    """Several problems in one host-buffer call (their copies and kernels overlap across
+    problems): every result is bit-identical to the same problem's own call and agrees with the
+    oracle; problems of different modes, sizes and piece counts, two of them sharing inputs."""
+    rep = dict(reproducible=1)       # automatic plans whose results do not depend on the order of atomic adds
+    shapes = [("one_to_one", 16, 16, 1, 1, xc.make_hints(**rep)),
+              ("one_to_many", 24, 20, 1, 13, xc.make_hints(host_chunks=3, **rep)),
+              ("n_to_m", 12, 12, 6, 5, xc.make_hints(host_chunks=2, **rep)),
+              ("n_to_mn", 10, 14, 4, 12, xc.make_hints(**rep)),
+              ("one_to_one", 40, 40, 1, 1, None),
+              ("one_to_many", 24, 20, 1, 13, xc.make_hints(kernel="overlap_wise"))]
+    jobs, alone = [], []
+    for k, (mode, r, c, nl, nr, hints) in enumerate(shapes):
+        left, right = seeded_inputs(r, c, nl, nr, 40 + (k if k != 5 else 1))
+        jobs.append((mode, left, right, hints))
+        alone.append(xc.run_host(mode, left, right, hints))
+    got = xc.run_host_batch(jobs)
+    assert xc.last_launch().startswith("host_batch=6 [")
+    assert len(got) == len(jobs)
+    for (mode, left, right, hints), g, a in zip(jobs, got, alone):
+        if hints is not None:
+            assert np.array_equal(g, a)
+        else:                            # stream-K with atomic adds: last bits vary run to run
+            assert np.abs(g - a).max() <= 2e-6 * np.abs(a).max()
+        assert rel_err(g, oracle_grouped(oracle, mode, left, right)) <= REL_TOL
+    # again with the cached buffers, results written into caller-provided arrays
+    outs = [np.full_like(a, np.nan) for a in alone]
+    again = xc.run_host_batch([j + (o,) for j, o in zip(jobs, outs)])
+    for o, a, r in zip(outs, alone, again):
+        assert r is o and np.abs(o - a).max() <= 2e-6 * np.abs(a).max()
+    assert xc.run_host_batch([]) == []
+    xc.check_device()
+
+
+def test_host_batch_errors(xc):
+    """A bad job ends the batch with its status before anything is queued; a NULL job list
+    and a negative count are argument errors."""
+    left, right = seeded_inputs(8, 8, 1, 3, 5)
+    bad = np.zeros((2, 8, 8), np.float32)
+    with pytest.raises(xc.XcorrError) as e:
+        xc.run_host_batch([("one_to_many", left, right), ("n_to_mn", np.zeros((3, 8, 8), np.float32), bad)])
+    assert e.value.status == 2
+    with pytest.raises(xc.XcorrError) as e:
+        xc.run_host_batch([("one_to_many", left, right, xc.make_hints(host_chunks=-2))])
+    assert e.value.status == 3
+    lib = xc.lib()
+    assert lib.xcorr_run_host_batch_f32(None, 2, 0) == 1
+    assert lib.xcorr_run_host_batch_f32(None, -1, 0) == 2
+    assert lib.xcorr_run_host_batch_f32(None, 0, 0) == 0
+    with pytest.raises(xc.XcorrError) as e:
+        xc.run_host_batch([("one_to_many", left, right)], device=torch.cuda.device_count() + 3)
+    assert e.value.status == 7
+    xc.check_device()
+
+
 def test_launch_bookkeeping(xc):
     left, right = seeded_inputs(16, 16, 1, 1, 2)
     xc.reset_launch_count()
