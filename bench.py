@@ -330,6 +330,38 @@ def fft_path_timings(xc, dev, stream, hbm_peak, iters=20):
     return out
 
 
+def f64_path_timings(xc, dev, stream, iters=5):
+    """The double-precision entry point (xcorr_run_f64) on the same configurations, inputs widened
+    to double: GFLOP/s, fraction of the FP64-FMA peak measured now, and the distance of the float
+    result to it.  Reported beside the headline, not part of it."""
+    import torch
+    dfma_flops, _ = xc.dfma_peak_probe(stream)
+    out = {"dfma_peak_measured_tflops": dfma_flops / 1e12}
+    for k, (mode, r, c, nl, nr) in CONFIGS.items():
+        d = dev[k]
+        left, right = d["left"].double(), d["right"].double()
+        res = torch.empty(d["out"].shape, dtype=torch.float64, device="cuda")
+
+        def run():
+            xc.run_device_f64(mode, left.data_ptr(), right.data_ptr(), res.data_ptr(), r, c, nl, nr, stream)
+        for _ in range(2):
+            run()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(iters):
+            run()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / iters
+        out[k] = {"ms": ms, "gflops": flop_of(k) / (ms * 1e-3) / 1e9,
+                  "frac_dfma_measured": flop_of(k) / (ms * 1e-3) / dfma_flops,
+                  "float_result_max_abs_diff_over_max": float((d["out"].double() - res).abs().max() / res.abs().max())}
+        del left, right, res
+    return out
+
+
 # The reference's own benchmark grid (benchmark/benchmark.yml: groups one_to_one, one_to_many,
 # n_to_mn, n_to_m and their "saturated" variants), as rows x cols x left x right.
 GRID = {
@@ -757,6 +789,7 @@ def main():
         }
         if world == 1 and not args.no_extras:
             line["fft_path"] = fft_path_timings(xc, dev, stream, hbm_peak)
+            line["f64_path"] = f64_path_timings(xc, dev, stream)
             for k, e in line["fft_path"].items():
                 e["direct_ms"] = per_ms_max[k]
             ref_gpu = reference_gpu_baseline(dev)

@@ -264,6 +264,21 @@ XCORR_API xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, con
                                           uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                                           const xcorr_hints* hints, int32_t device);
 
+/* ---- double precision ----------------------------------------------------------------------
+ * The reference parses `--data_type double` and refuses it (main.cpp:433-434); its <double>
+ * kernel instantiations are commented out (e.g. naive_shuffle.cu:545-552).  Same modes,
+ * layouts (n_to_mn GROUPED) and definition as the float entry points; no workspace, no
+ * hints: one kernel (a warp per 8 x 32 block of one result matrix, double accumulation in
+ * a fixed order: results are bit-reproducible).  Asynchronous on `stream`. */
+XCORR_API xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_right, double* d_out,
+                                     uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                     void* stream);
+
+/* Host pointers in, host result out (allocate, copy, run, copy back, free); synchronous. */
+XCORR_API xcorr_status xcorr_run_host_f64(int32_t mode, const double* h_left, const double* h_right, double* h_out,
+                                          uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
+                                          int32_t device);
+
 /* Several problems in one call.  The reference runs its algorithm objects one after the other,
  * each through prepare / transfer / run / finalize (main.cpp:123-174; benchmark.py starts one
  * process per input): a result copy that has to end before the next problem's input copy
@@ -336,6 +351,9 @@ XCORR_API xcorr_status xcorr_check_device(void);
  * register-only FFMA kernel on every SM, timed with CUDA events on `stream`
  * (synchronises).  The denominator for "fraction of FFMA peak". */
 XCORR_API xcorr_status xcorr_ffma_peak_probe(double* flops_per_second, double* kernel_ms, void* stream);
+
+/* The same for FP64 FMA: the denominator for the double-precision entry points. */
+XCORR_API xcorr_status xcorr_dfma_peak_probe(double* flops_per_second, double* kernel_ms, void* stream);
 
 #ifdef __cplusplus
 }

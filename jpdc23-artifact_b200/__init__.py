@@ -106,6 +106,8 @@ def lib() -> C.CDLL:
     L.xcorr_validate_input_size.argtypes = [i32, u32, u32, u32, u32]
     L.xcorr_validate_input_size.restype = i32
     L.xcorr_run_host_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, hp, i32]
+    L.xcorr_run_f64.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, vp]
+    L.xcorr_run_host_f64.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, i32]
     L.xcorr_run_host_batch_f32.argtypes = [C.POINTER(HostJob), i32, i32]
     L.xcorr_run_host_sharded_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, hp,
                                              C.POINTER(i32), i32]
@@ -124,6 +126,7 @@ def lib() -> C.CDLL:
     L.xcorr_reset_launch_count.argtypes = []
     L.xcorr_reset_launch_count.restype = None
     L.xcorr_ffma_peak_probe.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_double), vp]
+    L.xcorr_dfma_peak_probe.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_double), vp]
     L.xcorr_fft_workspace_bytes.argtypes = [i32, u32, u32, u32, u32, i32]
     L.xcorr_fft_workspace_bytes.restype = sz
     L.xcorr_fft_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, i32, vp, sz, vp]
@@ -234,6 +237,32 @@ def run_host(mode, left: np.ndarray, right: np.ndarray, hints: Hints | None = No
     return out
 
 
+def run_device_f64(mode, left_ptr, right_ptr, out_ptr, rows, cols, n_left, n_right, stream=0) -> None:
+    """``xcorr_run_f64`` on device pointers (float64, same layouts as the float entry points)."""
+    check(lib().xcorr_run_f64(_mode(mode), left_ptr, right_ptr, out_ptr, rows, cols, n_left, n_right, stream))
+
+
+def run_host_f64(mode, left: np.ndarray, right: np.ndarray, device: int = 0) -> np.ndarray:
+    """Double precision, host arrays in, host result out (``xcorr_run_host_f64``)."""
+    left = np.ascontiguousarray(left, np.float64)
+    right = np.ascontiguousarray(right, np.float64)
+    if left.ndim == 2:
+        left = left[None]
+    if right.ndim == 2:
+        right = right[None]
+    nl, rows, cols = left.shape
+    nr = right.shape[0]
+    if right.shape[1:] != (rows, cols):
+        raise ValueError("left and right matrices must have the same size")
+    shape = out_shape(mode, rows, cols, nl, nr)
+    if shape[0] == 0:
+        check(2)
+    out = np.empty(shape, np.float64)
+    check(lib().xcorr_run_host_f64(_mode(mode), left.ctypes.data, right.ctypes.data, out.ctypes.data,
+                                   rows, cols, nl, nr, device))
+    return out
+
+
 def run_host_batch(jobs, device: int = 0) -> list[np.ndarray]:
     """Several problems in one call (``xcorr_run_host_batch_f32``): ``jobs`` is a list of
     ``(mode, left, right)``, ``(mode, left, right, hints)`` or ``(mode, left, right, hints, out)``;
@@ -295,4 +324,10 @@ def reset_launch_count() -> None:
 def ffma_peak_probe(stream: int = 0):
     flops, ms = C.c_double(0), C.c_double(0)
     check(lib().xcorr_ffma_peak_probe(C.byref(flops), C.byref(ms), stream or None))
+    return flops.value, ms.value
+
+
+def dfma_peak_probe(stream: int = 0):
+    flops, ms = C.c_double(0), C.c_double(0)
+    check(lib().xcorr_dfma_peak_probe(C.byref(flops), C.byref(ms), stream or None))
     return flops.value, ms.value

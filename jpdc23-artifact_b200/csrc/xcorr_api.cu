@@ -1021,6 +1021,54 @@ xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, const float* 
     return run_host(mode, h_left, h_right, h_out, rows, cols, n_left, n_right, hints, device);
 }
 
+xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_right, double* d_out,
+                           uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right, void* stream) {
+    if (!d_left || !d_right || !d_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+    PairMap pm{};
+    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+    if (st != XCORR_OK) return st;
+    dim3 g, b;
+    XC_CUDA(launch_strip_f64(d_left, d_right, d_out, (int)rows, (int)cols, pm,
+                             (unsigned long long)pm.n_left * pm.m, &g, &b, static_cast<cudaStream_t>(stream)));
+    char buf[128];
+    std::snprintf(buf, sizeof buf, "kernel=strip_f64 grid=(%u,1,1) block=(%u,1,1) smem=0", g.x, b.x);
+    t_last_launch = buf;
+    ++t_launch_count;
+    return XCORR_OK;
+}
+
+xcorr_status xcorr_run_host_f64(int32_t mode, const double* h_left, const double* h_right, double* h_out,
+                                uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right, int32_t device) {
+    if (!h_left || !h_right || !h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+    PairMap pm{};
+    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+    if (st != XCORR_OK) return st;
+    int ndev = 0;
+    XC_CUDA(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) return fail(XCORR_ERR_DEVICE, "no such CUDA device");
+    XC_CUDA(cudaSetDevice(device));
+    const size_t in_elems = (size_t)rows * cols;
+    const size_t lbytes = in_elems * n_left * sizeof(double), rbytes = in_elems * n_right * sizeof(double);
+    const size_t obytes = (size_t)(2 * rows - 1) * (2 * cols - 1) * pm.n_left * pm.m * sizeof(double);
+    double *dl = nullptr, *dr = nullptr, *dout = nullptr;
+    cudaStream_t stream = nullptr;
+    cudaError_t e = cudaMalloc(&dl, lbytes);
+    if (e == cudaSuccess) e = cudaMalloc(&dr, rbytes);
+    if (e == cudaSuccess) e = cudaMalloc(&dout, obytes);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dl, h_left, lbytes, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dr, h_right, rbytes, cudaMemcpyHostToDevice, stream);
+    st = XCORR_OK;
+    if (e == cudaSuccess) st = xcorr_run_f64(mode, dl, dr, dout, rows, cols, n_left, n_right, stream);
+    if (e == cudaSuccess && st == XCORR_OK) e = cudaMemcpyAsync(h_out, dout, obytes, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess && stream) e = cudaStreamSynchronize(stream);
+    if (stream) cudaStreamDestroy(stream);
+    cudaFree(dl); cudaFree(dr); cudaFree(dout);
+    if (st != XCORR_OK) return st;
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return fail(XCORR_ERR_CUDA, cudaGetErrorString(e)); }
+    return XCORR_OK;
+}
+
 xcorr_status xcorr_run_host_batch_f32(const xcorr_host_job* jobs, int32_t n_jobs, int32_t device) {
     if (n_jobs < 0) return fail(XCORR_ERR_INVALID_SIZE, "n_jobs must not be negative");
     if (n_jobs == 0) return XCORR_OK;
@@ -1181,6 +1229,38 @@ xcorr_status xcorr_ffma_peak_probe(double* flops_per_second, double* kernel_ms, 
     for (int rep = 0; rep < 4; ++rep) {            // first repetition is the warm-up
         XC_CUDA(cudaEventRecord(e0, stream));
         XC_CUDA(launch_ffma_probe(sink, iters, blocks, stream));
+        XC_CUDA(cudaEventRecord(e1, stream));
+        XC_CUDA(cudaEventSynchronize(e1));
+        float ms = 0.f;
+        XC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        if (rep > 0 && ms < best_ms) best_ms = ms;
+        ++t_launch_count;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(sink);
+    const double flop = 2.0 * 16.0 * 8.0 * (double)iters * 1024.0 * (double)blocks;
+    *flops_per_second = flop / (best_ms * 1e-3);
+    if (kernel_ms) *kernel_ms = best_ms;
+    return XCORR_OK;
+}
+
+xcorr_status xcorr_dfma_peak_probe(double* flops_per_second, double* kernel_ms, void* stream_v) {
+    if (!flops_per_second) return fail(XCORR_ERR_NULL_POINTER, "flops_per_second must not be NULL");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    DeviceInfo dev;
+    xcorr_status st = current_device_info(&dev);
+    if (st != XCORR_OK) return st;
+    double* sink = nullptr;
+    XC_CUDA(cudaMalloc(&sink, sizeof(double)));
+    cudaEvent_t e0, e1;
+    XC_CUDA(cudaEventCreate(&e0));
+    XC_CUDA(cudaEventCreate(&e1));
+    const int blocks = dev.sm_count * 2, iters = 2048;
+    double best_ms = 1e30;
+    for (int rep = 0; rep < 4; ++rep) {            // first repetition is the warm-up
+        XC_CUDA(cudaEventRecord(e0, stream));
+        XC_CUDA(launch_dfma_probe(sink, iters, blocks, stream));
         XC_CUDA(cudaEventRecord(e1, stream));
         XC_CUDA(cudaEventSynchronize(e1));
         float ms = 0.f;

@@ -1,0 +1,138 @@
+// Double-precision direct cross-correlation (the reference stubs `--data_type double` out,
+// main.cpp:433-434, and comments out every <double> instantiation, e.g. naive_shuffle.cu:545-552).
+//
+// Column-strip kernel: a warp owns 32 consecutive output columns of RT consecutive output rows
+// of one pair.  For every right column x it walks down the right rows; the RT left values that
+// meet right row y in the RT output rows form a window that slides down one left row per step,
+// so a step costs one left load (coalesced over the lanes' 32 shifts), one right load (one
+// address for the whole warp) and RT DFMA.  The loop over y is unrolled RT times so that the
+// window rotates through fixed registers.  Loads outside a matrix are predicated to zero; the x
+// range is the union over the warp's lanes and the y range the union over its RT rows.
+// FP64 runs at half the FP32 lane count on this part (64 lanes per SM and clock), so the
+// two loads per RT DFMA stay under the load/store bandwidth for RT = 8.
+#include "xcorr_launch.h"
+
+namespace xcorr {
+namespace {
+
+constexpr int kRT = 8;            // output rows per warp
+constexpr int kStripWarps = 8;    // warps per block
+
+__global__ void __launch_bounds__(kStripWarps * 32)
+strip_f64_kernel(const double* __restrict__ left, const double* __restrict__ right, double* __restrict__ out,
+                 int H, int W, PairMap pm, unsigned long long ntasks, int row_tiles, int col_tiles) {
+    const int OW = 2 * W - 1, OH = 2 * H - 1;
+    const int lane = threadIdx.x & 31;
+    const unsigned long long task = (unsigned long long)blockIdx.x * kStripWarps + (threadIdx.x >> 5);
+    if (task >= ntasks) return;
+    const int ct = (int)(task % col_tiles);
+    const unsigned long long t2 = task / col_tiles;
+    const int rt = (int)(t2 % row_tiles);
+    const unsigned long long pair = t2 / row_tiles;
+    const unsigned long long l = pair / pm.m, j = pair % pm.m;
+    const double* L = left + l * (size_t)H * W;
+    const double* R = right + (l * pm.right_stride + j) * (size_t)H * W;
+
+    const int oy0 = rt * kRT, ox = ct * 32 + lane;
+    const int sy0 = oy0 - (H - 1), sx = ox - (W - 1);
+    // right columns any lane of the warp needs, right rows any of the RT output rows needs
+    const int sx_lo = ct * 32 - (W - 1);
+    const int sx_hi = min(ct * 32 + 31, OW - 1) - (W - 1);
+    const int xa = max(0, -sx_hi), xb = min(W, W - sx_lo);
+    const int ya = max(0, -(sy0 + kRT - 1)), yb = min(H, H - sy0);
+
+    double acc[kRT];
+#pragma unroll
+    for (int k = 0; k < kRT; ++k) acc[k] = 0.0;
+
+    // right rows whose newest left row (y + sy0 + RT - 1) is inside the left matrix: no checks there
+    const int y_in = min(yb, H - sy0 - (kRT - 1));
+    const size_t rowW = (size_t)W;
+    for (int x = xa; x < xb; ++x) {
+        const int lx = x + sx;
+        // lanes whose shift has no left element over this right column sit the column out (the
+        // loop bounds below are the same for every lane, so they rejoin at its end)
+        if (ox < OW && lx >= 0 && lx < W) {
+            double w[kRT];
+            // window at y = ya: left rows ya + sy0 + k, k = 0 .. RT-2 (the last one is loaded in the loop)
+#pragma unroll
+            for (int k = 0; k < kRT - 1; ++k) {
+                const int row = ya + sy0 + k;
+                w[k] = (row >= 0 && row < H) ? __ldg(L + (size_t)row * rowW + lx) : 0.0;
+            }
+            const double* pl = L + (size_t)(ya + sy0 + kRT - 1) * rowW + lx;    // newest left row of the window
+            const double* pr = R + (size_t)ya * rowW + x;
+            int y = ya;
+            for (; y + kRT <= y_in; y += kRT) {
+#pragma unroll
+                for (int u = 0; u < kRT; ++u) {
+                    w[(u + kRT - 1) % kRT] = __ldg(pl);
+                    const double r = __ldg(pr);
+                    pl += rowW;
+                    pr += rowW;
+#pragma unroll
+                    for (int k = 0; k < kRT; ++k) acc[k] = fma(w[(u + k) % kRT], r, acc[k]);
+                }
+            }
+            // the last rows: the window runs off the left matrix and / or the right rows end
+            for (; y < yb; y += kRT) {
+#pragma unroll
+                for (int u = 0; u < kRT; ++u) {
+                    const int yy = y + u;
+                    w[(u + kRT - 1) % kRT] = (yy + sy0 + kRT - 1 < H) ? __ldg(pl) : 0.0;
+                    const double r = yy < yb ? __ldg(pr) : 0.0;
+                    pl += rowW;
+                    pr += rowW;
+#pragma unroll
+                    for (int k = 0; k < kRT; ++k) acc[k] = fma(w[(u + k) % kRT], r, acc[k]);
+                }
+            }
+        }
+    }
+    if (ox < OW) {
+        double* o = out + pair * (size_t)OW * OH + (size_t)oy0 * OW + ox;
+#pragma unroll
+        for (int k = 0; k < kRT; ++k)
+            if (oy0 + k < OH) o[(size_t)k * OW] = acc[k];
+    }
+}
+
+// FP64 FMA peak probe: 16 independent chains per thread, registers only
+__global__ void __launch_bounds__(1024) dfma_probe_kernel(double* sink, double b, double c, int iters) {
+    double v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = (double)(threadIdx.x + i) * 1e-3;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int rep = 0; rep < 8; ++rep)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = fma(v[i], b, c);
+    }
+    double s = 0.0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s += v[i];
+    if (s == 123.456) sink[0] = s;    // never true in practice; keeps the chains alive
+}
+
+}  // namespace
+
+cudaError_t launch_dfma_probe(double* sink, int iters, int blocks, cudaStream_t stream) {
+    dfma_probe_kernel<<<blocks, 1024, 0, stream>>>(sink, 0.999, 1e-3, iters);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_strip_f64(const double* left, const double* right, double* out, int H, int W, PairMap pm,
+                             unsigned long long npairs, dim3* grid_out, dim3* block_out, cudaStream_t stream) {
+    const int OW = 2 * W - 1, OH = 2 * H - 1;
+    const int row_tiles = (OH + kRT - 1) / kRT, col_tiles = (OW + 31) / 32;
+    const unsigned long long ntasks = npairs * row_tiles * col_tiles;
+    const unsigned long long blocks = (ntasks + kStripWarps - 1) / kStripWarps;
+    if (blocks == 0 || blocks > 2147483647ull) return cudaErrorInvalidConfiguration;
+    dim3 grid((unsigned)blocks), block(kStripWarps * 32);
+    strip_f64_kernel<<<grid, block, 0, stream>>>(left, right, out, H, W, pm, ntasks, row_tiles, col_tiles);
+    *grid_out = grid;
+    *block_out = block;
+    return cudaGetLastError();
+}
+
+}  // namespace xcorr

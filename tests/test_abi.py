@@ -123,6 +123,11 @@ def test_argument_errors_come_back_as_status_codes(xc):
     assert lib.xcorr_run_host_batch_f32(job, 1, 0) == 1
     assert lib.xcorr_n_to_mn_reorder_f32(None, p, 1, 1, 1, 1) == 1
     assert lib.xcorr_ffma_peak_probe(None, None, None) == 1
+    assert lib.xcorr_dfma_peak_probe(None, None, None) == 1
+    assert lib.xcorr_run_f64(0, None, p, p, 4, 4, 1, 1, None) == 1
+    assert lib.xcorr_run_f64(2, p, p, p, 4, 4, 3, 10, None) == 2
+    assert lib.xcorr_run_host_f64(1, p, None, p, 4, 4, 1, 2, 0) == 1
+    assert lib.xcorr_run_host_f64(3, p, p, p, 4, 0, 1, 2, 0) == 2
 
 
 def test_plans_exist_and_fit_for_a_sweep_of_shapes(xc):

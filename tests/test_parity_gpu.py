@@ -393,6 +393,48 @@ def test_host_batch_errors(xc):
     xc.check_device()
 
 
+# ---- double precision ------------------------------------------------------------------------------
+F64_TOL = 1e-13      # relative to max|result|: double accumulation, another order of summation
+
+
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [
+    ("one_to_one", 1, 1, 1, 1), ("one_to_one", 16, 16, 1, 1), ("one_to_one", 5, 37, 1, 1), ("one_to_one", 64, 64, 1, 1),
+    ("one_to_one", 33, 8, 1, 1), ("one_to_one", 96, 128, 1, 1), ("one_to_many", 24, 20, 1, 7),
+    ("n_to_mn", 10, 14, 3, 9), ("n_to_m", 12, 12, 4, 5), ("one_to_many", 3, 70, 1, 2)])
+def test_double_precision_against_the_oracle(xc, oracle, mode, rows, cols, nl, nr):
+    """float32-valued inputs widened to double: every product is exact in double, so the double
+    entry point has to agree with the oracle's double accumulation to rounding of the sums."""
+    left, right = seeded_inputs(rows, cols, nl, nr, 61)
+    want = oracle_grouped(oracle, mode, left, right)
+    got = xc.run_host_f64(mode, left.astype(np.float64), right.astype(np.float64))
+    assert got.dtype == np.float64 and got.shape == want.shape
+    assert xc.last_launch().startswith("kernel=strip_f64")
+    assert np.abs(got - want).max() <= F64_TOL * max(np.abs(want).max(), 1e-300)
+
+
+def test_double_precision_inputs_against_float64_correlation(xc):
+    """Inputs that need all 53 bits, against scipy's float64 correlation (an independent
+    statement of the definition); on device pointers, twice: bit-identical (fixed summation order)."""
+    from scipy.signal import correlate2d
+    rng = np.random.default_rng(77)
+    left = rng.random((1, 40, 52)) - 0.5
+    right = rng.random((6, 40, 52)) * 3.0
+    want = np.stack([correlate2d(left[0], r, mode="full") for r in right])
+    d_l, d_r = torch.from_numpy(left).cuda(), torch.from_numpy(right).cuda()
+    d_o = torch.full((6, 79, 103), float("nan"), dtype=torch.float64, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    xc.run_device_f64("one_to_many", d_l.data_ptr(), d_r.data_ptr(), d_o.data_ptr(), 40, 52, 1, 6, stream)
+    first = d_o.cpu().numpy().copy()
+    xc.run_device_f64("one_to_many", d_l.data_ptr(), d_r.data_ptr(), d_o.data_ptr(), 40, 52, 1, 6, stream)
+    assert np.array_equal(first, d_o.cpu().numpy())
+    assert np.abs(first - want).max() <= F64_TOL * np.abs(want).max()
+    with pytest.raises(xc.XcorrError) as e:
+        xc.run_host_f64("n_to_mn", np.zeros((3, 4, 4)), np.zeros((4, 4, 4)))
+    assert e.value.status == 2
+    assert xc.lib().xcorr_run_f64(0, None, None, None, 4, 4, 1, 1, None) == 1
+    xc.check_device()
+
+
 def test_launch_bookkeeping(xc):
     left, right = seeded_inputs(16, 16, 1, 1, 2)
     xc.reset_launch_count()
