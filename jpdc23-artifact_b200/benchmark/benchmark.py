@@ -195,7 +195,10 @@ def read_times(path: Path) -> dict[str, float]:
     for j, label in enumerate(rows[0]):
         if label.endswith("_iterations"):
             continue
-        vals = [float(r[j]) for r in rows[1:] if j < len(r) and r[j] != ""]
+        try:
+            vals = [float(r[j]) for r in rows[1:] if j < len(r) and r[j] != ""]
+        except ValueError:               # a property column of the algorithm (e.g. a distribution name)
+            continue
         if vals:
             cols[label] = sum(vals) / len(vals)
     return cols
