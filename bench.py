@@ -527,6 +527,41 @@ def workload_config(n_gpus):
 
 
 # ---- our arm -------------------------------------------------------------------------------------------
+def bind_to_gpu_numa_node(device_index):
+    """Pins this process to the CPUs of the NUMA node its GPU hangs off, before any page-locked
+    buffer is allocated: with several ranks per host the device -> host copies of a rank then
+    land in memory next to its GPU instead of crossing the socket link.  Returns what was done
+    (for the JSON line); any missing piece (no NVML, no sysfs entry, one node) leaves the
+    affinity as it is."""
+    info = {"numa_node": None}
+    try:
+        import pynvml
+        import torch
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        if not uuid.startswith("GPU-"):
+            uuid = "GPU-" + uuid
+        handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        bus = pynvml.nvmlDeviceGetPciInfo(handle).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        domain, rest = bus.lower().split(":", 1)
+        path = f"/sys/bus/pci/devices/{domain[-4:]}:{rest}/numa_node"
+        node = int(open(path).read().strip())
+        info["numa_node"] = node
+        if node >= 0:
+            cpus = set()
+            for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            cpus &= os.sched_getaffinity(0)
+            if cpus:
+                os.sched_setaffinity(0, cpus)
+                info["cpus"] = len(cpus)
+    except Exception as e:                      # noqa: BLE001 -- best effort, never fatal
+        info["note"] = f"{type(e).__name__}: {e}"[:120]
+    return info
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -658,6 +693,8 @@ def main():
             strong_ms[k] = a.elapsed_time(b) / args.steps
 
     # ---- end to end through the host-buffer entry point (pinned host memory both ways)
+    original_affinity = os.sched_getaffinity(0)
+    host_affinity = bind_to_gpu_numa_node(local_rank)      # page-locked buffers next to this rank's GPU
     host = {}
     for k, (mode, r, c, nl, nr) in CONFIGS.items():
         left, right = config_inputs(k, rank)
@@ -705,6 +742,7 @@ def main():
     checksum = float(host[last][2].reshape(-1)[0])   # a device result read on the host
     barrier()
 
+    os.sched_setaffinity(0, original_affinity)             # the CPU baseline uses every core again
     xc.check_device()          # no failed launch, no bounded device-side wait that gave up
 
     # ---- FFMA peak of this GPU, measured now
@@ -784,7 +822,7 @@ def main():
                     "per_call": {"value": world * flop_step / (e2e_percall_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                                  "ms_per_step": e2e_percall_ms,
                                  "api": "xcorr_run_host_f32, one call per configuration"},
-                    "result_probe": checksum},
+                    "host_affinity": host_affinity, "result_probe": checksum},
             "gpu_launches": int(launches),
         }
         if world == 1 and not args.no_extras:
