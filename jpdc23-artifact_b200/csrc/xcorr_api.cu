@@ -1027,9 +1027,12 @@ xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_r
     PairMap pm{};
     xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
     if (st != XCORR_OK) return st;
+    DeviceInfo dev;
+    if ((st = current_device_info(&dev)) != XCORR_OK) return st;
     dim3 g, b;
     XC_CUDA(launch_strip_f64(d_left, d_right, d_out, (int)rows, (int)cols, pm,
-                             (unsigned long long)pm.n_left * pm.m, &g, &b, static_cast<cudaStream_t>(stream)));
+                             (unsigned long long)pm.n_left * pm.m, dev.sm_count, &g, &b,
+                             static_cast<cudaStream_t>(stream)));
     char buf[128];
     std::snprintf(buf, sizeof buf, "kernel=strip_f64 grid=(%u,1,1) block=(%u,1,1) smem=0", g.x, b.x);
     t_last_launch = buf;

@@ -20,7 +20,8 @@ cudaError_t launch_warp_per_overlap(const float* left, const float* right, float
 cudaError_t tile_stage_timeouts(unsigned* count);
 // Double precision (xcorr_f64.cu): one warp per 8 output rows x 32 output columns of a pair.
 cudaError_t launch_strip_f64(const double* left, const double* right, double* out, int H, int W, PairMap pm,
-                             unsigned long long npairs, dim3* grid_out, dim3* block_out, cudaStream_t stream);
+                             unsigned long long npairs, int sm_count, dim3* grid_out, dim3* block_out,
+                             cudaStream_t stream);
 cudaError_t launch_dfma_probe(double* sink, int iters, int blocks, cudaStream_t stream);
 cudaError_t launch_ffma_probe(float* sink, int iters, int blocks, cudaStream_t stream);
 
