@@ -1,15 +1,15 @@
 // Double-precision direct cross-correlation (the reference stubs `--data_type double` out,
 // main.cpp:433-434, and comments out every <double> instantiation, e.g. naive_shuffle.cu:545-552).
 //
-// Column-strip kernel: a warp owns 32 consecutive output columns of RT consecutive output rows
-// of one pair.  For every right column x it walks down the right rows; the RT left values that
-// meet right row y in the RT output rows form a window that slides down one left row per step,
-// so a step costs one left load (coalesced over the lanes' 32 shifts), one right load (one
-// address for the whole warp) and RT DFMA.  The loop over y is unrolled RT times so that the
-// window rotates through fixed registers.  Loads outside a matrix are predicated to zero; the x
-// range is the union over the warp's lanes and the y range the union over its RT rows.
-// FP64 runs at half the FP32 lane count on this part (64 lanes per SM and clock), so the
-// two loads per RT DFMA stay under the load/store bandwidth for RT = 8.
+// Column-strip kernel: a warp owns 32 column classes (two result columns each, see the kernel)
+// of RT consecutive result rows of one pair.  For every right column x it walks down the right
+// rows; the RT left values that meet right row y in the RT result rows form a window that slides
+// down one left row per step, so a step costs one left load (coalesced over the lanes), one right
+// load (one address for the whole warp) and RT DFMA.  The loop over y is unrolled RT times so
+// that the window rotates through fixed registers.  Every lane has work at every x (the column
+// classes are circular); the y range is the union over the RT rows, with a checked tail where the
+// window leaves the left matrix.  FP64 runs at half the FP32 lane count on this part (64 lanes per
+// SM and clock), so the two loads per RT DFMA stay under the load/store bandwidth for RT = 8.
 #include "xcorr_launch.h"
 
 namespace xcorr {
@@ -35,26 +35,34 @@ strip_f64_kernel(const double* __restrict__ left, const double* __restrict__ rig
     const double* L = left + l * (size_t)H * W;
     const double* R = right + (l * pm.right_stride + j) * (size_t)H * W;
 
-    const int oy0 = rt * kRT, ox = ct * 32 + lane;
-    const int sy0 = oy0 - (H - 1), sx = ox - (W - 1);
-    // right columns any lane of the warp needs, right rows any of the RT output rows needs
-    const int sx_lo = ct * 32 - (W - 1);
-    const int sx_hi = min(ct * 32 + 31, OW - 1) - (W - 1);
-    const int xa = max(0, -sx_hi), xb = min(W, W - sx_lo);
-    const int ya = max(0, -(sy0 + kRT - 1)), yb = min(H, H - sy0);
+    // Column classes: lane c owns result columns c (shift c - (W-1) <= 0, met by right columns
+    // x >= W-1-c) and c + W (shift c + 1 > 0, met by x < W-1-c).  Both read left column
+    // (x + c + 1) mod W, so walking x = 0 .. W-1 every lane has a left element at every step:
+    // first the sum of column c + W, stored when x reaches W-1-c, then the sum of column c.
+    const int oy0 = rt * kRT, c = ct * 32 + lane;
+    const int sy0 = oy0 - (H - 1);
+    const int split = W - 1 - c;
+    const int ya = max(0, -(sy0 + kRT - 1)), yb = min(H, H - sy0);    // right rows any of the RT result rows needs
+    // right rows whose newest left row (y + sy0 + RT - 1) is inside the left matrix: no checks there
+    const int y_in = min(yb, H - sy0 - (kRT - 1));
+    const size_t rowW = (size_t)W;
+    double* const o = out + pair * (size_t)OW * OH + (size_t)oy0 * OW + c;
 
     double acc[kRT];
 #pragma unroll
     for (int k = 0; k < kRT; ++k) acc[k] = 0.0;
 
-    // right rows whose newest left row (y + sy0 + RT - 1) is inside the left matrix: no checks there
-    const int y_in = min(yb, H - sy0 - (kRT - 1));
-    const size_t rowW = (size_t)W;
-    for (int x = xa; x < xb; ++x) {
-        const int lx = x + sx;
-        // lanes whose shift has no left element over this right column sit the column out (the
-        // loop bounds below are the same for every lane, so they rejoin at its end)
-        if (ox < OW && lx >= 0 && lx < W) {
+    if (c < W) {                      // (a ragged last column tile; loop bounds below are warp-uniform)
+        for (int x = 0; x < W; ++x) {
+            if (x == split && split > 0) {          // one lane per step: column c + W is complete
+#pragma unroll
+                for (int k = 0; k < kRT; ++k) {
+                    if (oy0 + k < OH) o[(size_t)k * OW + W] = acc[k];
+                    acc[k] = 0.0;
+                }
+            }
+            int lx = x + c + 1;
+            if (lx >= W) lx -= W;
             double w[kRT];
             // window at y = ya: left rows ya + sy0 + k, k = 0 .. RT-2 (the last one is loaded in the loop)
 #pragma unroll
@@ -90,9 +98,6 @@ strip_f64_kernel(const double* __restrict__ left, const double* __restrict__ rig
                 }
             }
         }
-    }
-    if (ox < OW) {
-        double* o = out + pair * (size_t)OW * OH + (size_t)oy0 * OW + ox;
 #pragma unroll
         for (int k = 0; k < kRT; ++k)
             if (oy0 + k < OH) o[(size_t)k * OW] = acc[k];
@@ -126,11 +131,13 @@ cudaError_t launch_dfma_probe(double* sink, int iters, int blocks, cudaStream_t 
 cudaError_t launch_strip_f64(const double* left, const double* right, double* out, int H, int W, PairMap pm,
                              unsigned long long npairs, int sm_count, dim3* grid_out, dim3* block_out,
                              cudaStream_t stream) {
-    const int OW = 2 * W - 1, OH = 2 * H - 1;
-    const int row_tiles = (OH + kRT - 1) / kRT, col_tiles = (OW + 31) / 32;
+    const int OH = 2 * H - 1;
+    const int row_tiles = (OH + kRT - 1) / kRT, col_tiles = (W + 31) / 32;     // column classes, 32 per warp
     const unsigned long long ntasks = npairs * row_tiles * col_tiles;
     // (smaller blocks for few tasks were tried: one 256 x 256 pair ran 3.4 ms in 1-warp blocks
     // against 2.3 ms in blocks of 8 neighbouring row tiles, which share their rows in L1)
+    // (smaller blocks for few tasks were tried twice: one 256 x 256 pair ran 3.4 - 3.7 ms in 1- and
+    // 2-warp blocks against 2.4 ms in blocks of 8 neighbouring row tiles, which share rows in L1)
     (void)sm_count;
     const int warps = kStripWarps;
     const unsigned long long blocks = (ntasks + warps - 1) / warps;
