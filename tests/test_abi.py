@@ -170,6 +170,9 @@ def test_header_is_plain_c(xc, tmp_path):
     src = tmp_path / "t.c"
     src.write_text('#include <stdio.h>\n#include "xcorr.h"\n'
                    'int main(void) { xcorr_hints h = {0}; unsigned first = 0, count = 0; (void)h;\n'
+                   '  float buf[16] = {0};\n'
+                   '  xcorr_host_job jobs[1] = { { XCORR_N_TO_MN, 2, 2, 3, 4, buf, buf, buf, NULL } };\n'
+                   '  if (xcorr_run_host_batch_f32(jobs, 1, 0) != XCORR_ERR_INVALID_SIZE) return 3;  /* 4 rights, 3 lefts */\n'
                    '  xcorr_shard_range(10, 3, 1, &first, &count);\n'
                    '  printf("%u %u %llu %s\\n", first, count, (unsigned long long)xcorr_num_results(XCORR_N_TO_M, 3, 4),\n'
                    '         xcorr_status_string(XCORR_ERR_WORKSPACE)); return 0; }\n')
