@@ -56,7 +56,9 @@ typedef enum xcorr_status {
     XCORR_ERR_CUDA = 5,              /* a CUDA runtime call failed; see xcorr_last_error_string() */
     XCORR_ERR_UNSUPPORTED = 6,       /* shape needs more shared memory than one SM has */
     XCORR_ERR_DEVICE = 7,            /* bad device index / no usable device for the sharded runner */
-    XCORR_ERR_TIMEOUT = 8            /* a bounded device-side wait gave up */
+    XCORR_ERR_TIMEOUT = 8,           /* a bounded device-side wait gave up */
+    XCORR_ERR_INTERNAL = 9           /* host-side failure inside the library (out of host memory, a thread
+                                        could not be started): caught at this boundary, never thrown across it */
 } xcorr_status;
 
 typedef enum xcorr_mode {
@@ -73,10 +75,22 @@ typedef enum xcorr_kernel {
     XCORR_KERNEL_TILE = 1,          /* register-tiled circular-class kernel (the fast path) */
     XCORR_KERNEL_OVERLAP_WISE = 2,  /* one thread per overlap -- run_cross_corr_naive_original, naive_original.cu:131-161 */
     XCORR_KERNEL_WARP_PER_OVERLAP = 3, /* one warp per overlap -- run_ccn_warp_per_shift, naive_warp_per_shift.cu:308-335 */
-    XCORR_KERNEL_FFT = 4            /* the cuFFT path (xcorr_fft_f32 with the normalized layout); needs the
+    XCORR_KERNEL_FFT = 4,           /* the cuFFT path (xcorr_fft_f32 with the normalized layout); needs the
                                        workspace xcorr_workspace_bytes() reports for this hint.  Never chosen
                                        automatically: its rounding differs from the direct path's */
+    XCORR_KERNEL_WARP_STAGED = 5    /* one warp per overlap, operands staged through shared memory --
+                                       run_ccn_warp_per_shift_shared_mem, naive_warp_per_shift_shared_mem.cu:392-496.
+                                       The automatic choice for a handful of overlaps (a 16 x 16 pair) */
 } xcorr_kernel;
+
+/* How the rows of one overlap are shared by several warps of the plain warp-per-overlap kernel
+ * (row_distribution.cuh:34-284; the sums are added atomically onto the output, which the library
+ * zeroes first). */
+typedef enum xcorr_row_split {
+    XCORR_SPLIT_NONE = 0,        /* one warp per overlap */
+    XCORR_SPLIT_RECTANGLE = 1,   /* every output row gets the worker slots of the centre row; surplus ones return */
+    XCORR_SPLIT_TRIANGLE = 2     /* exactly the workers each output row needs */
+} xcorr_row_split;
 
 /* How partial sums of a row-split launch are combined (the reference's "work
  * distribution" kernels always use atomicAdd on a caller-zeroed buffer,
@@ -102,7 +116,8 @@ typedef struct xcorr_hints {
     int32_t warps_x;           /* TILE: warps of a block along x-class tiles (cf. warps_per_thread_block) */
     int32_t warps_y;           /* TILE: warps of a block along y-class groups */
     int32_t row_slices;        /* TILE: number of slices the right rows are split into (cf. rows_per_thread) */
-    int32_t block_threads;     /* OVERLAP_WISE / WARP_PER_OVERLAP: threads per block */
+    int32_t block_threads;     /* OVERLAP_WISE / WARP_PER_OVERLAP / WARP_STAGED: threads per block; for the two
+                                  warp families 32 * shifts_per_thread_block (a warp per overlap) */
     int32_t schedule;          /* TILE: how work reaches the blocks.  0 auto;
                                   1 static: one block per block task (and row slice);
                                   2 stream-K: the (block task, right row) units of all tasks are cut evenly
@@ -128,7 +143,18 @@ typedef struct xcorr_hints {
                                   for small inputs may add many parts atomically, like the reference's
                                   "work distribution" kernels.  The environment variable
                                   XCORR_REPRODUCIBLE=1 sets it for every call of the process */
-    int32_t reserved[5];
+    int32_t rows_per_warp;     /* WARP_PER_OVERLAP with row_split != 0: most rows of an overlap one warp sums
+                                  (cf. rows_per_warp of nai_warp_per_shift_work_distribution_one_to_one) */
+    int32_t row_split;         /* WARP_PER_OVERLAP: xcorr_row_split (cf. distribution_type) */
+    int32_t staged_rows;       /* WARP_STAGED: right rows per shared-memory slab (cf. shared_mem_rows); 0 auto */
+    int32_t staged_cols;       /* WARP_STAGED: columns per slab (cf. shared_mem_row_size); 0 auto */
+    int32_t staged_rights;     /* WARP_STAGED: right matrices a block takes together, 1..8
+                                  (cf. right_matrices_per_block); 0 auto */
+    int32_t staged_column_groups; /* WARP_STAGED: 1 = every column slab is a block of its own and the sums are
+                                  added atomically onto the zeroed output (cf. column_group_per_block) */
+    int32_t staged_warp_rows;  /* WARP_STAGED: how the slab is copied: 0 = the block's threads stride over its
+                                  elements, 1 = one warp per row (cf. strided_load = true / false) */
+    int32_t reserved[2];
 } xcorr_hints;
 
 /* ---- device-pointer entry points ------------------------------------------------------
@@ -145,7 +171,7 @@ typedef struct xcorr_hints {
  * run_ccn_warp_per_shift (kernels.cuh:98-106).  The search size is always the full
  * (2*cols-1, 2*rows-1), which is what every reference caller passes.
  * `workspace` may be NULL unless the chosen plan combines through the workspace
- * (see xcorr_workspace_bytes); it must be 256-byte aligned. */
+ * (see xcorr_workspace_bytes); it must be 16-byte aligned (any cudaMalloc pointer is). */
 XCORR_API xcorr_status xcorr_one_to_one_f32(const float* d_left, const float* d_right, float* d_out,
                                             uint32_t rows, uint32_t cols,
                                             const xcorr_hints* hints,
@@ -179,17 +205,27 @@ XCORR_API xcorr_status xcorr_n_to_m_f32(const float* d_left, const float* d_righ
  *
  *  - The array holds xcorr_noalloc_scratch_bytes() = 32 MiB and exists on every GPU that loads the
  *    library, from load to process exit, whether this entry point is used or not.
- *  - Results of more than 32 MiB, i.e. (2*rows-1)*(2*cols-1) > 8 Mi floats (inputs beyond about
- *    1024 x 1024), are refused with XCORR_ERR_UNSUPPORTED and a message naming the limit.
+ *  - Size limit: the result must fit the array once, (2*rows-1)*(2*cols-1) <= 8 Mi floats (square
+ *    inputs up to 1448 x 1448).  Larger inputs are refused with XCORR_ERR_UNSUPPORTED and a message
+ *    that names the limit.
+ *  - Within the limit there are two ways the partial results are combined.  Inputs whose row
+ *    slices fit the array AND one SM's shared memory (square inputs up to about 448 x 448) are
+ *    summed through the array in a fixed order: bit-reproducible.  Larger ones need more, finer
+ *    slices than the array holds; they are added onto the zeroed result with atomic adds instead
+ *    (cudaMemsetAsync + red.global.add, still nothing allocated): the last bits of such a result
+ *    can differ from run to run.  Inputs too wide for any slice (more than about 1700 columns)
+ *    take the overlap-wise kernel, which needs no scratch.  xcorr_last_launch_string() says which.
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
- *    keeps it; make that first call before any stream capture starts on the device.
+ *    keeps it; make that first call before any stream capture starts on the device.  The address
+ *    belongs to the device's context: after cudaDeviceReset (or any teardown of the primary
+ *    context) call xcorr_release_host_cache(), which also forgets the kept addresses.
  *  - All calls share the array, and it keeps what the last call left in it.  Nothing has to be
  *    cleared between calls -- every word the summation reads was written earlier in the same
  *    call -- but two calls that overlap on one GPU (different streams, different threads) race on
  *    it: issue them on one stream or otherwise order them.
  *  - Calls no cudaMalloc / cudaFree and no allocating library routine; asynchronous on `stream`
- *    like the other device entry points; the result equals xcorr_one_to_one_f32 with
- *    combine = workspace up to the float rounding of a possibly different number of row slices. */
+ *    like the other device entry points; the result equals xcorr_one_to_one_f32 up to the float
+ *    rounding of a possibly different number of row slices. */
 XCORR_API xcorr_status xcorr_one_to_one_noalloc_f32(const float* d_left, const float* d_right, float* d_out,
                                                     uint32_t rows, uint32_t cols, void* stream);
 XCORR_API size_t xcorr_noalloc_scratch_bytes(void);
@@ -238,7 +274,10 @@ XCORR_API int32_t xcorr_validate_input_size(int32_t mode, uint32_t rows, uint32_
  *   leaves it -- shift (sy, sx) at row sy mod 2*rows, column sx mod 2*cols, times 4*rows*cols:
  *   what the reference's fft classes hold in results() and write without --normalize.
  * The workspace (xcorr_fft_workspace_bytes) is required.  cuFFT plans are created on first use
- * of a (size, batch) and cached; xcorr_fft_release_plans() destroys them. */
+ * of a (device, size, batch) and cached; xcorr_fft_release_plans() destroys them.  A cached plan
+ * owns one cuFFT work area: calls of the same shape on the same device must be ordered on one
+ * stream (or otherwise not overlap on the GPU) -- unlike the direct entry points, which may run
+ * concurrently on different streams with their own workspaces. */
 typedef enum xcorr_fft_layout { XCORR_FFT_NORMALIZED = 0, XCORR_FFT_RAW = 1 } xcorr_fft_layout;
 
 XCORR_API size_t xcorr_fft_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols,
@@ -252,8 +291,9 @@ XCORR_API void xcorr_fft_release_plans(void);
  * The reference's whole computation step for one algorithm object: prepare (cudaMalloc),
  * transfer (H2D), run, finalize (D2H), free -- main.cpp:123-174, one_to_one.hpp:112-135 and
  * the other modes' naive_gpu_* classes.  Host pointers in, host result out; synchronous.
- * Device buffers are cached per device and reused across calls.  n_to_mn takes and
- * returns GROUPED order like the device entry point.
+ * Device buffers are cached per device and reused across calls; the caller's current device
+ * is the same after the call as before it.  n_to_mn takes and returns GROUPED order like the
+ * device entry point.
  * Results of more than a few MB are produced in pieces (blocks of right matrices for
  * one_to_many, of left matrices for n_to_m / n_to_mn; hints->host_chunks) on three streams,
  * so that the result copy of one piece runs under the kernel of the next and the input copy
@@ -317,7 +357,9 @@ XCORR_API xcorr_status xcorr_run_host_sharded_f32(int32_t mode, const float* h_l
 XCORR_API void xcorr_shard_range(uint32_t units, int32_t parts, int32_t index,
                                  uint32_t* first, uint32_t* count);
 
-/* Release the cached device buffers of xcorr_run_host*_f32 (all devices). */
+/* Release the cached device buffers of xcorr_run_host*_f32 (all devices) and forget the device
+ * addresses xcorr_one_to_one_noalloc_f32 keeps.  Call it before cudaDeviceReset, or after any
+ * teardown of a device's primary context: the library keeps nothing else that a reset makes stale. */
 XCORR_API void xcorr_release_host_cache(void);
 
 /* ---- n_to_mn order helpers (host memory) -------------------------------------------------
@@ -341,11 +383,22 @@ XCORR_API uint64_t xcorr_launch_count(void);
 XCORR_API void xcorr_reset_launch_count(void);
 
 /* Health of the current device as this library sees it: synchronises the device, then returns
- * XCORR_ERR_CUDA if an earlier launch failed, XCORR_ERR_TIMEOUT if any bounded device-side
- * wait of the library's kernels gave up since the library was loaded (the results of such a
- * launch are invalid; the count is in xcorr_last_error_string()), else XCORR_OK.  Stands in
- * for the CUCH(cudaDeviceSynchronize()); CUCH(cudaGetLastError()) pair of main.cpp:267-270. */
+ * XCORR_ERR_CUDA if an earlier launch failed, XCORR_ERR_TIMEOUT if a bounded device-side wait of
+ * the library's kernels gave up since the last call of this function (the blocks concerned
+ * dropped their work and returned, so results of launches since then are incomplete; the count
+ * is in xcorr_last_error_string() and is cleared by this call, the context stays usable), else
+ * XCORR_OK.  Stands in for the CUCH(cudaDeviceSynchronize()); CUCH(cudaGetLastError()) pair of
+ * main.cpp:267-270. */
 XCORR_API xcorr_status xcorr_check_device(void);
+
+/* Test hook for the one device-side wait of the library (a block of the tile kernel waiting for
+ * its bulk copies into shared memory).  poll_limit > 0 replaces the number of polls after which
+ * the wait gives up (default about 4 million); surplus_bytes > 0 makes every block announce that
+ * many bytes more than its copies deliver, so the wait cannot succeed and runs out: the launch
+ * then reports XCORR_ERR_TIMEOUT through xcorr_check_device without any fault, hang or lost
+ * context (the block takes the surplus back and lets its real copies land before it returns).
+ * (0, 0) restores normal operation.  Process-wide; affects launches made after the call. */
+XCORR_API void xcorr_debug_stage_wait(uint32_t poll_limit, uint32_t surplus_bytes);
 
 /* Measured FP32 FFMA throughput of the current device in FLOP/s: a dependency-free
  * register-only FFMA kernel on every SM, timed with CUDA events on `stream`

@@ -26,7 +26,8 @@ CROSS_PATH = os.path.join(PKG_DIR, "bin", "cross")
 HEADER_PATH = os.path.join(os.path.dirname(PKG_DIR), "include", "xcorr.h")
 
 MODES = {"one_to_one": 0, "one_to_many": 1, "n_to_mn": 2, "n_to_m": 3}
-KERNELS = {"auto": 0, "tile": 1, "overlap_wise": 2, "warp_per_overlap": 3, "fft": 4}
+KERNELS = {"auto": 0, "tile": 1, "overlap_wise": 2, "warp_per_overlap": 3, "fft": 4, "warp_staged": 5}
+ROW_SPLIT = {"none": 0, "rectangle": 1, "triangle": 2}
 COMBINE = {"auto": 0, "store": 1, "atomic": 2, "workspace": 3}
 
 
@@ -42,7 +43,10 @@ class Hints(C.Structure):
         ("kernel", C.c_int32), ("combine", C.c_int32), ("overlap_rows", C.c_int32),
         ("class_lanes", C.c_int32), ("warps_x", C.c_int32), ("warps_y", C.c_int32),
         ("row_slices", C.c_int32), ("block_threads", C.c_int32), ("schedule", C.c_int32),
-        ("host_chunks", C.c_int32), ("reproducible", C.c_int32), ("reserved", C.c_int32 * 5),
+        ("host_chunks", C.c_int32), ("reproducible", C.c_int32),
+        ("rows_per_warp", C.c_int32), ("row_split", C.c_int32), ("staged_rows", C.c_int32),
+        ("staged_cols", C.c_int32), ("staged_rights", C.c_int32), ("staged_column_groups", C.c_int32),
+        ("staged_warp_rows", C.c_int32), ("reserved", C.c_int32 * 2),
     ]
 
 
@@ -57,7 +61,9 @@ class HostJob(C.Structure):
 
 
 def make_hints(kernel="auto", combine="auto", overlap_rows=0, class_lanes=0, warps_x=0, warps_y=0,
-               row_slices=0, block_threads=0, schedule=0, host_chunks=0, reproducible=0) -> Hints:
+               row_slices=0, block_threads=0, schedule=0, host_chunks=0, reproducible=0,
+               rows_per_warp=0, row_split="none", staged_rows=0, staged_cols=0, staged_rights=0,
+               staged_column_groups=0, staged_warp_rows=0) -> Hints:
     h = Hints()
     h.kernel = KERNELS[kernel] if isinstance(kernel, str) else int(kernel)
     h.combine = COMBINE[combine] if isinstance(combine, str) else int(combine)
@@ -66,6 +72,10 @@ def make_hints(kernel="auto", combine="auto", overlap_rows=0, class_lanes=0, war
     h.schedule = schedule
     h.host_chunks = host_chunks
     h.reproducible = reproducible
+    h.rows_per_warp = rows_per_warp
+    h.row_split = ROW_SPLIT[row_split] if isinstance(row_split, str) else int(row_split)
+    h.staged_rows, h.staged_cols, h.staged_rights = staged_rows, staged_cols, staged_rights
+    h.staged_column_groups, h.staged_warp_rows = staged_column_groups, staged_warp_rows
     return h
 
 
@@ -131,6 +141,8 @@ def lib() -> C.CDLL:
     L.xcorr_fft_workspace_bytes.restype = sz
     L.xcorr_fft_f32.argtypes = [i32, vp, vp, vp, u32, u32, u32, u32, i32, vp, sz, vp]
     L.xcorr_check_device.argtypes = []
+    L.xcorr_debug_stage_wait.argtypes = [u32, u32]
+    L.xcorr_debug_stage_wait.restype = None
     L.xcorr_fft_release_plans.argtypes = []
     L.xcorr_fft_release_plans.restype = None
     _lib = L

@@ -43,6 +43,37 @@ xcorr_status cuda_fail(cudaError_t e, const char* what) {
         if (e__ != cudaSuccess) return cuda_fail(e__, #call);   \
     } while (0)
 
+// Nothing is thrown across the C boundary: the entry points build strings and vectors and start
+// threads, so every body that can do so runs inside this.
+template<typename F>
+xcorr_status guarded(F&& body) noexcept {
+    try {
+        return body();
+    } catch (const std::bad_alloc&) {
+        try { t_last_error = "out of host memory inside the library"; } catch (...) {}
+        return XCORR_ERR_INTERNAL;
+    } catch (const std::exception& e) {
+        try { t_last_error = std::string("host-side failure inside the library: ") + e.what(); } catch (...) {}
+        return XCORR_ERR_INTERNAL;
+    } catch (...) {
+        try { t_last_error = "host-side failure inside the library"; } catch (...) {}
+        return XCORR_ERR_INTERNAL;
+    }
+}
+
+// Restores the caller's current device when an entry point that switches devices returns.
+struct DeviceGuard {
+    int prev = -1;
+    DeviceGuard() { if (cudaGetDevice(&prev) != cudaSuccess) { (void)cudaGetLastError(); prev = -1; } }
+    ~DeviceGuard() { if (prev >= 0) (void)cudaSetDevice(prev); }
+    DeviceGuard(const DeviceGuard&) = delete;
+    DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+
+// xcorr_debug_stage_wait: bound and surplus of the tile kernel's staging wait (test hook).
+std::atomic<unsigned> g_stage_wait_limit{kStageWaitLimit};
+std::atomic<unsigned> g_stage_expect_surplus{0};
+
 struct DeviceInfo {
     int sm_count = 0;
     size_t smem_optin = 0;
@@ -477,12 +508,11 @@ int pick_kernel(const xcorr_hints* h) {
 }
 
 // The automatic choice for a handful of overlaps (one 16 x 16 pair has 961): one warp per
-// overlap, a single launch without staging -- 6 us of GPU time against 10 us of the best tile
-// plan (measured by graph replay on B200; from 24 x 24 on the tile kernel is faster).  Not for
-// callers who asked for reproducible or otherwise specific plans.
+// overlap with the operands staged in shared memory, a single wave of blocks -- the latency
+// kernel.  Not for callers who asked for specific plans.
 bool tiny_auto(const xcorr_hints* h, const PairMap& pm, uint32_t rows, uint32_t cols) {
     if (h && (h->kernel != XCORR_KERNEL_AUTO || h->combine || h->overlap_rows || h->class_lanes || h->warps_x ||
-              h->warps_y || h->row_slices || h->schedule || h->block_threads))
+              h->warps_y || h->row_slices || h->schedule || h->block_threads || h->reproducible))
         return false;
     return (double)pm.n_left * pm.m * (2.0 * rows - 1) * (2.0 * cols - 1) <= 1500.0;
 }
@@ -494,6 +524,38 @@ xcorr_status check_sizes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_
     if (!pair_map(mode, n_left, n_right, pm))
         return fail(XCORR_ERR_INVALID_SIZE, "matrix counts do not fit the mode "
                     "(one_to_one 1x1, one_to_many 1xN, n_to_mn N x k*N, n_to_m NxM)");
+    return XCORR_OK;
+}
+
+// Arguments of the staged warp-per-overlap kernel from the hints (0 = automatic).  The reference
+// requires shared_mem_rows >= shifts_per_thread_block (one_to_one.hpp:573-586); this kernel
+// takes any slab height.
+xcorr_status staged_args(const PairMap& pm, int H, int W, const xcorr_hints* h, const DeviceInfo& dev, StagedArgs* out) {
+    StagedArgs a{};
+    a.H = H; a.W = W; a.pm = pm;
+    const int bt = h ? h->block_threads : 0;
+    if (bt != 0 && (bt < 32 || bt > 1024 || bt % 32 != 0))
+        return fail(XCORR_ERR_INVALID_HINT, "block_threads must be a multiple of 32 in 32..1024");
+    a.shifts = bt ? bt / 32 : 8;
+    const int want_rows = h ? h->staged_rows : 0, want_cols = h ? h->staged_cols : 0, want_r = h ? h->staged_rights : 0;
+    if (want_rows < 0 || want_cols < 0 || want_r < 0 || want_r > 8)
+        return fail(XCORR_ERR_INVALID_HINT, "staged_rows / staged_cols must be positive, staged_rights 1..8 (0 = automatic)");
+    a.scols = std::min(want_cols ? want_cols : 32, W);
+    a.srows = std::min(want_rows ? want_rows : std::max(a.shifts, 32), H);
+    a.rights = (int)std::min<uint32_t>((uint32_t)(want_r ? want_r : 8), pm.m);
+    a.col_groups = h && h->staged_column_groups ? 1 : 0;
+    a.warp_rows = h && h->staged_warp_rows ? 1 : 0;
+    a.groups_per_left = (pm.m + (uint32_t)a.rights - 1) / (uint32_t)a.rights;
+    if (staged_smem_bytes(a) > dev.smem_optin) {
+        char msg[200];
+        std::snprintf(msg, sizeof msg, "the staged slabs (2 x (%d + %d - 1 + %d * %d) rows x %d columns) need %zu bytes of "
+                      "shared memory, the device has %zu", a.srows, a.shifts, a.rights, a.srows, a.scols,
+                      staged_smem_bytes(a), dev.smem_optin);
+        return fail(XCORR_ERR_UNSUPPORTED, msg);
+    }
+    if ((unsigned long long)pm.n_left * a.groups_per_left * (2ull * W - 1) > 2147483647ull)
+        return fail(XCORR_ERR_UNSUPPORTED, "too many (left, right group, x shift) blocks for one launch of the staged kernel");
+    *out = a;
     return XCORR_OK;
 }
 
@@ -523,14 +585,15 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
     const unsigned long long npairs = (unsigned long long)pm.n_left * pm.m;
     const unsigned long long total_out = npairs * (2ull * H - 1) * (2ull * W - 1);
     DeviceInfo dev;
-    st = current_device_info(&dev);
+    int device = 0;
+    st = current_device_info(&dev, &device);
     if (st != XCORR_OK) return st;
 
-    const int kernel = tiny_auto(hints, pm, rows, cols) ? (int)XCORR_KERNEL_WARP_PER_OVERLAP : pick_kernel(hints);
+    const int kernel = tiny_auto(hints, pm, rows, cols) ? (int)XCORR_KERNEL_WARP_STAGED : pick_kernel(hints);
     const int bt = hints && hints->block_threads ? hints->block_threads : 256;
     if (bt < 32 || bt > 1024 || bt % 32 != 0)
         return fail(XCORR_ERR_INVALID_HINT, "block_threads must be a multiple of 32 in 32..1024");
-    char buf[256];
+    char buf[320];
     if (kernel == XCORR_KERNEL_OVERLAP_WISE) {
         dim3 g, b;
         XC_CUDA(launch_overlap_wise(d_left, d_right, d_out, H, W, pm, npairs, bt, &g, &b, stream));
@@ -540,9 +603,32 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
         return XCORR_OK;
     }
     if (kernel == XCORR_KERNEL_WARP_PER_OVERLAP) {
+        const int split = hints ? hints->row_split : 0;
+        const int rpw = hints ? hints->rows_per_warp : 0;
+        if (split < 0 || split > 2) return fail(XCORR_ERR_INVALID_HINT, "row_split must be 0 (none), 1 (rectangle) or 2 (triangle)");
+        if (split != XCORR_SPLIT_NONE && rpw <= 0)
+            return fail(XCORR_ERR_INVALID_HINT, "row_split needs rows_per_warp > 0");
         dim3 g, b;
-        XC_CUDA(launch_warp_per_overlap(d_left, d_right, d_out, H, W, pm, npairs, bt, dev.sm_count, &g, &b, stream));
-        std::snprintf(buf, sizeof buf, "kernel=warp_per_overlap grid=(%u,1,1) block=(%u,1,1) smem=0", g.x, b.x);
+        // parts of an overlap are added atomically: the output starts at zero (one_to_one.hpp:503)
+        if (split != XCORR_SPLIT_NONE) XC_CUDA(cudaMemsetAsync(d_out, 0, total_out * sizeof(float), stream));
+        XC_CUDA(launch_warp_per_overlap(d_left, d_right, d_out, H, W, pm, npairs, bt, rpw, split, dev.sm_count, &g, &b, stream));
+        std::snprintf(buf, sizeof buf, "kernel=warp_per_overlap grid=(%u,1,1) block=(%u,1,1) smem=0 split=%s rows_per_warp=%d",
+                      g.x, b.x, split == XCORR_SPLIT_NONE ? "none" : split == XCORR_SPLIT_RECTANGLE ? "rectangle" : "triangle", rpw);
+        t_last_launch = buf;
+        ++t_launch_count;
+        return XCORR_OK;
+    }
+    if (kernel == XCORR_KERNEL_WARP_STAGED) {
+        StagedArgs sa{};
+        if ((st = staged_args(pm, H, W, kernel == pick_kernel(hints) ? hints : nullptr, dev, &sa)) != XCORR_OK) return st;
+        sa.left = d_left; sa.right = d_right; sa.out = d_out;
+        if (sa.col_groups) XC_CUDA(cudaMemsetAsync(d_out, 0, total_out * sizeof(float), stream));
+        dim3 g;
+        size_t smem = 0;
+        XC_CUDA(launch_warp_staged(sa, device, &g, &smem, stream));
+        std::snprintf(buf, sizeof buf, "kernel=warp_staged grid=(%u,%u,%u) block=(%d,1,1) smem=%zu shifts=%d slab=%dx%d rights=%d "
+                      "column_groups=%d loads=%s", g.x, g.y, g.z, sa.shifts * 32, smem, sa.shifts, sa.srows, sa.scols, sa.rights,
+                      sa.col_groups, sa.warp_rows ? "warp-per-row" : "strided");
         t_last_launch = buf;
         ++t_launch_count;
         return XCORR_OK;
@@ -593,9 +679,11 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
     a.p = p; a.pm = pm; a.total_out = total_out;
     a.vec_ok = (W % 4 == 0) && reinterpret_cast<uintptr_t>(d_left) % 16 == 0 &&
                reinterpret_cast<uintptr_t>(d_right) % 16 == 0;
+    a.stage_wait_limit = g_stage_wait_limit.load(std::memory_order_relaxed);
+    a.stage_expect_surplus = g_stage_expect_surplus.load(std::memory_order_relaxed);
     t_last_launch = describe_plan(p);
     if (p.combine == kAtomic) XC_CUDA(cudaMemsetAsync(d_out, 0, total_out * sizeof(float), stream));
-    XC_CUDA(launch_tile(a, stream));
+    XC_CUDA(launch_tile(a, device, stream));
     ++t_launch_count;
     if (p.combine == kWorkspace) {
         XC_CUDA(launch_reduce_partials(a.ws, d_out, total_out, H, W, p.Hp, p.S, dev.sm_count, stream));
@@ -615,36 +703,66 @@ xcorr_status run_one_to_one_noalloc(const float* d_left, const float* d_right, f
     const unsigned long long total_out = (2ull * H - 1) * (2ull * W - 1);
     const size_t limit = noalloc_scratch_bytes();
     if (total_out * sizeof(float) > limit) {
-        char msg[256];
+        char msg[320];
         std::snprintf(msg, sizeof msg,
-                      "a %u x %u pair has a result of %llu bytes; the built-in scratch of the entry point that "
-                      "allocates nothing holds %zu bytes (results up to %zu floats, e.g. 1024 x 1024 inputs)",
+                      "a %u x %u pair has a result of %llu bytes; the entry point that allocates nothing takes results "
+                      "of at most %zu bytes, the size of its built-in scratch array ((2*rows-1)*(2*cols-1) <= %zu "
+                      "floats, e.g. square inputs up to 1448 x 1448)",
                       rows, cols, total_out * 4ull, limit, limit / sizeof(float));
         return fail(XCORR_ERR_UNSUPPORTED, msg);
     }
     DeviceInfo dev;
-    if ((st = current_device_info(&dev)) != XCORR_OK) return st;
+    int device = 0;
+    if ((st = current_device_info(&dev, &device)) != XCORR_OK) return st;
     // the scratch array's device address, looked up once per device with that device current
     float* scratch = nullptr;
     XC_CUDA(noalloc_scratch_address(&scratch));
-    // same kernels and plan space as xcorr_one_to_one_f32 with combine = workspace, the
-    // number of row slices capped by what the scratch array holds
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    // First choice: the kernels and plan space of xcorr_one_to_one_f32 with combine = workspace, the
+    // number of row slices capped by what the scratch array holds.  Large inputs need more, finer
+    // slices than that (a slice must also fit one SM's shared memory): they take the plan that adds
+    // the slices atomically onto the zeroed output, which needs no scratch at all.
     xcorr_hints hints{};
     hints.kernel = XCORR_KERNEL_TILE;
     hints.combine = XCORR_COMBINE_WORKSPACE;
     TilePlan p{};
-    if ((st = plan_tile(pm, H, W, &hints, dev, &p, limit)) != XCORR_OK) return st;
+    st = plan_tile(pm, H, W, &hints, dev, &p, limit);
+    if (st == XCORR_ERR_UNSUPPORTED) {
+        hints.combine = XCORR_COMBINE_AUTO;
+        st = plan_tile(pm, H, W, &hints, dev, &p, limit);
+        if (st == XCORR_OK && (p.combine == kWorkspace || p.combine == kFixup)) {
+            // (the automatic plan only sums through a workspace that fits the cap; kept as a guard)
+            if (p.workspace_bytes > limit) { p.combine = kAtomic; p.workspace_bytes = 0; }
+        }
+    }
+    if (st == XCORR_ERR_UNSUPPORTED) {
+        // rows too wide for any slice in shared memory: one thread per overlap, no scratch
+        dim3 g, b;
+        XC_CUDA(launch_overlap_wise(d_left, d_right, d_out, H, W, pm, 1, 256, &g, &b, stream));
+        char buf[160];
+        std::snprintf(buf, sizeof buf, "kernel=overlap_wise grid=(%u,%u,%u) block=(%u,%u,1) smem=0 (no tile plan fits)",
+                      g.x, g.y, g.z, b.x, b.y);
+        t_last_launch = buf;
+        ++t_launch_count;
+        return XCORR_OK;
+    }
+    if (st != XCORR_OK) return st;
     TileArgs a{};
-    a.left = d_left; a.right = d_right; a.out = d_out; a.ws = scratch;
+    a.left = d_left; a.right = d_right; a.out = d_out;
+    a.ws = p.combine == kWorkspace ? scratch : nullptr;
     a.p = p; a.pm = pm; a.total_out = total_out;
     a.vec_ok = (W % 4 == 0) && reinterpret_cast<uintptr_t>(d_left) % 16 == 0 &&
                reinterpret_cast<uintptr_t>(d_right) % 16 == 0;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    a.stage_wait_limit = g_stage_wait_limit.load(std::memory_order_relaxed);
+    a.stage_expect_surplus = g_stage_expect_surplus.load(std::memory_order_relaxed);
     t_last_launch = describe_plan(p);
-    XC_CUDA(launch_tile(a, stream));
+    if (p.combine == kAtomic) XC_CUDA(cudaMemsetAsync(d_out, 0, total_out * sizeof(float), stream));
+    XC_CUDA(launch_tile(a, device, stream));
     ++t_launch_count;
-    XC_CUDA(launch_reduce_partials(scratch, d_out, total_out, H, W, p.Hp, p.S, dev.sm_count, stream));
-    ++t_launch_count;
+    if (p.combine == kWorkspace) {
+        XC_CUDA(launch_reduce_partials(scratch, d_out, total_out, H, W, p.Hp, p.S, dev.sm_count, stream));
+        ++t_launch_count;
+    }
     return XCORR_OK;
 }
 
@@ -753,6 +871,7 @@ xcorr_status run_host_batch(HostJob* jobs, int n_jobs, int32_t device) {
     int ndev = 0;
     XC_CUDA(cudaGetDeviceCount(&ndev));
     if (device < 0 || device >= ndev || device >= kMaxDevices) return fail(XCORR_ERR_DEVICE, "no such CUDA device");
+    DeviceGuard restore_device;                 // the caller's current device comes back on every return path
     XC_CUDA(cudaSetDevice(device));
     HostCache& c = g_host_cache[device];
     std::lock_guard<std::mutex> lock(c.mutex);
@@ -773,6 +892,9 @@ xcorr_status run_host_batch(HostJob* jobs, int n_jobs, int32_t device) {
 
     std::string plans;
     int piece = 0;
+    // Everything below queues work on the three cached streams.  Whatever fails, what was queued
+    // has to finish before the call returns: the next call may grow (free) the arenas.
+    auto enqueue_all = [&]() -> xcorr_status {
     for (int j = 0; j < n_jobs; ++j) {
         const HostJob& J = jobs[j];
         const int32_t mode = J.mode;
@@ -823,12 +945,8 @@ xcorr_status run_host_batch(HostJob* jobs, int n_jobs, int32_t device) {
             }
             XC_CUDA(cudaEventRecord(c.in_done[piece], c.copy_in));
             XC_CUDA(cudaStreamWaitEvent(c.stream, c.in_done[piece], 0));
-            st = run_device(mode, dl, dr, dout, J.rows, J.cols, nl, nr, J.hints, c.d_ws, c.ws_bytes, c.stream);
-            if (st != XCORR_OK) {
-                // let what was queued finish before the buffers can be reused
-                cudaStreamSynchronize(c.copy_in); cudaStreamSynchronize(c.stream); cudaStreamSynchronize(c.copy_out);
-                return st;
-            }
+            const xcorr_status rst = run_device(mode, dl, dr, dout, J.rows, J.cols, nl, nr, J.hints, c.d_ws, c.ws_bytes, c.stream);
+            if (rst != XCORR_OK) return rst;
             if (i == 0) {
                 if (!plans.empty()) plans += "; ";
                 plans += (J.chunks > 1 ? "host_chunks=" + std::to_string(J.chunks) + " first{" + t_last_launch + "}" : t_last_launch);
@@ -837,6 +955,16 @@ xcorr_status run_host_batch(HostJob* jobs, int n_jobs, int32_t device) {
             XC_CUDA(cudaStreamWaitEvent(c.copy_out, c.run_done[piece], 0));
             XC_CUDA(cudaMemcpyAsync(hout, dout, piece_out, cudaMemcpyDeviceToHost, c.copy_out));
         }
+    }
+    return XCORR_OK;
+    };
+    st = enqueue_all();
+    if (st != XCORR_OK) {
+        const std::string why = t_last_error;
+        (void)cudaStreamSynchronize(c.copy_in); (void)cudaStreamSynchronize(c.stream); (void)cudaStreamSynchronize(c.copy_out);
+        (void)cudaGetLastError();
+        t_last_error = why;
+        return st;
     }
     XC_CUDA(cudaStreamSynchronize(c.copy_out));
     t_last_launch = n_jobs > 1 ? "host_batch=" + std::to_string(n_jobs) + " [" + plans + "]" : plans;
@@ -860,20 +988,26 @@ extern "C" {
 xcorr_status xcorr_run_f32(int32_t mode, const float* d_left, const float* d_right, float* d_out,
                            uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                            const xcorr_hints* hints, void* d_workspace, size_t workspace_bytes, void* stream) {
-    return run_device(mode, d_left, d_right, d_out, rows, cols, n_left, n_right, hints,
-                      d_workspace, workspace_bytes, stream);
+    return guarded([&]() -> xcorr_status {
+        return run_device(mode, d_left, d_right, d_out, rows, cols, n_left, n_right, hints,
+                          d_workspace, workspace_bytes, stream);
+    });
 }
 
 xcorr_status xcorr_one_to_one_f32(const float* d_left, const float* d_right, float* d_out,
                                   uint32_t rows, uint32_t cols, const xcorr_hints* hints,
                                   void* d_workspace, size_t workspace_bytes, void* stream) {
-    return run_device(XCORR_ONE_TO_ONE, d_left, d_right, d_out, rows, cols, 1, 1, hints,
-                      d_workspace, workspace_bytes, stream);
+    return guarded([&]() -> xcorr_status {
+        return run_device(XCORR_ONE_TO_ONE, d_left, d_right, d_out, rows, cols, 1, 1, hints,
+                          d_workspace, workspace_bytes, stream);
+    });
 }
 
 xcorr_status xcorr_one_to_one_noalloc_f32(const float* d_left, const float* d_right, float* d_out,
                                           uint32_t rows, uint32_t cols, void* stream) {
-    return run_one_to_one_noalloc(d_left, d_right, d_out, rows, cols, stream);
+    return guarded([&]() -> xcorr_status {
+        return run_one_to_one_noalloc(d_left, d_right, d_out, rows, cols, stream);
+    });
 }
 
 size_t xcorr_noalloc_scratch_bytes(void) { return noalloc_scratch_bytes(); }
@@ -881,22 +1015,28 @@ size_t xcorr_noalloc_scratch_bytes(void) { return noalloc_scratch_bytes(); }
 xcorr_status xcorr_one_to_many_f32(const float* d_left, const float* d_right, float* d_out,
                                    uint32_t rows, uint32_t cols, uint32_t n_right, const xcorr_hints* hints,
                                    void* d_workspace, size_t workspace_bytes, void* stream) {
-    return run_device(XCORR_ONE_TO_MANY, d_left, d_right, d_out, rows, cols, 1, n_right, hints,
-                      d_workspace, workspace_bytes, stream);
+    return guarded([&]() -> xcorr_status {
+        return run_device(XCORR_ONE_TO_MANY, d_left, d_right, d_out, rows, cols, 1, n_right, hints,
+                          d_workspace, workspace_bytes, stream);
+    });
 }
 
 xcorr_status xcorr_n_to_mn_f32(const float* d_left, const float* d_right, float* d_out,
                                uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                                const xcorr_hints* hints, void* d_workspace, size_t workspace_bytes, void* stream) {
-    return run_device(XCORR_N_TO_MN, d_left, d_right, d_out, rows, cols, n_left, n_right, hints,
-                      d_workspace, workspace_bytes, stream);
+    return guarded([&]() -> xcorr_status {
+        return run_device(XCORR_N_TO_MN, d_left, d_right, d_out, rows, cols, n_left, n_right, hints,
+                          d_workspace, workspace_bytes, stream);
+    });
 }
 
 xcorr_status xcorr_n_to_m_f32(const float* d_left, const float* d_right, float* d_out,
                               uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                               const xcorr_hints* hints, void* d_workspace, size_t workspace_bytes, void* stream) {
-    return run_device(XCORR_N_TO_M, d_left, d_right, d_out, rows, cols, n_left, n_right, hints,
-                      d_workspace, workspace_bytes, stream);
+    return guarded([&]() -> xcorr_status {
+        return run_device(XCORR_N_TO_M, d_left, d_right, d_out, rows, cols, n_left, n_right, hints,
+                          d_workspace, workspace_bytes, stream);
+    });
 }
 
 size_t xcorr_fft_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
@@ -910,50 +1050,55 @@ size_t xcorr_fft_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols, uin
 xcorr_status xcorr_fft_f32(int32_t mode, const float* d_left, const float* d_right, float* d_out,
                            uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                            int32_t layout, void* d_workspace, size_t workspace_bytes, void* stream) {
-    if (!d_left || !d_right || !d_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
-    PairMap pm{};
-    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
-    if (st != XCORR_OK) return st;
-    if (layout != XCORR_FFT_NORMALIZED && layout != XCORR_FFT_RAW)
-        return fail(XCORR_ERR_INVALID_HINT, "layout must be XCORR_FFT_NORMALIZED or XCORR_FFT_RAW");
-    const FftLayout lay = fft_workspace_layout(pm, (int)rows, (int)cols, n_right, layout == XCORR_FFT_RAW);
-    if (!d_workspace || workspace_bytes < lay.total)
-        return fail(XCORR_ERR_WORKSPACE, "the FFT path needs xcorr_fft_workspace_bytes() bytes of workspace");
-    if (reinterpret_cast<uintptr_t>(d_workspace) % 256 != 0)
-        return fail(XCORR_ERR_WORKSPACE, "the FFT workspace must be 256-byte aligned");
-    DeviceInfo dev;
-    int device = 0;
-    if ((st = current_device_info(&dev, &device)) != XCORR_OK) return st;
-    std::string err;
-    int launches = 0;
-    const int rc = fft_run(d_left, d_right, d_out, (int)rows, (int)cols, pm, n_right, layout == XCORR_FFT_RAW,
-                           d_workspace, device, dev.sm_count, static_cast<cudaStream_t>(stream), &err, &launches);
-    t_launch_count += (uint64_t)launches;
-    if (rc != 0) return fail(XCORR_ERR_CUDA, err);
-    char buf[256];
-    std::snprintf(buf, sizeof buf, "kernel=fft transform=%ux%u inputs=%llu pairs=%llu product=%s layout=%s workspace=%zu",
-                  2 * rows, 2 * cols, (unsigned long long)pm.n_left + n_right, (unsigned long long)pm.n_left * pm.m,
-                  lay.product_in_place ? "in-place" : "separate", layout == XCORR_FFT_RAW ? "raw" : "normalized",
-                  lay.total);
-    t_last_launch = buf;
-    return XCORR_OK;
+    return guarded([&]() -> xcorr_status {
+        if (!d_left || !d_right || !d_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+        PairMap pm{};
+        xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+        if (st != XCORR_OK) return st;
+        if (layout != XCORR_FFT_NORMALIZED && layout != XCORR_FFT_RAW)
+            return fail(XCORR_ERR_INVALID_HINT, "layout must be XCORR_FFT_NORMALIZED or XCORR_FFT_RAW");
+        const FftLayout lay = fft_workspace_layout(pm, (int)rows, (int)cols, n_right, layout == XCORR_FFT_RAW);
+        if (!d_workspace || workspace_bytes < lay.total)
+            return fail(XCORR_ERR_WORKSPACE, "the FFT path needs xcorr_fft_workspace_bytes() bytes of workspace");
+        if (reinterpret_cast<uintptr_t>(d_workspace) % 256 != 0)
+            return fail(XCORR_ERR_WORKSPACE, "the FFT workspace must be 256-byte aligned");
+        DeviceInfo dev;
+        int device = 0;
+        if ((st = current_device_info(&dev, &device)) != XCORR_OK) return st;
+        std::string err;
+        int launches = 0;
+        const int rc = fft_run(d_left, d_right, d_out, (int)rows, (int)cols, pm, n_right, layout == XCORR_FFT_RAW,
+                               d_workspace, device, dev.sm_count, static_cast<cudaStream_t>(stream), &err, &launches);
+        t_launch_count += (uint64_t)launches;
+        if (rc != 0) return fail(XCORR_ERR_CUDA, err);
+        char buf[256];
+        std::snprintf(buf, sizeof buf, "kernel=fft transform=%ux%u inputs=%llu pairs=%llu product=%s layout=%s workspace=%zu",
+                      2 * rows, 2 * cols, (unsigned long long)pm.n_left + n_right, (unsigned long long)pm.n_left * pm.m,
+                      lay.product_in_place ? "in-place" : "separate", layout == XCORR_FFT_RAW ? "raw" : "normalized",
+                      lay.total);
+        t_last_launch = buf;
+        return XCORR_OK;
+    });
 }
 
 void xcorr_fft_release_plans(void) { fft_release_plans(); }
 
 xcorr_status xcorr_check_device(void) {
-    XC_CUDA(cudaDeviceSynchronize());
-    XC_CUDA(cudaGetLastError());
-    unsigned timeouts = 0;
-    XC_CUDA(tile_stage_timeouts(&timeouts));
-    if (timeouts != 0)
-        return fail(XCORR_ERR_TIMEOUT, std::to_string(timeouts) + " bounded staging wait(s) of tile_kernel gave up; "
-                    "results of those launches are invalid");
-    return XCORR_OK;
+    return guarded([&]() -> xcorr_status {
+        XC_CUDA(cudaDeviceSynchronize());
+        XC_CUDA(cudaGetLastError());
+        unsigned timeouts = 0;
+        XC_CUDA(tile_stage_timeouts(&timeouts));
+        if (timeouts != 0)
+            return fail(XCORR_ERR_TIMEOUT, std::to_string(timeouts) + " block(s) of tile_kernel gave up a bounded staging wait "
+                        "and dropped their work; results of the launches since the last check are incomplete");
+        return XCORR_OK;
+    });
 }
 
 size_t xcorr_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                              const xcorr_hints* hints) {
+    try {
     PairMap pm{};
     if (check_sizes(mode, rows, cols, n_left, n_right, &pm) != XCORR_OK) return 0;
     if (pick_kernel(hints) == XCORR_KERNEL_FFT)
@@ -968,18 +1113,23 @@ size_t xcorr_workspace_bytes(int32_t mode, uint32_t rows, uint32_t cols, uint32_
     TilePlan p{};
     if (plan_tile(pm, (int)rows, (int)cols, hints, dev, &p) != XCORR_OK) return 0;
     return p.workspace_bytes;
+    } catch (...) {
+        return 0;
+    }
 }
 
 int32_t xcorr_describe_plan(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                             const xcorr_hints* hints, char* buffer, size_t buffer_bytes) {
+    return guarded([&]() -> xcorr_status {
     if (!buffer || buffer_bytes == 0) return fail(XCORR_ERR_NULL_POINTER, "buffer must not be NULL");
     PairMap pm{};
     xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
     if (st != XCORR_OK) return st;
     std::string text;
-    const int kernel = tiny_auto(hints, pm, rows, cols) ? (int)XCORR_KERNEL_WARP_PER_OVERLAP : pick_kernel(hints);
+    const int kernel = tiny_auto(hints, pm, rows, cols) ? (int)XCORR_KERNEL_WARP_STAGED : pick_kernel(hints);
     if (kernel == XCORR_KERNEL_OVERLAP_WISE) text = "kernel=overlap_wise";
     else if (kernel == XCORR_KERNEL_WARP_PER_OVERLAP) text = "kernel=warp_per_overlap";
+    else if (kernel == XCORR_KERNEL_WARP_STAGED) text = "kernel=warp_staged";
     else if (kernel == XCORR_KERNEL_FFT) text = "kernel=fft";
     else if (kernel == XCORR_KERNEL_TILE) {
         DeviceInfo dev;
@@ -1002,6 +1152,7 @@ int32_t xcorr_describe_plan(int32_t mode, uint32_t rows, uint32_t cols, uint32_t
     }
     std::snprintf(buffer, buffer_bytes, "%s", text.c_str());
     return XCORR_OK;
+    });
 }
 
 uint64_t xcorr_num_results(int32_t mode, uint32_t n_left, uint32_t n_right) {
@@ -1018,73 +1169,82 @@ int32_t xcorr_validate_input_size(int32_t mode, uint32_t rows, uint32_t cols, ui
 xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, const float* h_right, float* h_out,
                                 uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                                 const xcorr_hints* hints, int32_t device) {
-    return run_host(mode, h_left, h_right, h_out, rows, cols, n_left, n_right, hints, device);
+    return guarded([&]() -> xcorr_status {
+        return run_host(mode, h_left, h_right, h_out, rows, cols, n_left, n_right, hints, device);
+    });
 }
 
 xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_right, double* d_out,
                            uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right, void* stream) {
-    if (!d_left || !d_right || !d_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
-    PairMap pm{};
-    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
-    if (st != XCORR_OK) return st;
-    DeviceInfo dev;
-    if ((st = current_device_info(&dev)) != XCORR_OK) return st;
-    dim3 g, b;
-    XC_CUDA(launch_strip_f64(d_left, d_right, d_out, (int)rows, (int)cols, pm,
-                             (unsigned long long)pm.n_left * pm.m, dev.sm_count, &g, &b,
-                             static_cast<cudaStream_t>(stream)));
-    char buf[128];
-    std::snprintf(buf, sizeof buf, "kernel=strip_f64 grid=(%u,1,1) block=(%u,1,1) smem=0", g.x, b.x);
-    t_last_launch = buf;
-    ++t_launch_count;
-    return XCORR_OK;
+    return guarded([&]() -> xcorr_status {
+        if (!d_left || !d_right || !d_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+        PairMap pm{};
+        xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+        if (st != XCORR_OK) return st;
+        DeviceInfo dev;
+        if ((st = current_device_info(&dev)) != XCORR_OK) return st;
+        dim3 g, b;
+        XC_CUDA(launch_strip_f64(d_left, d_right, d_out, (int)rows, (int)cols, pm,
+                                 (unsigned long long)pm.n_left * pm.m, dev.sm_count, &g, &b,
+                                 static_cast<cudaStream_t>(stream)));
+        char buf[128];
+        std::snprintf(buf, sizeof buf, "kernel=strip_f64 grid=(%u,1,1) block=(%u,1,1) smem=0", g.x, b.x);
+        t_last_launch = buf;
+        ++t_launch_count;
+        return XCORR_OK;
+    });
 }
 
 xcorr_status xcorr_run_host_f64(int32_t mode, const double* h_left, const double* h_right, double* h_out,
                                 uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right, int32_t device) {
-    if (!h_left || !h_right || !h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
-    PairMap pm{};
-    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
-    if (st != XCORR_OK) return st;
-    int ndev = 0;
-    XC_CUDA(cudaGetDeviceCount(&ndev));
-    if (device < 0 || device >= ndev) return fail(XCORR_ERR_DEVICE, "no such CUDA device");
-    XC_CUDA(cudaSetDevice(device));
-    const size_t in_elems = (size_t)rows * cols;
-    const size_t lbytes = in_elems * n_left * sizeof(double), rbytes = in_elems * n_right * sizeof(double);
-    const size_t obytes = (size_t)(2 * rows - 1) * (2 * cols - 1) * pm.n_left * pm.m * sizeof(double);
-    double *dl = nullptr, *dr = nullptr, *dout = nullptr;
-    cudaStream_t stream = nullptr;
-    cudaError_t e = cudaMalloc(&dl, lbytes);
-    if (e == cudaSuccess) e = cudaMalloc(&dr, rbytes);
-    if (e == cudaSuccess) e = cudaMalloc(&dout, obytes);
-    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(dl, h_left, lbytes, cudaMemcpyHostToDevice, stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(dr, h_right, rbytes, cudaMemcpyHostToDevice, stream);
-    st = XCORR_OK;
-    if (e == cudaSuccess) st = xcorr_run_f64(mode, dl, dr, dout, rows, cols, n_left, n_right, stream);
-    if (e == cudaSuccess && st == XCORR_OK) e = cudaMemcpyAsync(h_out, dout, obytes, cudaMemcpyDeviceToHost, stream);
-    if (e == cudaSuccess && stream) e = cudaStreamSynchronize(stream);
-    if (stream) cudaStreamDestroy(stream);
-    cudaFree(dl); cudaFree(dr); cudaFree(dout);
-    if (st != XCORR_OK) return st;
-    if (e != cudaSuccess) { (void)cudaGetLastError(); return fail(XCORR_ERR_CUDA, cudaGetErrorString(e)); }
-    return XCORR_OK;
+    return guarded([&]() -> xcorr_status {
+        if (!h_left || !h_right || !h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+        PairMap pm{};
+        xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+        if (st != XCORR_OK) return st;
+        int ndev = 0;
+        XC_CUDA(cudaGetDeviceCount(&ndev));
+        if (device < 0 || device >= ndev) return fail(XCORR_ERR_DEVICE, "no such CUDA device");
+        DeviceGuard restore_device;
+        XC_CUDA(cudaSetDevice(device));
+        const size_t in_elems = (size_t)rows * cols;
+        const size_t lbytes = in_elems * n_left * sizeof(double), rbytes = in_elems * n_right * sizeof(double);
+        const size_t obytes = (size_t)(2 * rows - 1) * (2 * cols - 1) * pm.n_left * pm.m * sizeof(double);
+        double *dl = nullptr, *dr = nullptr, *dout = nullptr;
+        cudaStream_t stream = nullptr;
+        cudaError_t e = cudaMalloc(&dl, lbytes);
+        if (e == cudaSuccess) e = cudaMalloc(&dr, rbytes);
+        if (e == cudaSuccess) e = cudaMalloc(&dout, obytes);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(dl, h_left, lbytes, cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(dr, h_right, rbytes, cudaMemcpyHostToDevice, stream);
+        st = XCORR_OK;
+        if (e == cudaSuccess) st = xcorr_run_f64(mode, dl, dr, dout, rows, cols, n_left, n_right, stream);
+        if (e == cudaSuccess && st == XCORR_OK) e = cudaMemcpyAsync(h_out, dout, obytes, cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess && stream) e = cudaStreamSynchronize(stream);
+        if (stream) cudaStreamDestroy(stream);
+        cudaFree(dl); cudaFree(dr); cudaFree(dout);
+        if (st != XCORR_OK) return st;
+        if (e != cudaSuccess) { (void)cudaGetLastError(); return fail(XCORR_ERR_CUDA, cudaGetErrorString(e)); }
+        return XCORR_OK;
+    });
 }
 
 xcorr_status xcorr_run_host_batch_f32(const xcorr_host_job* jobs, int32_t n_jobs, int32_t device) {
-    if (n_jobs < 0) return fail(XCORR_ERR_INVALID_SIZE, "n_jobs must not be negative");
-    if (n_jobs == 0) return XCORR_OK;
-    if (!jobs) return fail(XCORR_ERR_NULL_POINTER, "jobs must not be NULL");
-    std::vector<HostJob> hj((size_t)n_jobs);
-    for (int j = 0; j < n_jobs; ++j) {
-        hj[j].mode = jobs[j].mode;
-        hj[j].h_left = jobs[j].h_left; hj[j].h_right = jobs[j].h_right; hj[j].h_out = jobs[j].h_out;
-        hj[j].rows = jobs[j].rows; hj[j].cols = jobs[j].cols;
-        hj[j].n_left = jobs[j].n_left; hj[j].n_right = jobs[j].n_right;
-        hj[j].hints = jobs[j].hints;
-    }
-    return run_host_batch(hj.data(), n_jobs, device);
+    return guarded([&]() -> xcorr_status {
+        if (n_jobs < 0) return fail(XCORR_ERR_INVALID_SIZE, "n_jobs must not be negative");
+        if (n_jobs == 0) return XCORR_OK;
+        if (!jobs) return fail(XCORR_ERR_NULL_POINTER, "jobs must not be NULL");
+        std::vector<HostJob> hj((size_t)n_jobs);
+        for (int j = 0; j < n_jobs; ++j) {
+            hj[j].mode = jobs[j].mode;
+            hj[j].h_left = jobs[j].h_left; hj[j].h_right = jobs[j].h_right; hj[j].h_out = jobs[j].h_out;
+            hj[j].rows = jobs[j].rows; hj[j].cols = jobs[j].cols;
+            hj[j].n_left = jobs[j].n_left; hj[j].n_right = jobs[j].n_right;
+            hj[j].hints = jobs[j].hints;
+        }
+        return run_host_batch(hj.data(), n_jobs, device);
+    });
 }
 
 void xcorr_shard_range(uint32_t units, int32_t parts, int32_t index, uint32_t* first, uint32_t* count) {
@@ -1102,57 +1262,60 @@ void xcorr_shard_range(uint32_t units, int32_t parts, int32_t index, uint32_t* f
 xcorr_status xcorr_run_host_sharded_f32(int32_t mode, const float* h_left, const float* h_right, float* h_out,
                                         uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                                         const xcorr_hints* hints, const int32_t* devices, int32_t n_devices) {
-    if (!h_left || !h_right || !h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
-    PairMap pm{};
-    xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
-    if (st != XCORR_OK) return st;
-    if (n_devices <= 0 || n_devices > kMaxDevices) return fail(XCORR_ERR_DEVICE, "n_devices must be 1..64");
-    std::vector<int32_t> devs(n_devices);
-    for (int i = 0; i < n_devices; ++i) devs[i] = devices ? devices[i] : i;
-    if (mode == XCORR_ONE_TO_ONE || n_devices == 1)
-        return run_host(mode, h_left, h_right, h_out, rows, cols, n_left, n_right, hints, devs[0]);
-
-    const size_t in_elems = (size_t)rows * cols;
-    const size_t out_elems = (size_t)(2 * rows - 1) * (2 * cols - 1);
-    const uint32_t units = mode == XCORR_ONE_TO_MANY ? n_right : n_left;
-    std::vector<xcorr_status> status(n_devices, XCORR_OK);
-    std::vector<std::string> errors(n_devices);
-    std::vector<std::thread> workers;
-    for (int i = 0; i < n_devices; ++i) {
-        uint32_t first = 0, count = 0;
-        xcorr_shard_range(units, n_devices, i, &first, &count);
-        if (count == 0) continue;
-        workers.emplace_back([&, i, first, count]() {
-            const float* l = h_left;
-            const float* r = h_right;
-            float* o = h_out;
-            uint32_t nl = n_left, nr = n_right;
-            if (mode == XCORR_ONE_TO_MANY) {           // a block of right matrices
-                r += (size_t)first * in_elems;
-                o += (size_t)first * out_elems;
-                nr = count;
-            } else if (mode == XCORR_N_TO_M) {          // a block of left matrices, all rights
-                l += (size_t)first * in_elems;
-                o += (size_t)first * pm.m * out_elems;
-                nl = count;
-            } else {                                    // n_to_mn: lefts with their own m rights
-                l += (size_t)first * in_elems;
-                r += (size_t)first * pm.m * in_elems;
-                o += (size_t)first * pm.m * out_elems;
-                nl = count;
-                nr = count * pm.m;
-            }
-            status[i] = run_host(mode, l, r, o, rows, cols, nl, nr, hints, devs[i]);
-            if (status[i] != XCORR_OK) errors[i] = t_last_error;
-        });
-    }
-    for (auto& w : workers) w.join();
-    for (int i = 0; i < n_devices; ++i)
-        if (status[i] != XCORR_OK) return fail(status[i], "shard " + std::to_string(i) + ": " + errors[i]);
-    return XCORR_OK;
+    return guarded([&]() -> xcorr_status {
+        if (!h_left || !h_right || !h_out) return fail(XCORR_ERR_NULL_POINTER, "left, right and out must not be NULL");
+        PairMap pm{};
+        xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
+        if (st != XCORR_OK) return st;
+        if (n_devices <= 0 || n_devices > kMaxDevices) return fail(XCORR_ERR_DEVICE, "n_devices must be 1..64");
+        std::vector<int32_t> devs(n_devices);
+        for (int i = 0; i < n_devices; ++i) devs[i] = devices ? devices[i] : i;
+        if (mode == XCORR_ONE_TO_ONE || n_devices == 1)
+            return run_host(mode, h_left, h_right, h_out, rows, cols, n_left, n_right, hints, devs[0]);
+    
+        const size_t in_elems = (size_t)rows * cols;
+        const size_t out_elems = (size_t)(2 * rows - 1) * (2 * cols - 1);
+        const uint32_t units = mode == XCORR_ONE_TO_MANY ? n_right : n_left;
+        std::vector<xcorr_status> status(n_devices, XCORR_OK);
+        std::vector<std::string> errors(n_devices);
+        std::vector<std::thread> workers;
+        for (int i = 0; i < n_devices; ++i) {
+            uint32_t first = 0, count = 0;
+            xcorr_shard_range(units, n_devices, i, &first, &count);
+            if (count == 0) continue;
+            workers.emplace_back([&, i, first, count]() {
+                const float* l = h_left;
+                const float* r = h_right;
+                float* o = h_out;
+                uint32_t nl = n_left, nr = n_right;
+                if (mode == XCORR_ONE_TO_MANY) {           // a block of right matrices
+                    r += (size_t)first * in_elems;
+                    o += (size_t)first * out_elems;
+                    nr = count;
+                } else if (mode == XCORR_N_TO_M) {          // a block of left matrices, all rights
+                    l += (size_t)first * in_elems;
+                    o += (size_t)first * pm.m * out_elems;
+                    nl = count;
+                } else {                                    // n_to_mn: lefts with their own m rights
+                    l += (size_t)first * in_elems;
+                    r += (size_t)first * pm.m * in_elems;
+                    o += (size_t)first * pm.m * out_elems;
+                    nl = count;
+                    nr = count * pm.m;
+                }
+                status[i] = run_host(mode, l, r, o, rows, cols, nl, nr, hints, devs[i]);
+                if (status[i] != XCORR_OK) errors[i] = t_last_error;
+            });
+        }
+        for (auto& w : workers) w.join();
+        for (int i = 0; i < n_devices; ++i)
+            if (status[i] != XCORR_OK) return fail(status[i], "shard " + std::to_string(i) + ": " + errors[i]);
+        return XCORR_OK;
+    });
 }
 
 void xcorr_release_host_cache(void) {
+    noalloc_forget_addresses();
     int prev = 0;
     if (cudaGetDevice(&prev) != cudaSuccess) { (void)cudaGetLastError(); return; }
     for (int d = 0; d < kMaxDevices; ++d) {
@@ -1182,17 +1345,19 @@ void xcorr_release_host_cache(void) {
 
 xcorr_status xcorr_n_to_mn_reorder_f32(const float* src, float* dst, uint32_t n_left, uint32_t n_total,
                                        size_t elems, int32_t to_grouped) {
-    if (!src || !dst) return fail(XCORR_ERR_NULL_POINTER, "src and dst must not be NULL");
-    if (n_left == 0 || n_total % n_left != 0) return fail(XCORR_ERR_INVALID_SIZE, "n_total must be a multiple of n_left");
-    const uint32_t m = n_total / n_left;
-    for (uint32_t i = 0; i < n_total; ++i) {
-        // file index i = t*n_left + l  <->  grouped index l*m + t
-        const uint32_t l = i % n_left, t = i / n_left;
-        const uint32_t g = l * m + t;
-        if (to_grouped) std::memcpy(dst + (size_t)g * elems, src + (size_t)i * elems, elems * sizeof(float));
-        else            std::memcpy(dst + (size_t)i * elems, src + (size_t)g * elems, elems * sizeof(float));
-    }
-    return XCORR_OK;
+    return guarded([&]() -> xcorr_status {
+        if (!src || !dst) return fail(XCORR_ERR_NULL_POINTER, "src and dst must not be NULL");
+        if (n_left == 0 || n_total % n_left != 0) return fail(XCORR_ERR_INVALID_SIZE, "n_total must be a multiple of n_left");
+        const uint32_t m = n_total / n_left;
+        for (uint32_t i = 0; i < n_total; ++i) {
+            // file index i = t*n_left + l  <->  grouped index l*m + t
+            const uint32_t l = i % n_left, t = i / n_left;
+            const uint32_t g = l * m + t;
+            if (to_grouped) std::memcpy(dst + (size_t)g * elems, src + (size_t)i * elems, elems * sizeof(float));
+            else            std::memcpy(dst + (size_t)i * elems, src + (size_t)g * elems, elems * sizeof(float));
+        }
+        return XCORR_OK;
+    });
 }
 
 const char* xcorr_last_launch_string(void) { return t_last_launch.c_str(); }
@@ -1209,75 +1374,85 @@ const char* xcorr_status_string(int32_t status) {
     case XCORR_ERR_UNSUPPORTED: return "unsupported shape";
     case XCORR_ERR_DEVICE: return "bad device";
     case XCORR_ERR_TIMEOUT: return "device-side wait timed out";
+    case XCORR_ERR_INTERNAL: return "host-side failure inside the library";
     default: return "unknown status";
     }
+}
+
+void xcorr_debug_stage_wait(uint32_t poll_limit, uint32_t surplus_bytes) {
+    g_stage_wait_limit.store(poll_limit ? poll_limit : kStageWaitLimit, std::memory_order_relaxed);
+    g_stage_expect_surplus.store(surplus_bytes, std::memory_order_relaxed);
 }
 
 uint64_t xcorr_launch_count(void) { return t_launch_count; }
 void xcorr_reset_launch_count(void) { t_launch_count = 0; }
 
 xcorr_status xcorr_ffma_peak_probe(double* flops_per_second, double* kernel_ms, void* stream_v) {
-    if (!flops_per_second) return fail(XCORR_ERR_NULL_POINTER, "flops_per_second must not be NULL");
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    DeviceInfo dev;
-    xcorr_status st = current_device_info(&dev);
-    if (st != XCORR_OK) return st;
-    float* sink = nullptr;
-    XC_CUDA(cudaMalloc(&sink, sizeof(float)));
-    cudaEvent_t e0, e1;
-    XC_CUDA(cudaEventCreate(&e0));
-    XC_CUDA(cudaEventCreate(&e1));
-    const int blocks = dev.sm_count * 2, iters = 4096;
-    double best_ms = 1e30;
-    for (int rep = 0; rep < 4; ++rep) {            // first repetition is the warm-up
-        XC_CUDA(cudaEventRecord(e0, stream));
-        XC_CUDA(launch_ffma_probe(sink, iters, blocks, stream));
-        XC_CUDA(cudaEventRecord(e1, stream));
-        XC_CUDA(cudaEventSynchronize(e1));
-        float ms = 0.f;
-        XC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
-        if (rep > 0 && ms < best_ms) best_ms = ms;
-        ++t_launch_count;
-    }
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
-    cudaFree(sink);
-    const double flop = 2.0 * 16.0 * 8.0 * (double)iters * 1024.0 * (double)blocks;
-    *flops_per_second = flop / (best_ms * 1e-3);
-    if (kernel_ms) *kernel_ms = best_ms;
-    return XCORR_OK;
+    return guarded([&]() -> xcorr_status {
+        if (!flops_per_second) return fail(XCORR_ERR_NULL_POINTER, "flops_per_second must not be NULL");
+        cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+        DeviceInfo dev;
+        xcorr_status st = current_device_info(&dev);
+        if (st != XCORR_OK) return st;
+        float* sink = nullptr;
+        XC_CUDA(cudaMalloc(&sink, sizeof(float)));
+        cudaEvent_t e0, e1;
+        XC_CUDA(cudaEventCreate(&e0));
+        XC_CUDA(cudaEventCreate(&e1));
+        const int blocks = dev.sm_count * 2, iters = 4096;
+        double best_ms = 1e30;
+        for (int rep = 0; rep < 4; ++rep) {            // first repetition is the warm-up
+            XC_CUDA(cudaEventRecord(e0, stream));
+            XC_CUDA(launch_ffma_probe(sink, iters, blocks, stream));
+            XC_CUDA(cudaEventRecord(e1, stream));
+            XC_CUDA(cudaEventSynchronize(e1));
+            float ms = 0.f;
+            XC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+            if (rep > 0 && ms < best_ms) best_ms = ms;
+            ++t_launch_count;
+        }
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        cudaFree(sink);
+        const double flop = 2.0 * 16.0 * 8.0 * (double)iters * 1024.0 * (double)blocks;
+        *flops_per_second = flop / (best_ms * 1e-3);
+        if (kernel_ms) *kernel_ms = best_ms;
+        return XCORR_OK;
+    });
 }
 
 xcorr_status xcorr_dfma_peak_probe(double* flops_per_second, double* kernel_ms, void* stream_v) {
-    if (!flops_per_second) return fail(XCORR_ERR_NULL_POINTER, "flops_per_second must not be NULL");
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    DeviceInfo dev;
-    xcorr_status st = current_device_info(&dev);
-    if (st != XCORR_OK) return st;
-    double* sink = nullptr;
-    XC_CUDA(cudaMalloc(&sink, sizeof(double)));
-    cudaEvent_t e0, e1;
-    XC_CUDA(cudaEventCreate(&e0));
-    XC_CUDA(cudaEventCreate(&e1));
-    const int blocks = dev.sm_count * 2, iters = 2048;
-    double best_ms = 1e30;
-    for (int rep = 0; rep < 4; ++rep) {            // first repetition is the warm-up
-        XC_CUDA(cudaEventRecord(e0, stream));
-        XC_CUDA(launch_dfma_probe(sink, iters, blocks, stream));
-        XC_CUDA(cudaEventRecord(e1, stream));
-        XC_CUDA(cudaEventSynchronize(e1));
-        float ms = 0.f;
-        XC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
-        if (rep > 0 && ms < best_ms) best_ms = ms;
-        ++t_launch_count;
-    }
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
-    cudaFree(sink);
-    const double flop = 2.0 * 16.0 * 8.0 * (double)iters * 1024.0 * (double)blocks;
-    *flops_per_second = flop / (best_ms * 1e-3);
-    if (kernel_ms) *kernel_ms = best_ms;
-    return XCORR_OK;
+    return guarded([&]() -> xcorr_status {
+        if (!flops_per_second) return fail(XCORR_ERR_NULL_POINTER, "flops_per_second must not be NULL");
+        cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+        DeviceInfo dev;
+        xcorr_status st = current_device_info(&dev);
+        if (st != XCORR_OK) return st;
+        double* sink = nullptr;
+        XC_CUDA(cudaMalloc(&sink, sizeof(double)));
+        cudaEvent_t e0, e1;
+        XC_CUDA(cudaEventCreate(&e0));
+        XC_CUDA(cudaEventCreate(&e1));
+        const int blocks = dev.sm_count * 2, iters = 2048;
+        double best_ms = 1e30;
+        for (int rep = 0; rep < 4; ++rep) {            // first repetition is the warm-up
+            XC_CUDA(cudaEventRecord(e0, stream));
+            XC_CUDA(launch_dfma_probe(sink, iters, blocks, stream));
+            XC_CUDA(cudaEventRecord(e1, stream));
+            XC_CUDA(cudaEventSynchronize(e1));
+            float ms = 0.f;
+            XC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+            if (rep > 0 && ms < best_ms) best_ms = ms;
+            ++t_launch_count;
+        }
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        cudaFree(sink);
+        const double flop = 2.0 * 16.0 * 8.0 * (double)iters * 1024.0 * (double)blocks;
+        *flops_per_second = flop / (best_ms * 1e-3);
+        if (kernel_ms) *kernel_ms = best_ms;
+        return XCORR_OK;
+    });
 }
 
 }  // extern "C"

@@ -12,6 +12,7 @@
 //   warp_per_overlap_kernel one warp per overlap (naive_warp_per_shift.cu:192-244).
 // plus the fixed-order reduction of workspace partials and the FFMA peak probe.
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstdint>
 #include <mutex>
 
@@ -71,11 +72,11 @@ __device__ __forceinline__ void stage_wait() {
 // global -> shared as one cp.async.bulk each, completion counted in bytes on an mbarrier.
 // Used when rows need no column padding (cols a multiple of 16) and the operands are 16-byte
 // aligned; everything else takes the 16-byte cp.async path above.
-// Waits on the mbarrier are bounded: after kStageWaitLimit polls the block counts a timeout in
-// g_stage_timeouts (read by the host through tile_stage_timeouts()), polls once more with the
-// same bound so that its own copies can land, and carries on to its end without hanging.
+// Waits on the mbarrier are bounded: after TileArgs::stage_wait_limit polls (twice) the wait
+// gives up.  The block then agrees on that (one vote at its next barrier), counts one timeout in
+// g_stage_timeouts (read and cleared by the host through tile_stage_timeouts()), drops the rest
+// of its work and returns: nothing is computed from a buffer whose copies did not land.
 __device__ unsigned g_stage_timeouts = 0;
-constexpr unsigned kStageWaitLimit = 1u << 22;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(1) : "memory");
@@ -94,12 +95,14 @@ __device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (int attempt = 0; attempt < 2; ++attempt) {
-        for (unsigned it = 0; it < kStageWaitLimit; ++it)
-            if (mbar_poll(bar, parity)) return;
-        if (attempt == 0 && (threadIdx.x & 31) == 0) atomicAdd(&g_stage_timeouts, 1u);
-    }
+__device__ __forceinline__ void mbar_complete_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.complete_tx.relaxed.cta.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, unsigned limit) {
+    for (int attempt = 0; attempt < 2; ++attempt)
+        for (unsigned it = 0; it < limit; ++it)
+            if (mbar_poll(bar, parity)) return true;
+    return false;
 }
 
 // Load the N4*4 floats at `addr` into w[FIRST ...].
@@ -511,6 +514,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     }
 
     while (u < uend) {
+        bool stage_ok = true;
         int r0, r1, bx, by, rg, l, combine, q_first = 0, q_count = 0;
         unsigned task_id = 0, first_block = 0;
         int n_parts = 1, part = 0;
@@ -575,7 +579,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
-                if (lane == 0) mbar_expect(stage_bar, bytes);
+                if (lane == 0) mbar_expect(stage_bar, bytes + a.stage_expect_surplus);
                 __syncwarp();
                 for (int i = lane; i < nstage + p.ML; i += 32) {
                     if (i < nstage) {
@@ -603,7 +607,17 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             for (int mm = warp; mm < p.ML; mm += nthr >> 5)
                 if ((unsigned)rg * p.ML + mm >= a.pm.m)
                     for (int x = lane * 4; x < rs * Wp; x += 128) *reinterpret_cast<float4*>(sR + (size_t)mm * p.RMS + x) = zero4;
-            mbar_wait_bounded(stage_bar, stage_parity);
+            stage_ok = mbar_wait_bounded(stage_bar, stage_parity, a.stage_wait_limit);
+            if (!stage_ok) {
+                // Gave up.  Before the block leaves, its own copies must have landed (the shared
+                // memory they target goes to another block afterwards): take back the bytes a test
+                // announced in surplus, then wait once more with the default bound.
+                if (a.stage_expect_surplus != 0) {
+                    __syncthreads();
+                    if (tid == 0) mbar_complete_tx(stage_bar, a.stage_expect_surplus);
+                }
+                (void)mbar_wait_bounded(stage_bar, stage_parity, kStageWaitLimit);
+            }
             stage_parity ^= 1u;
         } else {
         {
@@ -663,7 +677,10 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         stage_wait();
         }
         if (p.schedule == kSchedWarpQueue && tid == 0) *queue = 0;
-        __syncthreads();
+        if (__syncthreads_or(!stage_ok)) {
+            if (tid == 0) atomicAdd(&g_stage_timeouts, 1u);
+            break;
+        }
 
         // ---- this warp's tile(s): its fixed tile of the block task, or tiles popped from the queue
         int item = 0;
@@ -780,21 +797,70 @@ __global__ void overlap_wise_kernel(const float* __restrict__ left, const float*
 // ------------------------------------------------------------------------------------------
 // warp-per-overlap: lanes stride the columns of the overlap, rows in sequence, butterfly sum
 // ------------------------------------------------------------------------------------------
+// Row split (naive_warp_per_shift.cu:100-189 with row_distribution.cuh): with rows_per_warp > 0
+// the rows of an overlap are shared by several warps ("workers"), each taking
+// ceil(overlap rows / workers) of them and adding its sum atomically onto the zeroed output.
+// An output row oy has n(oy) = H - |oy - (H-1)| overlapping rows and needs
+// ceil(n(oy) / rows_per_warp) workers.  kSplitRectangle gives every output row the
+// ceil(H / rows_per_warp) worker slots of the centre row and lets the surplus ones return at
+// once; kSplitTriangle enumerates exactly the workers needed (prefix sums in closed form).
+
+// Workers needed by the output rows [0, y) of one result matrix, y <= H (upper half: row j has
+// j + 1 overlapping rows): sum over j < y of ceil((j + 1) / r).
+__device__ __forceinline__ unsigned long long split_workers_upper(unsigned y, unsigned r) {
+    const unsigned long long q = y / r, rem = y % r;
+    return (unsigned long long)r * q * (q + 1) / 2 + rem * (q + 1);
+}
+// ... by the output rows [0, y) for any y <= 2H - 1 (the lower half mirrors the upper one).
+__device__ __forceinline__ unsigned long long split_workers_before(unsigned y, unsigned H, unsigned r) {
+    if (y <= H) return split_workers_upper(y, r);
+    // rows H .. y-1 have 2H-1-j overlapping rows = the rows 2H-1-y .. H-2 of the upper half
+    return split_workers_upper(H, r) + split_workers_upper(H - 1, r) - split_workers_upper(2 * H - 1 - y, r);
+}
+
 __global__ void warp_per_overlap_kernel(const float* __restrict__ left, const float* __restrict__ right,
                                         float* __restrict__ out, int H, int W, PairMap pm,
-                                        unsigned long long nshifts_total) {
+                                        unsigned long long ntasks, int rows_per_warp, int split) {
     const int OW = 2 * W - 1, OH = 2 * H - 1;
     const unsigned long long OE = (unsigned long long)OW * OH;
     const int lane = threadIdx.x & 31;
     const unsigned long long warps_per_grid = (unsigned long long)gridDim.x * (blockDim.x >> 5);
-    for (unsigned long long sh = (unsigned long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-         sh < nshifts_total; sh += warps_per_grid) {
-        const unsigned long long pair = sh / OE;
-        const unsigned long long oi = sh - pair * OE;
-        const int oy = (int)(oi / OW), ox = (int)(oi - (unsigned long long)oy * OW);
+    // worker slots of one result matrix: one per overlap, or the split's count per output row
+    const unsigned slots_rect = split == kSplitRectangle ? (unsigned)((H + rows_per_warp - 1) / rows_per_warp) : 1u;
+    const unsigned long long per_matrix =
+        split == kSplitTriangle ? split_workers_before((unsigned)OH, (unsigned)H, (unsigned)rows_per_warp) * OW
+                                : OE * slots_rect;
+    for (unsigned long long task = (unsigned long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+         task < ntasks; task += warps_per_grid) {
+        const unsigned long long pair = task / per_matrix;
+        const unsigned long long ti = task - pair * per_matrix;
+        int oy, ox, worker = 0, workers = 1;
+        if (split == kSplitTriangle) {
+            // worker rows: (output row, worker) pairs in row order, each OW overlaps wide
+            const unsigned long long wrow = ti / OW;
+            ox = (int)(ti - wrow * OW);
+            int lo = 0, hi = OH - 1;                       // last row whose prefix is <= wrow
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (split_workers_before((unsigned)mid, (unsigned)H, (unsigned)rows_per_warp) <= wrow) lo = mid; else hi = mid - 1;
+            }
+            oy = lo;
+            worker = (int)(wrow - split_workers_before((unsigned)oy, (unsigned)H, (unsigned)rows_per_warp));
+        } else {
+            const unsigned long long oi = ti / slots_rect;
+            worker = (int)(ti - oi * slots_rect);
+            oy = (int)(oi / OW); ox = (int)(oi - (unsigned long long)oy * OW);
+        }
         const int sx = ox - (W - 1), sy = oy - (H - 1);
         const int x0 = max(sx, 0), x1 = min(W + sx, W);
-        const int y0 = max(sy, 0), y1 = min(H + sy, H);
+        int y0 = max(sy, 0), y1 = min(H + sy, H);
+        if (split != kSplitNone) {
+            workers = (y1 - y0 + rows_per_warp - 1) / rows_per_warp;
+            if (worker >= workers) continue;               // a surplus slot of the rectangle
+            const int share = (y1 - y0 + workers - 1) / workers;
+            y0 += worker * share;
+            y1 = min(y1, y0 + share);
+        }
         const unsigned long long l = pair / pm.m, j = pair % pm.m;
         const float* L = left + l * (size_t)H * W;
         const float* R = right + (l * pm.right_stride + j) * (size_t)H * W;
@@ -806,7 +872,160 @@ __global__ void warp_per_overlap_kernel(const float* __restrict__ left, const fl
         }
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-        if (lane == 0) out[sh] = sum;
+        if (lane == 0) {
+            float* dst = out + pair * OE + (size_t)oy * OW + ox;
+            if (split != kSplitNone) atomicAdd(dst, sum); else *dst = sum;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// staged warp-per-overlap: the same warp-per-overlap sum, operands through shared memory
+// ------------------------------------------------------------------------------------------
+// Stands in for ccn_warp_per_shift_shared_mem (naive_warp_per_shift_shared_mem.cu:157-496,
+// shared_mem.cuh:25-218).  A block owns one x shift, `shifts` consecutive y shifts (one per
+// warp) and up to RMAX right matrices of one left matrix, so all its warps read the same
+// columns: a slab of `srows` right rows x `scols` columns of every right matrix, and the
+// srows + shifts - 1 left rows those y shifts meet them with, are copied to shared memory
+// (4-byte cp.async: the left columns start at an arbitrary x shift) and every left value a
+// lane loads is used for all the block's right matrices.  Two slabs are in flight: the copies
+// of the next one run under the arithmetic of the current one.  Small inputs fit one slab,
+// which makes this the latency kernel of the library: one wave of blocks, one copy, one sum.
+__device__ __forceinline__ void stage_copy4(uint32_t dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(dst), "l"(src) : "memory");
+}
+
+template<int RMAX>
+__global__ void __launch_bounds__(1024) warp_staged_kernel(const StagedArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    const int H = a.H, W = a.W, OW = 2 * W - 1, OH = 2 * H - 1;
+    const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
+    const int k = a.shifts, srows = a.srows, scols = a.scols;
+
+    // block -> (left matrix, group of right matrices, x shift), y shifts, column slab
+    const unsigned bx = blockIdx.x;
+    const int ox = (int)(bx % (unsigned)OW);
+    const unsigned gl = bx / (unsigned)OW;
+    const unsigned rg = gl % a.groups_per_left, l = gl / a.groups_per_left;
+    const int nr = (int)min((unsigned)a.rights, a.pm.m - rg * (unsigned)a.rights);   // live right matrices
+    const int sx = ox - (W - 1);
+    const int oy0 = (int)blockIdx.y * k;
+    const int sy_min = oy0 - (H - 1);
+    const int sy_max = min(oy0 + k - 1, OH - 1) - (H - 1);
+    const int sy_w = sy_min + warp;
+    const bool warp_live = oy0 + warp < OH;
+    int cx0 = max(0, -sx), cx1 = min(W, W - sx);               // right columns of the overlap
+    if (a.col_groups) {
+        cx0 += (int)blockIdx.z * scols;
+        cx1 = min(cx1, cx0 + scols);
+        if (cx0 >= cx1) return;                                 // the same for the whole block
+    }
+    const int ry0 = max(0, -sy_max), ry1 = min(H, H - sy_min);  // right rows any warp of the block needs
+    const int wy0 = max(0, -sy_w), wy1 = min(H, H - sy_w);      // ... this warp needs
+
+    const float* gL = a.left + (size_t)l * H * W;
+    const float* gR = a.right + ((size_t)l * a.pm.right_stride + (size_t)rg * a.rights) * H * W;
+    const int lrows = srows + k - 1;
+    const int stage_floats = (lrows + a.rights * srows) * scols;
+    const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);
+
+    const int nslab_y = ry1 > ry0 ? (ry1 - ry0 + srows - 1) / srows : 0;
+    const int nslab_x = (cx1 - cx0 + scols - 1) / scols;
+    const int nslabs = nslab_y * nslab_x;
+
+    // copies of slab i into stage s
+    auto issue = [&](int i, int s) {
+        const int ix = i / nslab_y, iy = i - ix * nslab_y;
+        const int cs = cx0 + ix * scols, cw = min(scols, cx1 - cs);
+        const int rb = ry0 + iy * srows, n = min(srows, ry1 - rb);
+        const uint32_t sL = smem_addr + (uint32_t)(s * stage_floats) * 4;
+        const uint32_t sR = sL + (uint32_t)(lrows * scols) * 4;
+        // left rows rb + sy_min .. rb + n - 1 + sy_max, kept at their offset from rb + sy_min
+        const int lr_lo = max(0, rb + sy_min), lr_hi = min(H, rb + n + sy_max);
+        const int nl = max(0, lr_hi - lr_lo);
+        const int total_rows = nl + nr * n;
+        if (a.warp_rows) {
+            for (int row = warp; row < total_rows; row += nthr >> 5) {
+                const float* src;
+                uint32_t dst;
+                if (row < nl) {
+                    src = gL + (size_t)(lr_lo + row) * W + cs + sx;
+                    dst = sL + (uint32_t)((lr_lo + row - (rb + sy_min)) * scols) * 4;
+                } else {
+                    const int rr = row - nl, mm = rr / n, r = rr - mm * n;
+                    src = gR + ((size_t)mm * H + rb + r) * W + cs;
+                    dst = sR + (uint32_t)((mm * srows + r) * scols) * 4;
+                }
+                for (int c = lane; c < cw; c += 32) stage_copy4(dst + c * 4, src + c);
+            }
+        } else {
+            const int total = total_rows * cw;
+            for (int idx = tid; idx < total; idx += nthr) {
+                const int row = idx / cw, c = idx - row * cw;
+                if (row < nl) {
+                    stage_copy4(sL + (uint32_t)((lr_lo + row - (rb + sy_min)) * scols + c) * 4,
+                                gL + (size_t)(lr_lo + row) * W + cs + sx + c);
+                } else {
+                    const int rr = row - nl, mm = rr / n, r = rr - mm * n;
+                    stage_copy4(sR + (uint32_t)((mm * srows + r) * scols + c) * 4,
+                                gR + ((size_t)mm * H + rb + r) * W + cs + c);
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float sum[RMAX];
+#pragma unroll
+    for (int i = 0; i < RMAX; ++i) sum[i] = 0.f;
+
+    if (nslabs > 0) issue(0, 0);
+    for (int i = 0; i < nslabs; ++i) {
+        if (i + 1 < nslabs) {
+            issue(i + 1, (i + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        {
+            const int ix = i / nslab_y, iy = i - ix * nslab_y;
+            const int cs = cx0 + ix * scols, cw = min(scols, cx1 - cs);
+            const int rb = ry0 + iy * srows, n = min(srows, ry1 - rb);
+            const float* sL = smem + (size_t)(i & 1) * stage_floats;
+            const float* sR = sL + lrows * scols;
+            // lanes: LC columns x 32 / LC rows of the slab per step
+            int lc = 32;
+            while (lc > 1 && (lc >> 1) >= cw) lc >>= 1;
+            const int lrn = 32 / lc;
+            const int c0 = lane & (lc - 1), r_off = lane / lc;
+            const int ra = max(wy0, rb), rbnd = min(wy1, rb + n);
+            if (warp_live) {
+                for (int r = ra + r_off; r < rbnd; r += lrn) {
+                    const float* lrow = sL + (r - rb + warp) * scols;   // left row r + sy_w
+                    const float* rrow = sR + (r - rb) * scols;
+                    for (int c = c0; c < cw; c += lc) {
+                        const float lv = lrow[c];
+#pragma unroll
+                        for (int m2 = 0; m2 < RMAX; ++m2)
+                            if (m2 < nr) sum[m2] = fmaf(lv, rrow[m2 * srows * scols + c], sum[m2]);
+                    }
+                }
+            }
+        }
+        __syncthreads();                                   // the stage is refilled two slabs on
+    }
+
+    if (!warp_live) return;
+#pragma unroll
+    for (int m2 = 0; m2 < RMAX; ++m2) {
+        float v = sum[m2];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+        if (lane == 0 && m2 < nr) {
+            float* dst = a.out + (((size_t)l * a.pm.m + (size_t)rg * a.rights + m2) * OH + (oy0 + warp)) * OW + ox;
+            if (a.col_groups) atomicAdd(dst, v); else *dst = v;
+        }
     }
 }
 
@@ -832,29 +1051,45 @@ __global__ void __launch_bounds__(1024) ffma_probe_kernel(float* sink, float b, 
 // ------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------
-template<int TY, int BOUND>
-static cudaError_t launch_tile_variant(const TileArgs& a, cudaStream_t stream) {
-    auto kernel = a.p.combine == kFixup ? tile_kernel<TY, BOUND, true> : tile_kernel<TY, BOUND, false>;
-    if (a.p.smem_bytes > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.p.smem_bytes);
-        if (e != cudaSuccess) return e;
-    }
-    kernel<<<a.p.grid, a.p.threads, a.p.smem_bytes, stream>>>(a);
+// Kernels that need more than 48 KB of dynamic shared memory have the limit raised once per
+// (kernel instance, device); `raised` remembers the largest size granted so far.
+constexpr int kAttrDevices = 64;
+template<typename K>
+static cudaError_t allow_smem(K kernel, std::atomic<size_t>* raised, int device, size_t bytes) {
+    if (bytes <= 48 * 1024) return cudaSuccess;
+    if (device >= 0 && device < kAttrDevices && raised[device].load(std::memory_order_relaxed) >= bytes) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && device >= 0 && device < kAttrDevices) raised[device].store(bytes, std::memory_order_relaxed);
+    return e;
+}
+
+template<int TY, int BOUND, bool FIXUP>
+static cudaError_t launch_tile_instance(const TileArgs& a, int device, cudaStream_t stream) {
+    static std::atomic<size_t> raised[kAttrDevices];
+    cudaError_t e = allow_smem(tile_kernel<TY, BOUND, FIXUP>, raised, device, a.p.smem_bytes);
+    if (e != cudaSuccess) return e;
+    tile_kernel<TY, BOUND, FIXUP><<<a.p.grid, a.p.threads, a.p.smem_bytes, stream>>>(a);
     return cudaGetLastError();
 }
 
-template<int TY>
-static cudaError_t launch_tile_ty(const TileArgs& a, cudaStream_t stream) {
-    return a.p.threads <= kSmallBlockThreads ? launch_tile_variant<TY, kSmallBlockThreads>(a, stream)
-                                             : launch_tile_variant<TY, kMaxWarps * 32>(a, stream);
+template<int TY, int BOUND>
+static cudaError_t launch_tile_variant(const TileArgs& a, int device, cudaStream_t stream) {
+    return a.p.combine == kFixup ? launch_tile_instance<TY, BOUND, true>(a, device, stream)
+                                 : launch_tile_instance<TY, BOUND, false>(a, device, stream);
 }
 
-cudaError_t launch_tile(const TileArgs& a, cudaStream_t stream) {
+template<int TY>
+static cudaError_t launch_tile_ty(const TileArgs& a, int device, cudaStream_t stream) {
+    return a.p.threads <= kSmallBlockThreads ? launch_tile_variant<TY, kSmallBlockThreads>(a, device, stream)
+                                             : launch_tile_variant<TY, kMaxWarps * 32>(a, device, stream);
+}
+
+cudaError_t launch_tile(const TileArgs& a, int device, cudaStream_t stream) {
     switch (a.p.TY) {
-    case 1: return launch_tile_ty<1>(a, stream);
-    case 2: return launch_tile_ty<2>(a, stream);
-    case 3: return launch_tile_ty<3>(a, stream);
-    case 4: return launch_tile_ty<4>(a, stream);
+    case 1: return launch_tile_ty<1>(a, device, stream);
+    case 2: return launch_tile_ty<2>(a, device, stream);
+    case 3: return launch_tile_ty<3>(a, device, stream);
+    case 4: return launch_tile_ty<4>(a, device, stream);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -888,18 +1123,57 @@ cudaError_t launch_overlap_wise(const float* left, const float* right, float* ou
 
 cudaError_t launch_warp_per_overlap(const float* left, const float* right, float* out, int H, int W,
                                     PairMap pm, unsigned long long npairs, int block_threads,
-                                    int sm_count, dim3* grid_out, dim3* block_out, cudaStream_t stream) {
-    const unsigned long long OE = (unsigned long long)(2 * W - 1) * (2 * H - 1);
-    const unsigned long long nshifts = OE * npairs;
+                                    int rows_per_warp, int split, int sm_count, dim3* grid_out, dim3* block_out,
+                                    cudaStream_t stream) {
+    const unsigned long long OW = 2ull * W - 1, OH = 2ull * H - 1;
+    unsigned long long per_matrix = OW * OH;
+    if (split == kSplitRectangle) {
+        per_matrix *= (unsigned long long)((H + rows_per_warp - 1) / rows_per_warp);
+    } else if (split == kSplitTriangle) {
+        // sum over the output rows of ceil(overlapping rows / rows_per_warp)
+        unsigned long long workers = 0;
+        for (int y = 0; y < 2 * H - 1; ++y) {
+            const int n = y < H ? y + 1 : 2 * H - 1 - y;
+            workers += (unsigned long long)((n + rows_per_warp - 1) / rows_per_warp);
+        }
+        per_matrix = workers * OW;
+    }
+    const unsigned long long ntasks = per_matrix * npairs;
     const int wpb = block_threads / 32 > 0 ? block_threads / 32 : 1;
-    unsigned long long blocks = (nshifts + wpb - 1) / wpb;
+    unsigned long long blocks = (ntasks + wpb - 1) / wpb;
     const unsigned long long cap = (unsigned long long)sm_count * 64;
     if (blocks > cap) blocks = cap;
     dim3 grid((unsigned)blocks), block(wpb * 32);
-    warp_per_overlap_kernel<<<grid, block, 0, stream>>>(left, right, out, H, W, pm, nshifts);
+    warp_per_overlap_kernel<<<grid, block, 0, stream>>>(left, right, out, H, W, pm, ntasks, rows_per_warp, split);
     *grid_out = grid;
     *block_out = block;
     return cudaGetLastError();
+}
+
+size_t staged_smem_bytes(const StagedArgs& a) {
+    return 2ull * (size_t)(a.srows + a.shifts - 1 + a.rights * a.srows) * a.scols * sizeof(float);
+}
+
+template<int RMAX>
+static cudaError_t launch_staged_instance(const StagedArgs& a, dim3 grid, size_t smem, int device, cudaStream_t stream) {
+    static std::atomic<size_t> raised[kAttrDevices];
+    cudaError_t e = allow_smem(warp_staged_kernel<RMAX>, raised, device, smem);
+    if (e != cudaSuccess) return e;
+    warp_staged_kernel<RMAX><<<grid, a.shifts * 32, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_warp_staged(const StagedArgs& a, int device, dim3* grid_out, size_t* smem_out, cudaStream_t stream) {
+    const int OW = 2 * a.W - 1, OH = 2 * a.H - 1;
+    dim3 grid((unsigned)((unsigned long long)a.pm.n_left * a.groups_per_left * OW), (unsigned)((OH + a.shifts - 1) / a.shifts),
+              a.col_groups ? (unsigned)((a.W + a.scols - 1) / a.scols) : 1u);
+    const size_t smem = staged_smem_bytes(a);
+    *grid_out = grid;
+    *smem_out = smem;
+    if (a.rights <= 1) return launch_staged_instance<1>(a, grid, smem, device, stream);
+    if (a.rights <= 2) return launch_staged_instance<2>(a, grid, smem, device, stream);
+    if (a.rights <= 4) return launch_staged_instance<4>(a, grid, smem, device, stream);
+    return launch_staged_instance<8>(a, grid, smem, device, stream);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -913,7 +1187,10 @@ constexpr size_t kNoAllocScratchFloats = (size_t)8 << 20;            // 32 MiB
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
 
 cudaError_t tile_stage_timeouts(unsigned* count) {
-    return cudaMemcpyFromSymbol(count, g_stage_timeouts, sizeof(unsigned));
+    cudaError_t e = cudaMemcpyFromSymbol(count, g_stage_timeouts, sizeof(unsigned));
+    if (e != cudaSuccess || *count == 0) return e;
+    const unsigned zero = 0;                     // reported once: the next check starts from zero
+    return cudaMemcpyToSymbol(g_stage_timeouts, &zero, sizeof(unsigned));
 }
 
 size_t noalloc_scratch_bytes() { return kNoAllocScratchFloats * sizeof(float); }
@@ -921,23 +1198,31 @@ size_t noalloc_scratch_bytes() { return kNoAllocScratchFloats * sizeof(float); }
 // In host code `g_noalloc_scratch` is only a handle for the runtime, not a device address
 // a kernel could be given: the address is asked for once per device, with that device
 // current, and cached.
+constexpr int kScratchDevices = 64;
+static std::mutex g_scratch_mutex;
+static float* g_scratch_address[kScratchDevices] = {};
+
 cudaError_t noalloc_scratch_address(float** ptr) {
-    constexpr int kDevices = 64;
-    static std::mutex mutex;
-    static float* address[kDevices] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= kDevices) return cudaErrorInvalidDevice;
-    std::lock_guard<std::mutex> lock(mutex);
-    if (address[dev] == nullptr) {
+    if (dev < 0 || dev >= kScratchDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_address[dev] == nullptr) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess) return e;
-        address[dev] = static_cast<float*>(p);
+        g_scratch_address[dev] = static_cast<float*>(p);
     }
-    *ptr = address[dev];
+    *ptr = g_scratch_address[dev];
     return cudaSuccess;
+}
+
+// The addresses belong to the contexts they were asked in: after the application has reset a
+// device or destroyed its primary context they are stale and must be looked up again.
+void noalloc_forget_addresses() {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    for (float*& p : g_scratch_address) p = nullptr;
 }
 
 cudaError_t launch_ffma_probe(float* sink, int iters, int blocks, cudaStream_t stream) {

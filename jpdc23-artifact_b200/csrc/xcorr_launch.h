@@ -6,17 +6,25 @@
 
 namespace xcorr {
 
-cudaError_t launch_tile(const TileArgs& a, cudaStream_t stream);
+// `device` = the current device (remembers per device that the shared-memory limit was raised).
+cudaError_t launch_tile(const TileArgs& a, int device, cudaStream_t stream);
 cudaError_t launch_reduce_partials(const float* ws, float* out, unsigned long long total_out,
                                    int H, int W, int Hp, int S, int sm_count, cudaStream_t stream);
 cudaError_t launch_overlap_wise(const float* left, const float* right, float* out, int H, int W,
                                 PairMap pm, unsigned long long npairs, int block_threads,
                                 dim3* grid_out, dim3* block_out, cudaStream_t stream);
+// rows_per_warp / split (RowSplit): the overlap's rows shared by several warps adding atomically onto
+// a zeroed output; split = kSplitNone writes every overlap once.
 cudaError_t launch_warp_per_overlap(const float* left, const float* right, float* out, int H, int W,
                                     PairMap pm, unsigned long long npairs, int block_threads,
-                                    int sm_count, dim3* grid_out, dim3* block_out, cudaStream_t stream);
-// Number of bounded staging waits of the tile kernel that gave up on the current device since
-// the library was loaded (0 in every healthy run); synchronises with the device.
+                                    int rows_per_warp, int split, int sm_count, dim3* grid_out, dim3* block_out,
+                                    cudaStream_t stream);
+// Staged warp-per-overlap kernel; a.col_groups = 1 adds atomically onto a zeroed output.
+size_t staged_smem_bytes(const StagedArgs& a);
+cudaError_t launch_warp_staged(const StagedArgs& a, int device, dim3* grid_out, size_t* smem_out, cudaStream_t stream);
+// Number of blocks of the tile kernel whose bounded staging wait gave up on the current device
+// since the last call (0 in every healthy run); reads and clears the count, synchronises with
+// the device.
 cudaError_t tile_stage_timeouts(unsigned* count);
 // Double precision (xcorr_f64.cu): one warp per 8 output rows x 32 output columns of a pair.
 cudaError_t launch_strip_f64(const double* left, const double* right, double* out, int H, int W, PairMap pm,
@@ -29,6 +37,8 @@ cudaError_t launch_ffma_probe(float* sink, int iters, int blocks, cudaStream_t s
 // address on the current device (looked up once per device).
 size_t noalloc_scratch_bytes();
 cudaError_t noalloc_scratch_address(float** ptr);
+// Forget the cached addresses (after the application reset a device or tore its context down).
+void noalloc_forget_addresses();
 
 // FFT path (xcorr_fft.cu).  Workspace layout in bytes: padded real inputs, spectra of all
 // inputs, spectrum products (absent when they overwrite the right spectra: every mode but

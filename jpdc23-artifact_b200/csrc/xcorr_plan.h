@@ -80,6 +80,32 @@ struct TileArgs {
     PairMap pm;
     int vec_ok;        // rows may be fetched with 16-byte loads
     unsigned long long total_out;  // floats in the whole output array
+    unsigned stage_wait_limit;     // polls after which a wait on the staging barrier gives up
+    unsigned stage_expect_surplus; // test hook: bytes announced on the staging barrier that never arrive
 };
+
+// Default bound of the staging wait: ~4 million polls, a second or so; healthy copies land in microseconds.
+constexpr unsigned kStageWaitLimit = 1u << 22;
+
+// Arguments of the staged warp-per-overlap kernel: a block owns one x shift, `shifts` consecutive
+// y shifts (one per warp) and up to `rights` right matrices of one left; operands go through
+// shared memory in slabs of `srows` right rows x `scols` columns, two slabs in flight.
+struct StagedArgs {
+    const float* left;
+    const float* right;
+    float* out;
+    int H, W;
+    PairMap pm;
+    int shifts;        // warps per block = consecutive y shifts
+    int srows, scols;  // slab: right rows x columns
+    int rights;        // right matrices per block (1..8)
+    int col_groups;    // 1: every column slab is a block of its own (grid z), sums added atomically
+    int warp_rows;     // loader: 0 = threads stride over the slab's elements, 1 = a warp per row
+    unsigned groups_per_left;   // ceil(m / rights)
+};
+
+// Row split of the plain warp-per-overlap kernel: an overlap's rows are divided over several
+// warps ("workers") which add their sums atomically.
+enum RowSplit : int { kSplitNone = 0, kSplitRectangle = 1, kSplitTriangle = 2 };
 
 }  // namespace xcorr

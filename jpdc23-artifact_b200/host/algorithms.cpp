@@ -94,12 +94,12 @@ std::vector<algorithm_spec> build_registry() {
          {I("shifts_per_thread_block", 8)}, false},
         {"nai_warp_per_shift_work_distribution_one_to_one", O2O, family::warp_per_overlap,
          {I("shifts_per_thread_block", 8), I("rows_per_warp", 3), T("distribution_type", "rectangle")}, false},
-        {"nai_warp_per_shift_shared_mem_one_to_one", O2O, family::warp_per_overlap, smem(32), false},
-        {"nai_warp_per_shift_shared_mem_one_to_many", O2M, family::warp_per_overlap,
+        {"nai_warp_per_shift_shared_mem_one_to_one", O2O, family::warp_staged, smem(32), false},
+        {"nai_warp_per_shift_shared_mem_one_to_many", O2M, family::warp_staged,
          with(smem(16), {I("right_matrices_per_block", 8)}), false},
-        {"nai_warp_per_shift_shared_mem_n_to_mn", NMN, family::warp_per_overlap,
+        {"nai_warp_per_shift_shared_mem_n_to_mn", NMN, family::warp_staged,
          with(smem(16), {I("right_matrices_per_block", 8), streams}), false},
-        {"nai_warp_per_shift_shared_mem_n_to_m", N2M, family::warp_per_overlap,
+        {"nai_warp_per_shift_shared_mem_n_to_m", N2M, family::warp_staged,
          with(smem(16), {I("right_matrices_per_block", 8), streams}), false},
         {"nai_block_per_shift_one_to_one", O2O, family::warp_per_overlap, {I("block_size", 128)}, false},
         // FFT engine (main.cpp:403-409); argument keys of one_to_one.hpp:895,1029-1031, n_to_m.hpp:655-656
@@ -212,6 +212,33 @@ algorithm::algorithm(const algorithm_spec& spec, const json_object& args, double
         if (ints.count("shifts_per_thread_block")) threads = 32 * ints["shifts_per_thread_block"];
         if (ints.count("block_size")) threads = (ints["block_size"] + 31) / 32 * 32;
         hints_.block_threads = static_cast<int32_t>(std::min<long>(std::max<long>(threads, 32), 1024));
+        // nai_warp_per_shift_work_distribution_one_to_one: the rows of an overlap shared by several
+        // warps (one_to_one.hpp:470-520)
+        if (ints.count("rows_per_warp")) {
+            std::string dist = "rectangle";
+            for (const auto& pr : properties_)
+                if (pr.first == "distribution_type") dist = pr.second;
+            hints_.rows_per_warp = static_cast<int32_t>(ints["rows_per_warp"]);
+            hints_.row_split = dist == "none" ? XCORR_SPLIT_NONE : dist == "triangle" ? XCORR_SPLIT_TRIANGLE : XCORR_SPLIT_RECTANGLE;
+        }
+        break;
+    }
+    case family::warp_staged: {
+        // The shared-memory warp-per-overlap family (one_to_one.hpp:540-680, one_to_many.hpp:395-499,
+        // n_to_mn.hpp:575-716, n_to_m.hpp:520-645): every key shapes the launch.
+        hints_.kernel = XCORR_KERNEL_WARP_STAGED;
+        const long shifts = std::min<long>(std::max<long>(ints["shifts_per_thread_block"], 1), 32);
+        hints_.block_threads = static_cast<int32_t>(32 * shifts);
+        hints_.staged_cols = static_cast<int32_t>(ints["shared_mem_row_size"]);
+        hints_.staged_rows = static_cast<int32_t>(ints["shared_mem_rows"]);
+        hints_.staged_rights = static_cast<int32_t>(ints.count("right_matrices_per_block") ? ints["right_matrices_per_block"] : 1);
+        if (hints_.staged_rights > 8)      // WARP_PER_SHIFT_SHARED_MEM_RIGHT_MATRICES_PER_BLOCK_LIMIT (CMakeLists.txt:45)
+            throw argument_error("Invalid number of right matrices per block " + std::to_string(hints_.staged_rights) +
+                                 ", must be at most 8", "right_matrices_per_block");
+        for (const auto& pr : properties_) {
+            if (pr.first == "strided_load") hints_.staged_warp_rows = pr.second == "1" ? 0 : 1;
+            if (pr.first == "column_group_per_block") hints_.staged_column_groups = pr.second == "1" ? 1 : 0;
+        }
         break;
     }
     case family::fft:

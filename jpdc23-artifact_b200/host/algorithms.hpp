@@ -43,7 +43,7 @@ private:
     std::string arg_;
 };
 
-enum class family { cpu, overlap_wise, warp_per_overlap, tile, fft };
+enum class family { cpu, overlap_wise, warp_per_overlap, warp_staged, tile, fft };
 
 struct arg_spec {
     enum class kind { integer, boolean, text };

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol(xc):
 
 
 def test_hints_struct_layout(xc):
-    assert C.sizeof(xc.Hints) == 16 * 4
+    assert C.sizeof(xc.Hints) == 20 * 4
 
 
 def test_status_strings(xc):
@@ -142,7 +142,7 @@ def test_plans_exist_and_fit_for_a_sweep_of_shapes(xc):
         for mode, nl, nr in (("one_to_one", 1, 1), ("one_to_many", 1, int(rng.integers(1, 600))),
                              ("n_to_mn", 3, 3 * int(rng.integers(1, 40))), ("n_to_m", int(rng.integers(1, 20)), int(rng.integers(1, 70)))):
             text = xc.describe_plan(mode, rows, cols, nl, nr)
-            if text == "kernel=warp_per_overlap":          # a handful of overlaps: one warp per overlap
+            if text == "kernel=warp_staged":               # a handful of overlaps: the staged warp-per-overlap kernel
                 assert nl * (nr if mode != "n_to_mn" else nr // nl) * (2 * rows - 1) * (2 * cols - 1) <= 1500 or \
                     (mode == "n_to_mn" and nr * (2 * rows - 1) * (2 * cols - 1) <= 1500)
                 assert xc.workspace_bytes(mode, rows, cols, nl, nr) == 0
