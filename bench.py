@@ -224,6 +224,41 @@ def cpu_baseline(target_seconds: float, threads: int):
     return total_flop / total_s / 1e9, kind, "; ".join(parts)
 
 
+def cpu_single_thread():
+    """The reference's CPU path exactly as the reference runs it: one thread (validate.hpp:237 leaves
+    the pair loop sequential).  A small sample of every configuration: the whole of the two single
+    pairs, a few pairs of the three many-matrix ones.  Returns (GFLOP/s, description)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import pyoracle
+    if pyoracle.Reference.available():
+        ref = pyoracle.Reference()
+        run = lambda mode, l, r: ref.run_threaded(mode, l, r, 1)      # noqa: E731
+    else:
+        orc = pyoracle.Oracle()
+        run = lambda mode, l, r: orc.run(mode, l, r, threads=1)       # noqa: E731
+    sample = {"one_to_one": 1, "one_to_many": 4, "n_to_m": 16, "n_to_mn": 8}
+    flop, secs, parts = 0.0, 0.0, []
+    for k, (mode, r, c, nl, nr) in CONFIGS.items():
+        left, right = config_inputs(k)
+        n = sample[mode]
+        if mode == "one_to_one":
+            l, rt = left, right
+        elif mode == "one_to_many":
+            l, rt = left, right[:n]
+        elif mode == "n_to_m":
+            l, rt = left[:1], right[:n]
+        else:                                   # file order t*n + l: n_left lefts, one right each
+            n = nl
+            l, rt = left, right[:nl]
+        t0 = time.perf_counter()
+        run(mode, l, rt)
+        dt = time.perf_counter() - t0
+        flop += 2.0 * r * r * c * c * n
+        secs += dt
+        parts.append(f"{k}:{n} pairs {dt:.2f}s")
+    return flop / secs / 1e9, "; ".join(parts)
+
+
 # ---- the reference arm -----------------------------------------------------------------------------
 def reference_gpu_baseline(dev, iters=20):
     """The reference's own best CUDA kernels, recompiled unmodified for sm_100 (optional
@@ -237,10 +272,13 @@ def reference_gpu_baseline(dev, iters=20):
     if not pyoracle.ReferenceCuda.available():
         return None
     rc = pyoracle.ReferenceCuda()
+    wps = pyoracle.ReferenceWarpPerShift() if pyoracle.ReferenceWarpPerShift.available() else None
     side = [torch.cuda.Stream() for _ in range(8)]
     legacy = torch.cuda.default_stream()        # launchers without a stream argument use it
-    out = {"kind": "reference CUDA kernels (grouped-overlap / multi-matrix families) compiled for sm_100",
-           "args": {"one_to_one": "4_8_8", "one_to_many": "4_4_4_4", "n_to_mn": "4_4_4_4 on 8 streams",
+    out = {"kind": "reference CUDA kernels (warp-per-overlap for 16x16, grouped-overlap / multi-matrix families "
+                   "for the rest) compiled for sm_100",
+           "args": {"one_to_one 16x16": "warp_per_shift 16" if wps else "4_8_8 (warp_per_shift library not built)",
+                    "one_to_one": "4_8_8", "one_to_many": "4_4_4_4", "n_to_mn": "4_4_4_4 on 8 streams",
                     "n_to_m": "4_4_4_4_4"}, "per_config": {}}
     for k, (mode, r, c, nl, nr) in CONFIGS.items():
         if mode == "n_to_m" and rc.n2m is None:
@@ -251,7 +289,9 @@ def reference_gpu_baseline(dev, iters=20):
         L, R, O = d["left"].data_ptr(), d["right"].data_ptr(), res.data_ptr()
 
         def run():
-            if mode == "one_to_one":
+            if mode == "one_to_one" and wps is not None and r * c <= 32 * 32:
+                wps.warp_per_shift(L, R, O, r, c, 16)      # the reference's published winner at 16 x 16
+            elif mode == "one_to_one":
                 rc.one_to_one(L, R, O, r, c)
             elif mode == "one_to_many":
                 rc.one_to_many(L, R, O, r, c, nr)
@@ -395,6 +435,7 @@ def run_grid(args):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import pyoracle
     rc = pyoracle.ReferenceCuda() if pyoracle.ReferenceCuda.available() else None
+    wps = pyoracle.ReferenceWarpPerShift() if pyoracle.ReferenceWarpPerShift.available() else None
     side = [torch.cuda.Stream() for _ in range(8)]
     legacy = torch.cuda.default_stream()
     gen = torch.Generator(device="cuda").manual_seed(1234)
@@ -445,7 +486,9 @@ def run_grid(args):
             del fws
             if rc is not None and flop <= 0.2 * args.grid_max_tflop * 1e12 and not (mode == "n_to_m" and rc.n2m is None):
                 def ref():
-                    if mode == "one_to_one":
+                    if mode == "one_to_one" and wps is not None and r * c <= 32 * 32:
+                        wps.warp_per_shift(L, R, O, r, c, 16)
+                    elif mode == "one_to_one":
                         rc.one_to_one(L, R, O, r, c)
                     elif mode == "one_to_many":
                         rc.one_to_many(L, R, O, r, c, nr)
@@ -469,7 +512,8 @@ def run_grid(args):
             del left, right, out, direct, ws
             torch.cuda.empty_cache()
     xc.check_device()
-    print(json.dumps({"grid": rows_out, "reference_args": {"one_to_one": "4_8_8", "one_to_many": "4_4_4_4",
+    print(json.dumps({"grid": rows_out, "reference_args": {"one_to_one up to 32x32": "warp_per_shift 16" if wps else "4_8_8",
+                                                            "one_to_one": "4_8_8", "one_to_many": "4_4_4_4",
                                                             "n_to_mn": "4_4_4_4", "n_to_m": "4_4_4_4_4"}}))
     return 0
 
@@ -510,6 +554,18 @@ def run_reference_arm(args):
     }
     print(json.dumps(line))
     return 0
+
+
+def plan_signature(plan_text):
+    """The part of a launch string that identifies the plan: kernel, grid, block, schedule, combine."""
+    import re
+    m = re.search(r"kernel=(\S+) grid=\((\d+),.*?block=\((\d+),", plan_text)
+    sched = re.search(r"schedule=([a-z-]+)", plan_text)
+    comb = re.search(r"combine=([a-z]+)", plan_text)
+    if not m:
+        return plan_text.split(" ")[0]
+    return "%s/grid=%s/block=%s/%s/%s" % (m.group(1), m.group(2), m.group(3), sched.group(1) if sched else "-",
+                                          comb.group(1) if comb else "-")
 
 
 def workload_config(n_gpus):
@@ -604,8 +660,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
+    host_group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        host_group = dist.new_group(backend="gloo")     # barriers that keep waiting ranks off their GPUs
     warmup = max(3, args.warmup)
     stream = torch.cuda.current_stream().cuda_stream
 
@@ -631,6 +689,11 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def host_barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group=host_group)
 
     for _ in range(warmup):
         for k in CONFIGS:
@@ -738,6 +801,53 @@ def main():
     for k in CONFIGS:
         host[k][2].zero_()
     e2e_ms = time_e2e(e2e_batch_pass)
+
+    # ---- what the host links can carry: the same pinned bytes per step, copies only, all ranks at once
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def copies_only():
+        for k in CONFIGS:
+            hl, hr, ho = host[k]
+            with torch.cuda.stream(copy_in):
+                dev[k]["left"].copy_(hl, non_blocking=True)
+                dev[k]["right"].copy_(hr, non_blocking=True)
+            with torch.cuda.stream(copy_out):
+                ho.copy_(dev[k]["out"], non_blocking=True)
+        copy_in.synchronize()
+        copy_out.synchronize()
+    link_ms = time_e2e(copies_only)
+
+    # ---- the library's own multi-GPU call: rank 0 alone runs xcorr_run_host_sharded_f32 over all N
+    #      devices on the fixed configurations; the other ranks wait on the host, off their GPUs
+    sharded_api = {}
+    if world > 1:
+        host_barrier()
+        if rank == 0:
+            devs = (xc.C.c_int32 * world)(*range(world))
+            for k, (mode, r, c, nl, nr) in CONFIGS.items():
+                if mode == "one_to_one":
+                    continue
+                hl, hr, ho = host[k]
+
+                def one_gpu():
+                    xc.check(lib.xcorr_run_host_f32(xc.MODES[mode], hl.data_ptr(), hr.data_ptr(), ho.data_ptr(),
+                                                    r, c, nl, nr, None, local_rank))
+
+                def all_gpus():
+                    xc.check(lib.xcorr_run_host_sharded_f32(xc.MODES[mode], hl.data_ptr(), hr.data_ptr(), ho.data_ptr(),
+                                                            r, c, nl, nr, None, devs, world))
+                res = {}
+                for name, fn in (("ms_1gpu", one_gpu), ("ms_ngpu", all_gpus)):
+                    for _ in range(2):
+                        fn()
+                    t0 = time.perf_counter()
+                    for _ in range(e2e_steps):
+                        fn()
+                    res[name] = (time.perf_counter() - t0) * 1e3 / e2e_steps
+                res["speedup"] = res["ms_1gpu"] / res["ms_ngpu"]
+                res["gflops"] = flop_of(k) / (res["ms_ngpu"] * 1e-3) / 1e9
+                sharded_api[k] = res
+        host_barrier()
     last = list(CONFIGS)[-1]
     checksum = float(host[last][2].reshape(-1)[0])   # a device result read on the host
     barrier()
@@ -750,12 +860,13 @@ def main():
 
     # ---- max over ranks
     vec = max_over_ranks([region_ms, e2e_ms] + [per_ms[k] for k in CONFIGS] +
-                         [strong_ms.get(k, 0.0) for k in CONFIGS] + [e2e_percall_ms],
+                         [strong_ms.get(k, 0.0) for k in CONFIGS] + [link_ms, e2e_percall_ms],
                          dist if world > 1 else None, "cuda")
     e2e_percall_ms = vec[-1]
+    link_ms = vec[-2]
     region_ms, e2e_ms = vec[0], vec[1]
     per_ms_max = dict(zip(CONFIGS, vec[2:2 + len(CONFIGS)]))
-    strong_max = dict(zip(CONFIGS, vec[2 + len(CONFIGS):]))
+    strong_max = dict(zip(CONFIGS, vec[2 + len(CONFIGS):2 + 2 * len(CONFIGS)]))
 
     if rank == 0:
         ms_per_step = region_ms / args.steps
@@ -784,13 +895,21 @@ def main():
                                    "shifts_per_s": shifts_of(k) / ts if ts > 0 else None}
             per_config[k] = entry
         dom = max(CONFIGS, key=lambda k: per_ms_max[k])
-        traffic = None     # DRAM bytes per launch of the dominant kernel, from the committed ncu summary
+        # DRAM bytes per launch of the dominant kernel: not measurable inside this run (it takes a
+        # profiler); the committed capture's figure is given only when it was taken for the very plan
+        # that ran now (profiles/dram_traffic.txt: configuration, bytes, plan signature)
+        traffic, traffic_note = None, "no capture on file for this configuration"
         tp = os.path.join(ROOT, "profiles", "dram_traffic.txt")
         if os.path.exists(tp):
             for tl in open(tp):
-                parts = tl.split()
-                if len(parts) == 2 and parts[0] == dom:
-                    traffic = int(parts[1])
+                parts = tl.split(None, 2)
+                if len(parts) == 3 and parts[0] == dom:
+                    if parts[2].strip() == plan_signature(plans[dom]):
+                        traffic = int(parts[1])
+                        traffic_note = "ncu capture profiles/tile_kernel_%s.md, plan %s" % (dom, parts[2].strip())
+                    else:
+                        traffic_note = ("the capture on file is for plan %s, this run used %s: figure withheld"
+                                        % (parts[2].strip(), plan_signature(plans[dom])))
         achieved = flop_of(dom) / (per_ms_max[dom] * 1e-3) / 1e12
         roofline = {
             "bound": "fp32_ffma", "kernel": plans[dom].split(" ")[0].replace("kernel=", "") + f" ({dom})",
@@ -798,7 +917,7 @@ def main():
             "frac": achieved / (ffma_flops / 1e12),
             "peak_source": "of measured: register-only FFMA probe on this GPU in this run "
                            f"(nominal 148 SM x 128 lanes x 2 x {sm_max:.0f} MHz = {nominal_peak / 1e12:.1f})",
-            "traffic": traffic,
+            "traffic": traffic, "traffic_source": traffic_note,
             "hbm": {"achieved": bytes_of(dom) / (per_ms_max[dom] * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                     "frac": bytes_of(dom) / (per_ms_max[dom] * 1e-3) / 1e9 / hbm_peak,
                     "note": "compulsory bytes / time: far below the HBM roofline, the kernel is FFMA-bound"},
@@ -822,6 +941,12 @@ def main():
                     "per_call": {"value": world * flop_step / (e2e_percall_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                                  "ms_per_step": e2e_percall_ms,
                                  "api": "xcorr_run_host_f32, one call per configuration"},
+                    "link_ceiling": {
+                        "ms_per_step": link_ms,
+                        "gbs": world * sum(bytes_of(k) for k in CONFIGS) / (link_ms * 1e-3) / 1e9,
+                        "what": "the same pinned bytes per step, copies only (H2D and D2H on two streams), "
+                                "all ranks at once, max over ranks"},
+                    "frac_of_link_ceiling": link_ms / e2e_ms,
                     "host_affinity": host_affinity, "result_probe": checksum},
             "gpu_launches": int(launches),
         }
@@ -840,7 +965,19 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             v, kind, desc = cpu_baseline(args.cpu_seconds, threads)
-            line["cpu_baseline"] = {"value": v, "unit": "GFLOP/s", "cores": threads, "kind": kind, "sample": desc}
+            v1, desc1 = cpu_single_thread()
+            line["cpu_baseline"] = {"value": v, "unit": "GFLOP/s", "cores": threads, "kind": kind, "sample": desc,
+                                    "single_thread": {"value": v1, "unit": "GFLOP/s", "threads": 1, "sample": desc1,
+                                                      "note": "how the reference itself runs its CPU path"}}
+        # last key of the line: the fixed-size (strong) figures in compact form
+        summary = {"n_gpus": world, "e2e_ms": round(e2e_ms, 4), "link_ceiling_ms": round(link_ms, 4)}
+        if world > 1:
+            summary["strong"] = {
+                k: {"ms_1gpu": round(per_ms_max[k], 4), "ms_ngpu": round(strong_max[k], 4),
+                    "eff": round(per_ms_max[k] / (world * strong_max[k]), 3) if strong_max[k] > 0 else None}
+                for k in strong_ms}
+            summary["sharded_api"] = {k: {kk: round(vv, 4) for kk, vv in v.items()} for k, v in sharded_api.items()}
+        line["scaling_summary"] = summary
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -512,7 +512,7 @@ int pick_kernel(const xcorr_hints* h) {
 // kernel.  Not for callers who asked for specific plans.
 bool tiny_auto(const xcorr_hints* h, const PairMap& pm, uint32_t rows, uint32_t cols) {
     if (h && (h->kernel != XCORR_KERNEL_AUTO || h->combine || h->overlap_rows || h->class_lanes || h->warps_x ||
-              h->warps_y || h->row_slices || h->schedule || h->block_threads || h->reproducible))
+              h->warps_y || h->row_slices || h->schedule || h->block_threads))
         return false;
     return (double)pm.n_left * pm.m * (2.0 * rows - 1) * (2.0 * cols - 1) <= 1500.0;
 }

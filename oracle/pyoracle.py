@@ -280,3 +280,28 @@ class ReferenceCuda:
             raise RuntimeError("the reference n-to-m kernel library was not built (make -C oracle refcuda_n2m)")
         self._check(self.n2m.refcuda_n_to_m(d_left, d_right, d_out, rows, cols, n_left, n_right, warps, shifts,
                                             left_mats, right_mats, left_rows), "n_to_m")
+
+
+REFCUDA_WPS_SO = os.path.join(_HERE, "_ref", "libxcorr_refcuda_wps.so")
+
+
+class ReferenceWarpPerShift:
+    """The reference's plain warp-per-overlap launcher ``run_ccn_warp_per_shift``
+    (kernels.cuh:98-106, naive_warp_per_shift.cu:308-335), compiled unmodified for sm_100 by
+    ``make -C oracle refcuda_wps``: the reference's published winner for a 16 x 16 pair.  Device
+    pointers (ints), asynchronous launch on the default stream, one pair per call."""
+
+    def __init__(self, path: str = REFCUDA_WPS_SO):
+        self.lib = C.CDLL(path)
+        u32, vp, i = C.c_uint32, C.c_void_p, C.c_int
+        self.lib.refcuda_warp_per_shift.argtypes = [vp, vp, vp, u32, u32, u32]
+        self.lib.refcuda_warp_per_shift.restype = i
+
+    @staticmethod
+    def available(path: str = REFCUDA_WPS_SO) -> bool:
+        return os.path.exists(path)
+
+    def warp_per_shift(self, d_left, d_right, d_out, rows, cols, shifts_per_block=16):
+        rc = self.lib.refcuda_warp_per_shift(d_left, d_right, d_out, rows, cols, shifts_per_block)
+        if rc != 0:
+            raise RuntimeError(f"reference launcher warp_per_shift rejected its arguments (code {rc})")

@@ -327,6 +327,78 @@ def test_gpu_algorithms_files_match_the_oracle(cross, oracle, tmp_path, alg, mod
         assert vals[cols_.index(k)] == str(v)
 
 
+# one small shape per mode, ragged in both directions, counts that leave partial matrix groups
+ALL_NAMES_SHAPES = {"one_to_one": (19, 21, 1, 1), "one_to_many": (18, 20, 1, 11),
+                    "n_to_mn": (12, 17, 3, 9), "n_to_m": (14, 13, 3, 5)}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("alg", EXPECTED_NAMES)
+def test_every_registry_name_writes_the_oracle_result(cross, oracle, tmp_path, alg):
+    """Every name `cross list` prints (main.cpp:368-409), default arguments: the result file
+    equals the oracle's.  FFT names are run with --normalize so that the file has the direct
+    algorithms' layout."""
+    mode = next(m for m in ("one_to_one", "one_to_many", "n_to_mn", "n_to_m") if alg.endswith(m))
+    rows, cols, nl, nr = ALL_NAMES_SHAPES[mode]
+    left, right = seeded_inputs(rows, cols, nl, nr, 41)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    extra = ["--normalize"] if alg.startswith("fft") else []
+    r = run(cross, "run", "--out", tmp_path / "o.csv", *extra, alg, tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    want = oracle.run(mode, left, right, acc64=True)
+    got = read_matrices(tmp_path / "o.csv")
+    assert got.shape == want.shape
+    # the file holds six decimals (matrix.hpp:169-185): half a unit of the last one on top of the tolerance
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max() + 5.1e-7, alg
+
+
+STAGED_KEYS = [
+    ("nai_warp_per_shift_shared_mem_one_to_one", "one_to_one", 40, 37, 1, 1,
+     {"shifts_per_thread_block": 4, "shared_mem_row_size": 16, "shared_mem_rows": 8}),
+    ("nai_warp_per_shift_shared_mem_one_to_one", "one_to_one", 33, 70, 1, 1,
+     {"shifts_per_thread_block": 8, "shared_mem_row_size": 32, "shared_mem_rows": 8, "column_group_per_block": True}),
+    ("nai_warp_per_shift_shared_mem_one_to_one", "one_to_one", 21, 50, 1, 1,
+     {"shifts_per_thread_block": 16, "shared_mem_rows": 16, "strided_load": False}),
+    ("nai_warp_per_shift_shared_mem_one_to_many", "one_to_many", 20, 24, 1, 13,
+     {"shifts_per_thread_block": 8, "shared_mem_rows": 12, "right_matrices_per_block": 3}),
+    ("nai_warp_per_shift_shared_mem_n_to_mn", "n_to_mn", 16, 18, 3, 15,
+     {"right_matrices_per_block": 4, "column_group_per_block": True, "shared_mem_row_size": 8}),
+    ("nai_warp_per_shift_shared_mem_n_to_m", "n_to_m", 17, 16, 2, 9,
+     {"right_matrices_per_block": 8, "strided_load": False}),
+    ("nai_warp_per_shift_work_distribution_one_to_one", "one_to_one", 30, 22, 1, 1,
+     {"rows_per_warp": 4, "distribution_type": "rectangle"}),
+    ("nai_warp_per_shift_work_distribution_one_to_one", "one_to_one", 30, 22, 1, 1,
+     {"rows_per_warp": 7, "distribution_type": "triangle"}),
+    ("nai_warp_per_shift_work_distribution_one_to_one", "one_to_one", 9, 40, 1, 1,
+     {"rows_per_warp": 2, "distribution_type": "none"}),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", range(len(STAGED_KEYS)))
+def test_warp_per_overlap_families_honour_their_keys(cross, oracle, tmp_path, case):
+    """The shared-memory warp-per-overlap names and the row-split one: every JSON key of the
+    reference's classes (one_to_one.hpp:470-680, one_to_many.hpp:395-499) shapes the launch --
+    the results under each setting equal the oracle's, and the timing file echoes the values."""
+    alg, mode, rows, cols, nl, nr, args = STAGED_KEYS[case]
+    left, right = seeded_inputs(rows, cols, nl, nr, 43 + case)
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    (tmp_path / "args.json").write_text(json.dumps(args))
+    r = run(cross, "run", "--out", tmp_path / "o.csv", "--times", tmp_path / "t.csv", "--args_path", tmp_path / "args.json",
+            "--benchmark_type", "Algorithm", "--min_time", "0.002", alg, tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    want = oracle.run(mode, left, right, acc64=True)
+    got = read_matrices(tmp_path / "o.csv")
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max() + 5.1e-7
+    head, row = open(tmp_path / "t.csv").read().splitlines()[:2]
+    for k, v in args.items():
+        shown = {True: "1", False: "0"}.get(v, str(v)) if isinstance(v, bool) else str(v)
+        assert row.split(",")[head.split(",").index(k)] == shown
+
+
 @pytest.mark.gpu
 def test_gpu_property_columns_follow_the_reference_order(cross, tmp_path):
     left, right = seeded_inputs(16, 16, 2, 4, 2)

@@ -24,9 +24,16 @@ def rel_err(got, want64):
     return float(np.abs(got.astype(np.float64) - want64).max() / np.abs(want64).max())
 
 
+GUARD_FLOATS = 256          # words of a known pattern kept on both sides of every output and workspace
+GUARD_VALUE = -7.25e30
+
+
 def gpu_run(xc, mode, left, right, hints=None, with_workspace=True):
     """Run one launch through the device-pointer entry point; returns a numpy result.
-    n_to_mn inputs/outputs are in GROUPED order here."""
+    n_to_mn inputs/outputs are in GROUPED order here.  The output and the workspace sit inside
+    larger allocations whose first and last GUARD_FLOATS words hold a pattern that must survive
+    the launch: a store one row or one matrix past either end would be seen (the stand-in for a
+    memory checker run, for every plan the tests force: slices, stream-K, fix-up, warp queue)."""
     left = np.ascontiguousarray(left, np.float32)
     right = np.ascontiguousarray(right, np.float32)
     nl, rows, cols = left.shape
@@ -34,14 +41,22 @@ def gpu_run(xc, mode, left, right, hints=None, with_workspace=True):
     dl = torch.from_numpy(left).cuda()
     dr = torch.from_numpy(right).cuda()
     shape = xc.out_shape(mode, rows, cols, nl, nr)
-    out = torch.full(shape, float("nan"), dtype=torch.float32, device="cuda")
+    n_out = int(np.prod(shape))
+    out_all = torch.full((n_out + 2 * GUARD_FLOATS,), GUARD_VALUE, dtype=torch.float32, device="cuda")
+    out = out_all[GUARD_FLOATS:GUARD_FLOATS + n_out]
+    out.fill_(float("nan"))
     wsb = xc.workspace_bytes(mode, rows, cols, nl, nr, hints) if with_workspace else 0
-    ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device="cuda")
+    ws_floats = (wsb + 3) // 4
+    ws_all = torch.full((ws_floats + 2 * GUARD_FLOATS,), GUARD_VALUE, dtype=torch.float32, device="cuda")
+    ws_ptr = ws_all.data_ptr() + 4 * GUARD_FLOATS          # 1 KiB into a 256-byte aligned allocation
     stream = torch.cuda.current_stream().cuda_stream
     xc.run_device(mode, dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols, nl, nr, hints,
-                  ws.data_ptr() if wsb else 0, wsb, stream)
+                  ws_ptr if wsb else 0, wsb, stream)
     torch.cuda.synchronize()
-    return out.cpu().numpy()
+    for name, buf, n in (("output", out_all, n_out), ("workspace", ws_all, ws_floats)):
+        assert bool((buf[:GUARD_FLOATS] == GUARD_VALUE).all()), f"write before the {name}: {xc.last_launch()}"
+        assert bool((buf[GUARD_FLOATS + n:] == GUARD_VALUE).all()), f"write past the {name}: {xc.last_launch()}"
+    return out.reshape(shape).cpu().numpy()
 
 
 def oracle_grouped(oracle, mode, left, right, acc64=True, threads=None):
@@ -58,6 +73,8 @@ KERNEL_HINTS = {
     "tile_auto": dict(kernel="tile"),
     "overlap_wise": dict(kernel="overlap_wise"),
     "warp_per_overlap": dict(kernel="warp_per_overlap", block_threads=128),
+    "warp_per_overlap_split": dict(kernel="warp_per_overlap", block_threads=64, rows_per_warp=3, row_split="triangle"),
+    "warp_staged": dict(kernel="warp_staged"),
 }
 
 
@@ -493,6 +510,31 @@ def test_reference_cuda_kernels_agree(xc, oracle, mode, rows, cols, nl, nr):
     assert rel_err(ours, theirs.astype(np.float64)) <= 2e-5
 
 
+@pytest.mark.parametrize("rows,cols", [(16, 16), (24, 24), (32, 32), (9, 20)])
+def test_reference_warp_per_shift_kernel_agrees(xc, oracle, rows, cols):
+    """The reference's plain warp-per-overlap kernel (its winner at 16 x 16), compiled for this GPU
+    where the reference checkout was present at build time, against this library's two
+    warp-per-overlap kernels and the oracle."""
+    import pyoracle
+    if not pyoracle.ReferenceWarpPerShift.available():
+        pytest.skip("oracle/_ref/libxcorr_refcuda_wps.so not built")
+    ref = pyoracle.ReferenceWarpPerShift()
+    left, right = seeded_inputs(rows, cols, 1, 1, 78)
+    want = oracle.run("one_to_one", left, right, acc64=True)
+    dl, dr = torch.from_numpy(left).cuda(), torch.from_numpy(right).cuda()
+    out = torch.full(want.shape, float("nan"), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    ref.warp_per_shift(dl.data_ptr(), dr.data_ptr(), out.data_ptr(), rows, cols, 16)
+    torch.cuda.synchronize()
+    theirs = out.cpu().numpy()
+    assert not np.isnan(theirs).any()
+    assert rel_err(theirs, want) <= 2e-5
+    for kernel in ("warp_staged", "warp_per_overlap"):
+        ours = gpu_run(xc, "one_to_one", left, right, xc.make_hints(kernel=kernel))
+        assert rel_err(ours, want) <= REL_TOL, kernel
+        assert rel_err(ours, theirs.astype(np.float64)) <= 2e-5, kernel
+
+
 # ---- FFT path ---------------------------------------------------------------------------------
 def fft_run(xc, mode, left, right, layout="normalized"):
     left = np.ascontiguousarray(left, np.float32)
@@ -638,6 +680,95 @@ def test_device_health_after_all_launches(xc):
     xc.check_device()
 
 
+STAGED_VARIANTS = [
+    dict(),                                                       # automatic slab
+    dict(block_threads=32),                                       # one y shift per block
+    dict(block_threads=128, staged_rows=4, staged_cols=8),        # many small slabs, both directions
+    dict(block_threads=512, staged_rows=16, staged_cols=32, staged_rights=3),
+    dict(block_threads=256, staged_rows=3, staged_cols=5, staged_rights=8, staged_warp_rows=1),
+    dict(block_threads=256, staged_cols=16, staged_column_groups=1),
+    dict(block_threads=64, staged_rows=7, staged_cols=11, staged_column_groups=1, staged_rights=2, staged_warp_rows=1),
+    dict(block_threads=1024, staged_rows=40, staged_cols=64, staged_rights=1),
+]
+
+
+@pytest.mark.parametrize("variant", range(len(STAGED_VARIANTS)))
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [
+    ("one_to_one", 16, 16, 1, 1),
+    ("one_to_one", 37, 70, 1, 1),
+    ("one_to_many", 21, 18, 1, 11),
+    ("n_to_mn", 9, 33, 3, 15),
+    ("n_to_m", 20, 12, 3, 5),
+])
+def test_staged_warp_per_overlap_variants(xc, oracle, mode, rows, cols, nl, nr, variant):
+    """The staged warp-per-overlap kernel under every key of the reference's shared-memory family
+    (shifts per block, slab rows and columns, rights per block, column groups, load pattern),
+    slabs that do and do not divide the overlap, right-matrix counts that leave a partial group."""
+    hints = xc.make_hints(kernel="warp_staged", **STAGED_VARIANTS[variant])
+    left, right = seeded_inputs(rows, cols, nl, nr, 700 + variant)
+    want = oracle_grouped(oracle, mode, left, right)
+    got = gpu_run(xc, mode, left, right, hints)
+    assert "kernel=warp_staged" in xc.last_launch()
+    assert not np.isnan(got).any(), xc.last_launch()
+    assert rel_err(got, want) <= REL_TOL, xc.last_launch()
+
+
+@pytest.mark.parametrize("split,rpw", [("rectangle", 1), ("rectangle", 5), ("triangle", 1), ("triangle", 4),
+                                       ("triangle", 100), ("none", 3)])
+@pytest.mark.parametrize("mode,rows,cols,nl,nr", [("one_to_one", 16, 16, 1, 1), ("one_to_one", 23, 40, 1, 1),
+                                                  ("n_to_m", 11, 9, 2, 3)])
+def test_warp_per_overlap_row_split(xc, oracle, mode, rows, cols, nl, nr, split, rpw):
+    """Rows of an overlap shared by several warps that add atomically (the reference's
+    rows_per_warp / distribution_type): both ways of counting the workers, worker counts that do
+    and do not divide the rows, more rows per warp than the matrix has."""
+    hints = xc.make_hints(kernel="warp_per_overlap", block_threads=96, rows_per_warp=rpw, row_split=split)
+    left, right = seeded_inputs(rows, cols, nl, nr, 800 + rpw)
+    want = oracle_grouped(oracle, mode, left, right)
+    got = gpu_run(xc, mode, left, right, hints)
+    assert f"split={split}" in xc.last_launch()
+    assert not np.isnan(got).any(), xc.last_launch()
+    assert rel_err(got, want) <= REL_TOL, xc.last_launch()
+
+
+def test_staged_and_split_hints_are_checked(xc):
+    left, right = seeded_inputs(8, 8, 1, 1, 1)
+    for bad in (dict(kernel="warp_staged", staged_rights=9), dict(kernel="warp_staged", staged_rows=-1),
+                dict(kernel="warp_staged", block_threads=48), dict(kernel="warp_per_overlap", row_split=3),
+                dict(kernel="warp_per_overlap", row_split="triangle", rows_per_warp=0)):
+        with pytest.raises(xc.XcorrError) as e:
+            gpu_run(xc, "one_to_one", left, right, xc.make_hints(**bad))
+        assert e.value.status == 3, bad
+    # slabs larger than one SM's shared memory are refused, not launched
+    big_l, big_r = seeded_inputs(300, 300, 1, 1, 2)
+    with pytest.raises(xc.XcorrError) as e:
+        gpu_run(xc, "one_to_one", big_l, big_r, xc.make_hints(kernel="warp_staged", staged_rows=300, staged_cols=300))
+    assert e.value.status == 6 and "shared memory" in str(e.value)
+
+
+def test_bounded_staging_wait_gives_up_and_reports(xc, oracle):
+    """The one device-side wait of the library (a block waiting for its bulk copies) is bounded.
+    The test hook announces 64 bytes more than the copies deliver and lowers the poll limit, so
+    the wait runs out: no fault, no hang -- the blocks drop their work, the launch is reported as
+    XCORR_ERR_TIMEOUT by the device check (once), and the next launch is right again."""
+    lib = xc.lib()
+    xc.check_device()
+    left, right = seeded_inputs(32, 32, 1, 6, 77)         # cols a multiple of 16: the bulk staging path
+    want = oracle_grouped(oracle, "one_to_many", left, right)
+    hints = xc.make_hints(kernel="tile")
+    lib.xcorr_debug_stage_wait(64, 64)
+    try:
+        gpu_run(xc, "one_to_many", left, right, hints)
+        assert "kernel=tile" in xc.last_launch()
+        assert lib.xcorr_check_device() == 8
+        assert "gave up" in lib.xcorr_last_error_string().decode()
+    finally:
+        lib.xcorr_debug_stage_wait(0, 0)
+    xc.check_device()                                      # the count was cleared by the report
+    got = gpu_run(xc, "one_to_many", left, right, hints)
+    assert rel_err(got, want) <= REL_TOL
+    xc.check_device()
+
+
 def test_rows_too_wide_for_the_tile_kernel_fall_back(xc, oracle):
     """A staged left row of 6000 columns leaves no tile plan that fits one SM's shared memory:
     the automatic choice runs the overlap-wise kernel instead (slow, any size); asking for the
@@ -666,7 +797,7 @@ def test_reproducible_hint_gives_bit_identical_runs(xc, oracle, mode, rows, cols
     a = gpu_run(xc, mode, left, right, h)
     plan = xc.last_launch()
     assert ("combine=store" in plan or "combine=workspace" in plan or "combine=fixup" in plan or
-            "schedule=stream-k" in plan or "warp_per_overlap" in plan)
+            "schedule=stream-k" in plan or "warp_staged" in plan)
     for _ in range(3):
         assert np.array_equal(a, gpu_run(xc, mode, left, right, h)), plan
     assert rel_err(a, oracle_grouped(oracle, mode, left, right)) <= REL_TOL
