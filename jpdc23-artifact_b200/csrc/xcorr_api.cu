@@ -146,7 +146,7 @@ int largest_divisor_at_most(int n, int cap) {
 }
 
 // Fill the fields that follow from (TY, SL, WX, WY, S).
-void finish_plan(TilePlan& p, const PairMap& pm) {
+void finish_plan(TilePlan& p, const PairMap& pm, size_t smem_limit = kSmemLimit) {
     p.ML = 32 / p.SL;
     p.logSL = ilog2(p.SL);
     p.Wp = round_up(p.W, kTX);
@@ -163,9 +163,14 @@ void finish_plan(TilePlan& p, const PairMap& pm) {
     p.LS = p.Wp + 4;
     p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
     p.threads = 32 * p.WX * p.WY;
-    // staged left rows, staged right rows, per-warp flush staging
-    p.smem_bytes = ((size_t)p.nstage * p.LS + (size_t)p.ML * p.RMS) * sizeof(float) +
-                   (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;   // + the warp queue's counter
+    // staged left rows and per-warp flush staging (+ the warp queue's counter and the staging barrier)
+    const size_t fixed = (size_t)p.nstage * p.LS * sizeof(float) + (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;
+    const size_t per_group = (size_t)p.ML * p.RMS * sizeof(float);
+    // the warp queue stages as many matrix groups of a left together as fit (a round of its tasks)
+    p.KG = 1;
+    if (p.schedule == kSchedWarpQueue && smem_limit > fixed + per_group)
+        p.KG = (int)std::max<size_t>(1, std::min<size_t>(std::min<size_t>((size_t)p.RG, 16), (smem_limit - fixed) / per_group));
+    p.smem_bytes = fixed + (size_t)p.KG * per_group;
 }
 
 // Workspace of a stream-K plan with fix-up: `pieces` partial images, then one counter per task.
@@ -286,7 +291,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
             const double sm_rate = 128.0 * 1.8e9 * 0.8;
             for (const Cand& c : cands) {
                 p.WX = c.WX; p.WY = c.WY; p.S = c.S; p.schedule = c.sched;
-                finish_plan(p, pm);
+                finish_plan(p, pm, dev.smem_optin);
                 if (p.smem_bytes > dev.smem_optin) continue;
                 if (c.sched == kSchedStatic && want_combine == XCORR_COMBINE_WORKSPACE &&
                     (double)c.S * out_bytes > (double)max_workspace_bytes) continue;
@@ -324,19 +329,21 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 int sk_parts = 0;
                 unsigned grid;
                 if (c.sched == kSchedWarpQueue) {
-                    const double per_group = (double)p.NGY * p.NTX;
-                    const double wtasks = groups * per_group;
+                    // pass tasks (one pass of one warp tile, all rows) of unequal lengths, cut evenly by
+                    // weight over one resident wave of blocks and taken longest first by the warps
+                    const double units = groups * p.NGY * (double)queue_units_per_yrow(p.NTX);   // quarter chunks per row
+                    const double ptasks = groups * p.NGY * 2.0 * p.NTX;
                     double G = (double)dev.sm_count * blocks_sm;
-                    if (G > wtasks) G = wtasks;
+                    if (G > ptasks) G = ptasks;
                     grid = (unsigned)G;
-                    const double macs_per_wtask = 32.0 * H * p.Wp * TY * kTX;
-                    const double per_block = std::ceil(wtasks / G);
-                    const double phases = wtasks / G / per_group + 1.0;
-                    // a warp is bound to one of the SM's four schedulers and a task cannot be
-                    // shared: the busiest scheduler runs ceil(tasks of the block / 4) tasks
-                    const double t_rate = std::ceil(G / dev.sm_count) *
-                                          (4.0 * std::ceil(per_block / 4.0) * macs_per_wtask / rate + phases * t_stage);
-                    const double t_serial = std::ceil(per_block / warps_blk) * H * p.Wp * TY * kTX / 1.8e9;
+                    const double units_block = units / G;
+                    const double macs_per_unit = 32.0 * H * 2.0 * TY * kTX;          // a quarter chunk of every row
+                    // the busiest scheduler ends at most about one longest task after the average
+                    const double longest = 4.0 * (p.NCH - 2) + kQueueTriangleWeight;
+                    const double per_sched = units_block / 4.0 + 0.5 * longest / std::max(1.0, units_block / 4.0 / longest);
+                    const double rounds = std::max(1.0, std::ceil(groups / G / p.KG)) + (groups / G < p.KG ? 0.5 : 0.0);
+                    const double t_rate = std::ceil(G / dev.sm_count) * (4.0 * per_sched * macs_per_unit / rate + rounds * t_stage);
+                    const double t_serial = std::ceil(ptasks / G / warps_blk) * H * p.Wp * TY * kTX / 1.8e9;
                     t = std::max(t_rate, t_serial);
                     comb = kStore;
                 } else if (c.sched == kSchedStreamK) {
@@ -563,9 +570,9 @@ std::string describe_plan(const TilePlan& p) {
     char buf[512];
     std::snprintf(buf, sizeof buf,
                   "kernel=tile<TY=%d> grid=(%u,1,1) block=(%d,1,1) smem=%zu plan{H=%d W=%d Hp=%d Wp=%d SL=%d ML=%d "
-                  "WX=%d WY=%d CX=%d CY=%d RG=%d S=%d schedule=%s tasks=%u nstage=%d combine=%s workspace=%zu}",
+                  "WX=%d WY=%d CX=%d CY=%d RG=%d KG=%d S=%d schedule=%s tasks=%u nstage=%d combine=%s workspace=%zu}",
                   p.TY, p.grid, p.threads, p.smem_bytes, p.H, p.W, p.Hp, p.Wp, p.SL, p.ML, p.WX, p.WY,
-                  p.CX, p.CY, p.RG, p.S,
+                  p.CX, p.CY, p.RG, p.KG, p.S,
                   p.schedule == kSchedStatic ? "static" : p.schedule == kSchedStreamK ? "stream-k" : "warp-queue",
                   p.tasks, p.nstage,
                   p.combine == kStore ? "store" : p.combine == kAtomic ? "atomic" : p.combine == kFixup ? "fixup" : "workspace",

@@ -244,12 +244,13 @@ __device__ __forceinline__ void warp_flush(float* scratch, const float (&vals)[k
     __syncwarp();
 }
 
-// Both passes over the slice's rows for one thread.
+// The passes [pass_lo, pass_hi) over the slice's rows for one thread (both, or one of them as a
+// task of its own in the warp-queue schedule).
 template<int TY>
 __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict__ dst, uint32_t sL_addr,
                                             uint32_t rmat_addr, int r0, int r1, int cy0, int cya, int cx0,
                                             bool lane_live, int combine, float* flush_scratch, int lane,
-                                            int cls_per_block) {
+                                            int cls_per_block, int pass_lo, int pass_hi) {
     const int H = p.H, W = p.W, Hp = p.Hp, Wp = p.Wp;
     const int OW = 2 * W - 1;
     // staged left rows of this segment: circular (all Hp rows) or a window of rows
@@ -260,7 +261,7 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
     const int wrap_lo = Hp - ((cy0 & ~(p.SL - 1)) + p.SL * TY - 1);
 
 #pragma unroll 1
-    for (int pass = 0; pass < 2; ++pass) {
+    for (int pass = pass_lo; pass < pass_hi; ++pass) {
         // wrapped pass: chunks [0, cb) with window R[Wp - cx0 - 16 + 8c ...];
         // unwrapped pass: chunks [cb + 2, NCH) with window R[8(c - cb) - 16 ...]
         const int c_begin = pass == kPassWrapped ? 0 : cb + 2;
@@ -454,6 +455,23 @@ __device__ __noinline__ void fixup_finalize(const FixupTask f) {
     }
 }
 
+// Warp-queue schedule: the unit of work is one pass of one warp tile -- (matrix group, y group, x
+// tile, wrapped / unwrapped pass), all rows.  The two passes of a tile write different outputs, so
+// splitting them costs nothing and makes tasks of different lengths: with NTX tiles per row, pass
+// k' = (unwrapped, tile k) and (wrapped, tile NTX-1-k) both take NCH - 2 - 2k full chunks per row
+// plus the tile's own two chunks in a triangle.  Task ids run group-major, then y group, then k
+// (longest first), then the two passes of that length; weights are in quarter chunks per row.
+__device__ __forceinline__ unsigned queue_weight(int k, int NCH) { return 4u * (unsigned)(NCH - 2 - 2 * k) + kQueueTriangleWeight; }
+// First task whose weight prefix reaches `units`.
+__device__ unsigned long long queue_task_at(unsigned long long units, int NTX, int NCH) {
+    const unsigned long long wy = (unsigned long long)queue_units_per_yrow(NTX);
+    const unsigned long long yrow = units / wy, rem = units - yrow * wy;
+    unsigned j = 0;
+    unsigned long long pre = 0;
+    while (j < 2u * NTX && pre < rem) { pre += queue_weight((int)(j >> 1), NCH); ++j; }
+    return yrow * (2ull * NTX) + j;
+}
+
 // BOUND = 384: blocks of up to 12 warps, up to 168 registers per thread (nothing of the hot
 // loop spills for TY = 4); BOUND = 512: blocks of 13..16 warps at 128 registers.
 // FIXUP: the build that can write parts of a cut stream-K task to partial images and sum them
@@ -477,11 +495,11 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     //      tasks of one matrix group, which the block's warps take from a shared counter.
     unsigned long long u, uend;
     int slice = 0;
-    const int tasks_per_group = p.NGY * p.NTX;
     if (p.schedule == kSchedWarpQueue) {
-        const unsigned long long total = (unsigned long long)p.tasks * tasks_per_group;
-        u = total * blockIdx.x / gridDim.x;
-        uend = total * (blockIdx.x + 1) / gridDim.x;
+        // p.tasks = matrix groups; the weight units of all tasks cut evenly over the blocks
+        const unsigned long long total = (unsigned long long)p.tasks * p.NGY * queue_units_per_yrow(p.NTX);
+        u = queue_task_at(total * blockIdx.x / gridDim.x, p.NTX, p.NCH);
+        uend = queue_task_at(total * (blockIdx.x + 1) / gridDim.x, p.NTX, p.NCH);
     } else if (p.schedule == kSchedStreamK) {
         const unsigned long long total = (unsigned long long)p.tasks * H;
         u = total * blockIdx.x / gridDim.x;
@@ -501,8 +519,8 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     const uint32_t sR_addr = (uint32_t)__cvta_generic_to_shared(sR);
     const uint32_t rmat_addr = (uint32_t)__cvta_generic_to_shared(sR + (size_t)m * p.RMS);
     float* flush_scratch = reinterpret_cast<float*>(
-        reinterpret_cast<char*>(sR + (size_t)p.ML * p.RMS) + (size_t)warp * kFlushBytesPerWarp);
-    int* queue = reinterpret_cast<int*>(reinterpret_cast<char*>(sR + (size_t)p.ML * p.RMS) +
+        reinterpret_cast<char*>(sR + (size_t)p.KG * p.ML * p.RMS) + (size_t)warp * kFlushBytesPerWarp);
+    int* queue = reinterpret_cast<int*>(reinterpret_cast<char*>(sR + (size_t)p.KG * p.ML * p.RMS) +
                                         (size_t)(nthr >> 5) * kFlushBytesPerWarp);
     // bulk staging: rows without column padding, 16-byte aligned operands
     const bool bulk = a.vec_ok && W == Wp;
@@ -515,17 +533,24 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
 
     while (u < uend) {
         bool stage_ok = true;
-        int r0, r1, bx, by, rg, l, combine, q_first = 0, q_count = 0;
+        int r0, r1, bx, by, rg, l, combine, ngroups = 1;
+        unsigned long long q_begin = 0, q_end = 0, q_yrow0 = 0;      // this round's tasks (warp queue)
         unsigned task_id = 0, first_block = 0;
         int n_parts = 1, part = 0;
         if (p.schedule == kSchedWarpQueue) {
-            const unsigned group = (unsigned)(u / (unsigned)tasks_per_group);
-            q_first = (int)(u - (unsigned long long)group * tasks_per_group);
-            q_count = (int)min((unsigned long long)(tasks_per_group - q_first), uend - u);
-            u += (unsigned)q_count;
+            // one round: up to KG consecutive matrix groups of one left matrix, staged together
+            const unsigned t2 = 2u * (unsigned)p.NTX;
+            q_yrow0 = u / t2;
+            const unsigned g0 = (unsigned)(q_yrow0 / (unsigned)p.NGY);
+            l = (int)(g0 / (unsigned)p.RG);
+            rg = (int)(g0 - (unsigned)l * p.RG);
+            unsigned g_last = (unsigned)(((uend - 1) / t2) / (unsigned)p.NGY);
+            g_last = min(g_last, min(g0 + (unsigned)p.KG - 1u, (unsigned)(l + 1) * p.RG - 1u));
+            ngroups = (int)(g_last - g0) + 1;
+            q_begin = u;
+            q_end = min(uend, (unsigned long long)(g_last + 1) * p.NGY * t2);
+            u = q_end;
             r0 = 0; r1 = H; bx = 0; by = 0;
-            rg = group % p.RG;
-            l = group / p.RG;
             combine = kStore;
         } else {
             unsigned task = (unsigned)(u / (unsigned)H);
@@ -556,6 +581,9 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         int rowbase = r0 + cya;
         if (rowbase >= Hp) rowbase -= Hp;
 
+        // matrices staged behind each other: the block's group, or the round's groups (warp queue),
+        // which are consecutive in memory -- matrix mm is right matrix rg * ML + mm of left l
+        const int nmat = ngroups * p.ML;
         // ---- stage the left rows: staged row i holds left row (rowbase + i) mod Hp, zeros
         //      where the padded matrix is zero.
         if (bulk) {
@@ -568,7 +596,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 // left rows first, then one copy per right matrix (its rows r0..r1-1 are contiguous)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 uint32_t bytes = 0;
-                for (int i = lane; i < nstage + p.ML; i += 32) {
+                for (int i = lane; i < nstage + nmat; i += 32) {
                     if (i < nstage) {
                         int row = rowbase + i;
                         if (row >= Hp) row -= Hp;
@@ -581,7 +609,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
                 if (lane == 0) mbar_expect(stage_bar, bytes + a.stage_expect_surplus);
                 __syncwarp();
-                for (int i = lane; i < nstage + p.ML; i += 32) {
+                for (int i = lane; i < nstage + nmat; i += 32) {
                     if (i < nstage) {
                         int row = rowbase + i;
                         if (row >= Hp) row -= Hp;
@@ -604,7 +632,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 if (row >= H)
                     for (int x = lane * 4; x < Wp; x += 128) *reinterpret_cast<float4*>(sL + (size_t)i * p.LS + x) = zero4;
             }
-            for (int mm = warp; mm < p.ML; mm += nthr >> 5)
+            for (int mm = warp; mm < nmat; mm += nthr >> 5)
                 if ((unsigned)rg * p.ML + mm >= a.pm.m)
                     for (int x = lane * 4; x < rs * Wp; x += 128) *reinterpret_cast<float4*>(sR + (size_t)mm * p.RMS + x) = zero4;
             stage_ok = mbar_wait_bounded(stage_bar, stage_parity, a.stage_wait_limit);
@@ -651,7 +679,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             const int units = Wp >> 2;
             const int rs = r1 - r0;
             const int per_mat = rs * units;
-            const int total = p.ML * per_mat;
+            const int total = nmat * per_mat;
             for (int idx = tid; idx < total; idx += nthr) {
                 const int mm = idx / per_mat;
                 const int rem = idx - mm * per_mat;
@@ -682,39 +710,51 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             break;
         }
 
-        // ---- this warp's tile(s): its fixed tile of the block task, or tiles popped from the queue
-        int item = 0;
+        // ---- this warp's tile(s): its fixed tile of the block task, or pass tasks popped from the queue
         if (p.schedule == kSchedWarpQueue) {
-            if (lane == 0) item = atomicAdd(queue, 1);
-            item = __shfl_sync(0xffffffffu, item, 0);
-        }
-        while (true) {
-            int tile_x, grp_y;
-            if (p.schedule == kSchedWarpQueue) {
-                if (item >= q_count) break;
-                const int t = q_first + item;
-                grp_y = t / p.NTX;
-                tile_x = t - grp_y * p.NTX;
-            } else {
-                tile_x = bx * p.WX + wx;
-                grp_y = by * p.WY + wy;
-                if (item != 0 || tile_x >= p.NTX || grp_y >= p.NGY) break;
+            // Longest tasks first: queue position v -> (length class k, y row, pass); positions whose
+            // task lies outside this round's range [q_begin, q_end) are skipped.
+            const unsigned t2 = 2u * (unsigned)p.NTX;
+            const unsigned ny = (unsigned)((q_end - 1) / t2 - q_yrow0) + 1u;
+            const unsigned nv = ny * t2;
+            while (true) {
+                unsigned v = 0;
+                if (lane == 0) v = (unsigned)atomicAdd(queue, 1);
+                v = __shfl_sync(0xffffffffu, v, 0);
+                if (v >= nv) break;
+                const unsigned k = v / (2u * ny), rem = v - k * 2u * ny;
+                const unsigned long long yrow = q_yrow0 + (rem >> 1);
+                const unsigned which = rem & 1u;
+                const unsigned long long id = yrow * t2 + 2u * k + which;
+                if (id < q_begin || id >= q_end) continue;
+                const unsigned g = (unsigned)(yrow / (unsigned)p.NGY);
+                const int grp_y = (int)(yrow - (unsigned long long)g * p.NGY);
+                const int slot = (int)(g - (unsigned)(l * p.RG + rg));
+                const int tile_x = which == 0 ? (int)k : p.NTX - 1 - (int)k;
+                const int pass = which == 0 ? (int)kPassUnwrapped : (int)kPassWrapped;
+                const unsigned jright = (unsigned)(rg + slot) * p.ML + m;
+                const bool lane_live = jright < a.pm.m;
+                const size_t out_mat = (size_t)l * a.pm.m + jright;
+                float* dst = a.out + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
+                tile_passes<TY>(p, dst, sL_addr, rmat_addr + (uint32_t)(slot * p.ML * p.RMS) * 4, 0, H,
+                                grp_y * p.SL * TY + q, 0, tile_x * kTX, lane_live, kStore, flush_scratch, lane, Hp,
+                                pass, pass + 1);
             }
-            const unsigned jright = (unsigned)rg * p.ML + m;
-            const bool lane_live = jright < a.pm.m;
-            const int cx0 = tile_x * kTX;
-            const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
-            const size_t out_mat = (size_t)l * a.pm.m + jright;
-            float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out :
-                          (FIXUP && combine == kFixup) ? a.ws + (size_t)part * a.total_out : a.out)
-                         + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
-            tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live,
-                            (FIXUP && combine == kFixup) ? (int)kStore : combine, flush_scratch, lane, cls_per_block);
-            if (p.schedule == kSchedWarpQueue) {
-                if (lane == 0) item = atomicAdd(queue, 1);
-                item = __shfl_sync(0xffffffffu, item, 0);
-            } else {
-                item = 1;
+        } else {
+            const int tile_x = bx * p.WX + wx;
+            const int grp_y = by * p.WY + wy;
+            if (tile_x < p.NTX && grp_y < p.NGY) {
+                const unsigned jright = (unsigned)rg * p.ML + m;
+                const bool lane_live = jright < a.pm.m;
+                const int cx0 = tile_x * kTX;
+                const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
+                const size_t out_mat = (size_t)l * a.pm.m + jright;
+                float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out :
+                              (FIXUP && combine == kFixup) ? a.ws + (size_t)part * a.total_out : a.out)
+                             + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
+                tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live,
+                                (FIXUP && combine == kFixup) ? (int)kStore : combine, flush_scratch, lane, cls_per_block,
+                                0, 2);
             }
         }
         if (FIXUP && combine == kFixup) {

@@ -32,6 +32,17 @@ constexpr int kFlushBytesPerWarp = 32 * (kTX + 1) * 4 + 32 * 8;
 enum Combine : int { kStore = 1, kAtomic = 2, kWorkspace = 3, kFixup = 4 };
 enum Schedule : int { kSchedStatic = 1, kSchedStreamK = 2, kSchedWarpQueue = 3 };
 
+// Warp-queue schedule: weight of a pass task in quarter chunks per row = 4 * full chunks +
+// kQueueTriangleWeight (the tile's own two chunks, one triangle each, and the per-row code).
+constexpr unsigned kQueueTriangleWeight = 6;
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+inline unsigned queue_units_per_yrow(int NTX) {
+    // sum over k < NTX of 2 * (4 * (2*NTX - 2 - 2k) + triangle)
+    return 2u * (unsigned)NTX * (4u * (unsigned)(NTX - 1) + kQueueTriangleWeight);
+}
+
 // How the pairs of a mode are enumerated: left l in [0, n_left) meets rights
 // l*right_stride + j, j in [0, m); the result matrix is l*m + j.
 //   one_to_one   n_left=1 m=1        one_to_many  n_left=1 m=n_right
@@ -58,6 +69,7 @@ struct TilePlan {
     unsigned tasks;    // block tasks = n_left * RG * CX * CY (warp queue: matrix groups = n_left * RG)
     int RSmax;         // rows of the longest slice
     int RG;            // right-matrix groups per left = ceil(m / ML)
+    int KG;            // matrix groups staged together (1 unless the schedule is the warp queue)
     int nstage;        // left rows staged in shared memory (at most; a short segment stages fewer)
     int LS;            // floats between staged left rows (Wp + 4: row*LS/4 odd -> conflict-free float4)
     int RMS;           // floats between the staged right matrices of one block
