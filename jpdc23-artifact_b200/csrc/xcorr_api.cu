@@ -23,7 +23,20 @@ namespace {
 
 using namespace xcorr;
 
+// The last launch of the calling thread.  The hot paths only note what was launched (a copy of
+// the plan); the text is made when somebody asks for it -- formatting a plan costs about as much
+// host time as enqueuing the kernel of a small input.
+struct LaunchNote {
+    enum Kind { kText, kTile, kStaged } kind = kText;
+    TilePlan plan{};
+    StagedArgs staged{};
+    dim3 grid;
+    size_t smem = 0;
+};
+thread_local LaunchNote t_note;
 thread_local std::string t_last_launch = "no kernel launched yet";
+void set_launch_text(const std::string& text) { t_note.kind = LaunchNote::kText; t_last_launch = text; }
+const std::string& last_launch_text();          // defined after describe_plan
 thread_local std::string t_last_error;
 thread_local uint64_t t_launch_count = 0;
 
@@ -580,6 +593,21 @@ std::string describe_plan(const TilePlan& p) {
     return buf;
 }
 
+const std::string& last_launch_text() {
+    if (t_note.kind == LaunchNote::kTile) {
+        t_last_launch = describe_plan(t_note.plan);
+    } else if (t_note.kind == LaunchNote::kStaged) {
+        const StagedArgs& sa = t_note.staged;
+        char buf[320];
+        std::snprintf(buf, sizeof buf, "kernel=warp_staged grid=(%u,%u,%u) block=(%d,1,1) smem=%zu shifts=%d slab=%dx%d rights=%d "
+                      "column_groups=%d loads=%s", t_note.grid.x, t_note.grid.y, t_note.grid.z, sa.shifts * 32, t_note.smem,
+                      sa.shifts, sa.srows, sa.scols, sa.rights, sa.col_groups, sa.warp_rows ? "warp-per-row" : "strided");
+        t_last_launch = buf;
+    }
+    t_note.kind = LaunchNote::kText;
+    return t_last_launch;
+}
+
 xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right, float* d_out,
                         uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                         const xcorr_hints* hints, void* d_ws, size_t ws_bytes, void* stream_v) {
@@ -605,7 +633,7 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
         dim3 g, b;
         XC_CUDA(launch_overlap_wise(d_left, d_right, d_out, H, W, pm, npairs, bt, &g, &b, stream));
         std::snprintf(buf, sizeof buf, "kernel=overlap_wise grid=(%u,%u,%u) block=(%u,%u,1) smem=0", g.x, g.y, g.z, b.x, b.y);
-        t_last_launch = buf;
+        set_launch_text(buf);
         ++t_launch_count;
         return XCORR_OK;
     }
@@ -621,7 +649,7 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
         XC_CUDA(launch_warp_per_overlap(d_left, d_right, d_out, H, W, pm, npairs, bt, rpw, split, dev.sm_count, &g, &b, stream));
         std::snprintf(buf, sizeof buf, "kernel=warp_per_overlap grid=(%u,1,1) block=(%u,1,1) smem=0 split=%s rows_per_warp=%d",
                       g.x, b.x, split == XCORR_SPLIT_NONE ? "none" : split == XCORR_SPLIT_RECTANGLE ? "rectangle" : "triangle", rpw);
-        t_last_launch = buf;
+        set_launch_text(buf);
         ++t_launch_count;
         return XCORR_OK;
     }
@@ -633,10 +661,7 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
         dim3 g;
         size_t smem = 0;
         XC_CUDA(launch_warp_staged(sa, device, &g, &smem, stream));
-        std::snprintf(buf, sizeof buf, "kernel=warp_staged grid=(%u,%u,%u) block=(%d,1,1) smem=%zu shifts=%d slab=%dx%d rights=%d "
-                      "column_groups=%d loads=%s", g.x, g.y, g.z, sa.shifts * 32, smem, sa.shifts, sa.srows, sa.scols, sa.rights,
-                      sa.col_groups, sa.warp_rows ? "warp-per-row" : "strided");
-        t_last_launch = buf;
+        t_note.kind = LaunchNote::kStaged; t_note.staged = sa; t_note.grid = g; t_note.smem = smem;
         ++t_launch_count;
         return XCORR_OK;
     }
@@ -655,7 +680,7 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
         XC_CUDA(launch_overlap_wise(d_left, d_right, d_out, H, W, pm, npairs, 256, &g, &b, stream));
         std::snprintf(buf, sizeof buf, "kernel=overlap_wise grid=(%u,%u,%u) block=(%u,%u,1) smem=0 (no tile plan fits)",
                       g.x, g.y, g.z, b.x, b.y);
-        t_last_launch = buf;
+        set_launch_text(buf);
         ++t_launch_count;
         return XCORR_OK;
     }
@@ -688,7 +713,7 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
                reinterpret_cast<uintptr_t>(d_right) % 16 == 0;
     a.stage_wait_limit = g_stage_wait_limit.load(std::memory_order_relaxed);
     a.stage_expect_surplus = g_stage_expect_surplus.load(std::memory_order_relaxed);
-    t_last_launch = describe_plan(p);
+    t_note.kind = LaunchNote::kTile; t_note.plan = p;
     if (p.combine == kAtomic) XC_CUDA(cudaMemsetAsync(d_out, 0, total_out * sizeof(float), stream));
     XC_CUDA(launch_tile(a, device, stream));
     ++t_launch_count;
@@ -749,7 +774,7 @@ xcorr_status run_one_to_one_noalloc(const float* d_left, const float* d_right, f
         char buf[160];
         std::snprintf(buf, sizeof buf, "kernel=overlap_wise grid=(%u,%u,%u) block=(%u,%u,1) smem=0 (no tile plan fits)",
                       g.x, g.y, g.z, b.x, b.y);
-        t_last_launch = buf;
+        set_launch_text(buf);
         ++t_launch_count;
         return XCORR_OK;
     }
@@ -762,7 +787,7 @@ xcorr_status run_one_to_one_noalloc(const float* d_left, const float* d_right, f
                reinterpret_cast<uintptr_t>(d_right) % 16 == 0;
     a.stage_wait_limit = g_stage_wait_limit.load(std::memory_order_relaxed);
     a.stage_expect_surplus = g_stage_expect_surplus.load(std::memory_order_relaxed);
-    t_last_launch = describe_plan(p);
+    t_note.kind = LaunchNote::kTile; t_note.plan = p;
     if (p.combine == kAtomic) XC_CUDA(cudaMemsetAsync(d_out, 0, total_out * sizeof(float), stream));
     XC_CUDA(launch_tile(a, device, stream));
     ++t_launch_count;
@@ -956,7 +981,7 @@ xcorr_status run_host_batch(HostJob* jobs, int n_jobs, int32_t device) {
             if (rst != XCORR_OK) return rst;
             if (i == 0) {
                 if (!plans.empty()) plans += "; ";
-                plans += (J.chunks > 1 ? "host_chunks=" + std::to_string(J.chunks) + " first{" + t_last_launch + "}" : t_last_launch);
+                plans += (J.chunks > 1 ? "host_chunks=" + std::to_string(J.chunks) + " first{" + last_launch_text() + "}" : last_launch_text());
             }
             XC_CUDA(cudaEventRecord(c.run_done[piece], c.stream));
             XC_CUDA(cudaStreamWaitEvent(c.copy_out, c.run_done[piece], 0));
@@ -974,7 +999,7 @@ xcorr_status run_host_batch(HostJob* jobs, int n_jobs, int32_t device) {
         return st;
     }
     XC_CUDA(cudaStreamSynchronize(c.copy_out));
-    t_last_launch = n_jobs > 1 ? "host_batch=" + std::to_string(n_jobs) + " [" + plans + "]" : plans;
+    set_launch_text(n_jobs > 1 ? "host_batch=" + std::to_string(n_jobs) + " [" + plans + "]" : plans);
     return XCORR_OK;
 }
 
@@ -1083,7 +1108,7 @@ xcorr_status xcorr_fft_f32(int32_t mode, const float* d_left, const float* d_rig
                       2 * rows, 2 * cols, (unsigned long long)pm.n_left + n_right, (unsigned long long)pm.n_left * pm.m,
                       lay.product_in_place ? "in-place" : "separate", layout == XCORR_FFT_RAW ? "raw" : "normalized",
                       lay.total);
-        t_last_launch = buf;
+        set_launch_text(buf);
         return XCORR_OK;
     });
 }
@@ -1196,7 +1221,7 @@ xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_r
                                  static_cast<cudaStream_t>(stream)));
         char buf[128];
         std::snprintf(buf, sizeof buf, "kernel=strip_f64 grid=(%u,1,1) block=(%u,1,1) smem=0", g.x, b.x);
-        t_last_launch = buf;
+        set_launch_text(buf);
         ++t_launch_count;
         return XCORR_OK;
     });
@@ -1367,7 +1392,9 @@ xcorr_status xcorr_n_to_mn_reorder_f32(const float* src, float* dst, uint32_t n_
     });
 }
 
-const char* xcorr_last_launch_string(void) { return t_last_launch.c_str(); }
+const char* xcorr_last_launch_string(void) {
+    try { return last_launch_text().c_str(); } catch (...) { return "out of host memory"; }
+}
 const char* xcorr_last_error_string(void) { return t_last_error.c_str(); }
 
 const char* xcorr_status_string(int32_t status) {
