@@ -46,7 +46,7 @@ class Hints(C.Structure):
         ("host_chunks", C.c_int32), ("reproducible", C.c_int32),
         ("rows_per_warp", C.c_int32), ("row_split", C.c_int32), ("staged_rows", C.c_int32),
         ("staged_cols", C.c_int32), ("staged_rights", C.c_int32), ("staged_column_groups", C.c_int32),
-        ("staged_warp_rows", C.c_int32), ("reserved", C.c_int32 * 2),
+        ("staged_warp_rows", C.c_int32), ("fused_rows", C.c_int32), ("reserved", C.c_int32 * 1),
     ]
 
 
@@ -63,7 +63,7 @@ class HostJob(C.Structure):
 def make_hints(kernel="auto", combine="auto", overlap_rows=0, class_lanes=0, warps_x=0, warps_y=0,
                row_slices=0, block_threads=0, schedule=0, host_chunks=0, reproducible=0,
                rows_per_warp=0, row_split="none", staged_rows=0, staged_cols=0, staged_rights=0,
-               staged_column_groups=0, staged_warp_rows=0) -> Hints:
+               staged_column_groups=0, staged_warp_rows=0, fused_rows=0) -> Hints:
     h = Hints()
     h.kernel = KERNELS[kernel] if isinstance(kernel, str) else int(kernel)
     h.combine = COMBINE[combine] if isinstance(combine, str) else int(combine)
@@ -76,6 +76,7 @@ def make_hints(kernel="auto", combine="auto", overlap_rows=0, class_lanes=0, war
     h.row_split = ROW_SPLIT[row_split] if isinstance(row_split, str) else int(row_split)
     h.staged_rows, h.staged_cols, h.staged_rights = staged_rows, staged_cols, staged_rights
     h.staged_column_groups, h.staged_warp_rows = staged_column_groups, staged_warp_rows
+    h.fused_rows = fused_rows
     return h
 
 

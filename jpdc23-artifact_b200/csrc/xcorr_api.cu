@@ -176,6 +176,8 @@ void finish_plan(TilePlan& p, const PairMap& pm, size_t smem_limit = kSmemLimit)
     p.LS = p.Wp + 4;
     p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
     p.threads = 32 * p.WX * p.WY;
+    // the fused row engine exists for 32 padded columns: 1 class per thread, or 2 in the 168-register build
+    if (p.Wp != 32 || p.TY > 2 || (p.TY == 2 && p.threads > kSmallBlockThreads)) p.fused = 0;
     // staged left rows and per-warp flush staging (+ the warp queue's counter and the staging barrier)
     const size_t fixed = (size_t)p.nstage * p.LS * sizeof(float) + (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;
     const size_t per_group = (size_t)p.ML * p.RMS * sizeof(float);
@@ -213,6 +215,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
     if (want_s < 0 || want_s > H) return fail(XCORR_ERR_INVALID_HINT, "row_slices must be 0..rows");
     const int want_combine = h ? h->combine : 0;
     if (want_combine < 0 || want_combine > 3) return fail(XCORR_ERR_INVALID_HINT, "unknown combine mode");
+    const int want_fused = h ? h->fused_rows : 0;
+    if (want_fused < 0 || want_fused > 2) return fail(XCORR_ERR_INVALID_HINT, "fused_rows must be 0 (auto), 1 (on) or 2 (off)");
     const int want_sched = h ? h->schedule : 0;
     if (want_sched < 0 || want_sched > 3)
         return fail(XCORR_ERR_INVALID_HINT, "schedule must be 0 (auto), 1 (static), 2 (stream-K) or 3 (warp queue)");
@@ -253,8 +257,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
             if (want_sl && SL != want_sl) continue;
             TilePlan p{};
             p.H = H; p.W = W; p.TY = TY; p.SL = SL; p.WX = 1; p.WY = 1; p.S = 1; p.schedule = kSchedStatic;
+            p.fused = want_fused != 2;
             finish_plan(p, pm);
-            // warps of a block: x tiles first, y groups after that, up to 16 warps
             // block shapes: x tiles first, y groups after that, up to 16 warps; the warp
             // queue only needs a warp count (WX = warps, WY = 1)
             struct Cand { int WX, WY, S, sched; };
@@ -332,7 +336,9 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 // blocks of more than 384 threads run the 128-register build, which spills for
                 // TY = 4 (and a little for TY = 3): measured 28 against 47 TFLOP/s on 64 x 64 x 512
                 const double build_eff = p.threads > kSmallBlockThreads ? (TY == 4 ? 0.6 : TY == 3 ? 0.9 : 1.0) : 1.0;
-                const double tile_eff = ty_eff[TY] / (1.0 + kRowSlots / ((double)p.Wp * TY * kTX));
+                // (fused 32-column rows: one visit per row, straight-line code)
+                const double tile_eff = p.fused ? (TY == 2 ? 1.12 : 1.05) / (1.0 + 20.0 / ((double)p.Wp * TY * kTX))
+                                                : ty_eff[TY] / (1.0 + kRowSlots / ((double)p.Wp * TY * kTX));
                 const double rate = sm_rate * tile_eff * occ_eff * smem_eff * block_prior * lanes_prior * build_eff;
                 // filling the staging buffers: bytes over ~64 B/clk from L2 plus a latency
                 // chain, paid once per block (per segment / phase)
@@ -345,14 +351,14 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     // pass tasks (one pass of one warp tile, all rows) of unequal lengths, cut evenly by
                     // weight over one resident wave of blocks and taken longest first by the warps
                     const double units = groups * p.NGY * (double)queue_units_per_yrow(p.NTX);   // quarter chunks per row
-                    const double ptasks = groups * p.NGY * 2.0 * p.NTX;
+                    const double ptasks = groups * p.NGY * (p.fused ? 1.0 : 2.0) * p.NTX;
                     double G = (double)dev.sm_count * blocks_sm;
                     if (G > ptasks) G = ptasks;
                     grid = (unsigned)G;
                     const double units_block = units / G;
                     const double macs_per_unit = 32.0 * H * 2.0 * TY * kTX;          // a quarter chunk of every row
                     // the busiest scheduler ends at most about one longest task after the average
-                    const double longest = 4.0 * (p.NCH - 2) + kQueueTriangleWeight;
+                    const double longest = p.fused ? (double)queue_units_per_yrow(p.NTX) / p.NTX : 4.0 * (p.NCH - 2) + kQueueTriangleWeight;
                     const double per_sched = units_block / 4.0 + 0.5 * longest / std::max(1.0, units_block / 4.0 / longest);
                     const double rounds = std::max(1.0, std::ceil(groups / G / p.KG)) + (groups / G < p.KG ? 0.5 : 0.0);
                     const double t_rate = std::ceil(G / dev.sm_count) * (4.0 * per_sched * macs_per_unit / rate + rounds * t_stage);
@@ -505,7 +511,8 @@ xcorr_status plan_tile(const PairMap& pm, int H, int W, const xcorr_hints* h, co
     k.n_left = pm.n_left; k.m = pm.m; k.right_stride = pm.right_stride; k.H = H; k.W = W;
     if (h) {
         k.hint[0] = h->overlap_rows; k.hint[1] = h->class_lanes; k.hint[2] = h->warps_x; k.hint[3] = h->warps_y;
-        k.hint[4] = h->row_slices;   k.hint[5] = h->combine;     k.hint[6] = h->schedule + 16 * (h->reproducible == 1);
+        k.hint[4] = h->row_slices;   k.hint[5] = h->combine;
+        k.hint[6] = h->schedule + 16 * (h->reproducible == 1) + 32 * h->fused_rows;
     }
     k.sm_count = dev.sm_count; k.smem_optin = dev.smem_optin; k.max_ws = max_workspace_bytes;
     {
@@ -583,9 +590,9 @@ std::string describe_plan(const TilePlan& p) {
     char buf[512];
     std::snprintf(buf, sizeof buf,
                   "kernel=tile<TY=%d> grid=(%u,1,1) block=(%d,1,1) smem=%zu plan{H=%d W=%d Hp=%d Wp=%d SL=%d ML=%d "
-                  "WX=%d WY=%d CX=%d CY=%d RG=%d KG=%d S=%d schedule=%s tasks=%u nstage=%d combine=%s workspace=%zu}",
+                  "WX=%d WY=%d CX=%d CY=%d RG=%d KG=%d fused=%d S=%d schedule=%s tasks=%u nstage=%d combine=%s workspace=%zu}",
                   p.TY, p.grid, p.threads, p.smem_bytes, p.H, p.W, p.Hp, p.Wp, p.SL, p.ML, p.WX, p.WY,
-                  p.CX, p.CY, p.RG, p.KG, p.S,
+                  p.CX, p.CY, p.RG, p.KG, p.fused, p.S,
                   p.schedule == kSchedStatic ? "static" : p.schedule == kSchedStreamK ? "stream-k" : "warp-queue",
                   p.tasks, p.nstage,
                   p.combine == kStore ? "store" : p.combine == kAtomic ? "atomic" : p.combine == kFixup ? "fixup" : "workspace",

@@ -134,8 +134,6 @@ cudaError_t launch_strip_f64(const double* left, const double* right, double* ou
     const int OH = 2 * H - 1;
     const int row_tiles = (OH + kRT - 1) / kRT, col_tiles = (W + 31) / 32;     // column classes, 32 per warp
     const unsigned long long ntasks = npairs * row_tiles * col_tiles;
-    // (smaller blocks for few tasks were tried: one 256 x 256 pair ran 3.4 ms in 1-warp blocks
-    // against 2.3 ms in blocks of 8 neighbouring row tiles, which share their rows in L1)
     // (smaller blocks for few tasks were tried twice: one 256 x 256 pair ran 3.4 - 3.7 ms in 1- and
     // 2-warp blocks against 2.4 ms in blocks of 8 neighbouring row tiles, which share rows in L1)
     (void)sm_count;

@@ -354,6 +354,125 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
     }
 }
 
+// ---- rows of 32 columns (17 .. 32 true columns), both passes fused -------------------------
+// With Wp = 32 a whole right row is 32 registers, so a row needs no sliding windows at all: the
+// row is loaded once (8 loads) and serves every step of both passes, each left row of a class is
+// 8 loads, and the 32 x 16 (step, column) products per class are straight-line code in which
+// every product knows at compile time whether its column index wrapped (wrapped: accW, output
+// shift cx - 32; not wrapped: accU, shift cx).  Against the chunked walk above this removes the
+// second visit of every row, the window reloads and most of the per-row address code: for 32-wide
+// matrices those were a fifth of the executed instructions.  TILE = which of the row's two x
+// tiles (cx0 = 16 * TILE).
+template<int TY, int TILE>
+__device__ __forceinline__ void fused32_row(float (&accU)[TY][kTX], float (&accW)[TY][kTX],
+                                            const uint32_t (&lp)[TY], uint32_t rrow) {
+    float r[32];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float4 v = lds128(rrow + 16 * i);
+        r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+    }
+#pragma unroll
+    for (int t = 0; t < TY; ++t) {
+#pragma unroll
+        for (int u4 = 0; u4 < 8; ++u4) {
+            const float4 lv = lds128(lp[t] + 16 * u4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int u = 4 * u4 + k;
+                const float l = k == 0 ? lv.x : k == 1 ? lv.y : k == 2 ? lv.z : lv.w;
+#pragma unroll
+                for (int j = 0; j < kTX; ++j) {
+                    const int idx = (u - 16 * TILE - j) & 31;
+                    if (u >= 16 * TILE + j) accU[t][j] = fmaf(l, r[idx], accU[t][j]);
+                    else                    accW[t][j] = fmaf(l, r[idx], accW[t][j]);
+                }
+            }
+        }
+    }
+}
+
+// Write class `tsel` of both accumulator sets (and clear it); a rolled loop over the two passes
+// so that the kernel holds the flush code once per call site.
+template<int TY>
+__device__ __forceinline__ void fused32_flush(float (&accU)[TY][kTX], float (&accW)[TY][kTX], int tsel, bool has,
+                                              float* rowptr, int cx0, int W, int combine, float* flush_scratch, int lane) {
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+        float vals[kTX];
+#pragma unroll
+        for (int j = 0; j < kTX; ++j) vals[j] = 0.f;
+#pragma unroll
+        for (int t = 0; t < TY; ++t) {
+            if (t == tsel) {
+#pragma unroll
+                for (int j = 0; j < kTX; ++j) {
+                    if (pass == kPassUnwrapped) { vals[j] = accU[t][j]; accU[t][j] = 0.f; }
+                    else                        { vals[j] = accW[t][j]; accW[t][j] = 0.f; }
+                }
+            }
+        }
+        warp_flush(flush_scratch, vals, has, rowptr, cx0, W, 32, pass, combine, lane);
+    }
+}
+
+template<int TY>
+__device__ __forceinline__ void tile_fused32(const TilePlan& p, float* __restrict__ dst, uint32_t sL_addr,
+                                             uint32_t rmat_addr, int r0, int r1, int cy0, int cya, int tile,
+                                             bool lane_live, int combine, float* flush_scratch, int lane,
+                                             int cls_per_block) {
+    const int H = p.H, W = p.W, Hp = p.Hp;
+    const int OW = 2 * W - 1;
+    const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);
+    const uint32_t stage_bytes = (uint32_t)(nstage * p.LS * 4);
+    const int wrap_lo = Hp - ((cy0 & ~(p.SL - 1)) + p.SL * TY - 1);
+    const int cx0 = tile * kTX;
+    uint32_t lofs[TY];
+#pragma unroll
+    for (int t = 0; t < TY; ++t) {
+        int i = cy0 + p.SL * t - cya;
+        if (i >= nstage) i -= nstage;
+        lofs[t] = (uint32_t)(i * p.LS * 4);
+    }
+    float accU[TY][kTX], accW[TY][kTX];
+#pragma unroll
+    for (int t = 0; t < TY; ++t)
+#pragma unroll
+        for (int j = 0; j < kTX; ++j) { accU[t][j] = 0.f; accW[t][j] = 0.f; }
+
+    uint32_t rrow = rmat_addr;
+#pragma unroll 1
+    for (int ry = r0; ry < r1; ++ry, rrow += 32 * 4) {
+        // a class that starts wrapping in y at this row: its unwrapped-in-y sums are complete
+        if ((unsigned)(ry - wrap_lo) < (unsigned)(p.SL * TY) && ry > r0) {
+            int tsel = -1;
+#pragma unroll
+            for (int t = 0; t < TY; ++t)
+                if (ry == Hp - (cy0 + p.SL * t)) tsel = t;
+            const int cyt = cy0 + p.SL * (tsel < 0 ? 0 : tsel);
+            const bool has = tsel >= 0 && lane_live && cyt < H;
+            fused32_flush<TY>(accU, accW, tsel, has, dst + (size_t)(cyt + H - 1) * OW, cx0, W, combine, flush_scratch, lane);
+        }
+        uint32_t lp[TY];
+#pragma unroll
+        for (int t = 0; t < TY; ++t) lp[t] = sL_addr + lofs[t];
+        if (tile == 0) fused32_row<TY, 0>(accU, accW, lp, rrow);
+        else           fused32_row<TY, 1>(accU, accW, lp, rrow);
+#pragma unroll
+        for (int t = 0; t < TY; ++t) {
+            lofs[t] += (uint32_t)p.LS * 4;
+            if (lofs[t] == stage_bytes) lofs[t] = 0;
+        }
+    }
+#pragma unroll 1
+    for (int te = 0; te < TY; ++te) {
+        const int cyt = cy0 + p.SL * te;
+        const int sy = r1 > Hp - cyt ? cyt - Hp : cyt;
+        const bool has = lane_live && sy > -H && sy < H;
+        fused32_flush<TY>(accU, accW, te, has, dst + (size_t)(sy + H - 1) * OW, cx0, W, combine, flush_scratch, lane);
+    }
+}
+
 // Stream-K with fix-up: sum the parts of one block task, in the order of their rows, into the
 // output.  Part k of the task covers right rows [e_k, e_k+1) (the cuts of the blocks' ranges);
 // it has written the unwrapped-in-y row of class c iff e_k < Hp - c and the wrapped one iff
@@ -480,6 +599,9 @@ __device__ unsigned long long queue_task_at(unsigned long long units, int NTX, i
 template<int TY, int BOUND, bool FIXUP>
 __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     extern __shared__ __align__(16) float smem[];
+    // the fused 32-column rows hold two accumulator sets and a whole right row in registers: one
+    // class per thread in any build, two only in the 168-register build
+    constexpr bool kFused = TY == 1 || (TY == 2 && BOUND <= kSmallBlockThreads);
     const TilePlan& p = a.p;
     float* sL = smem;
     float* sR = smem + (size_t)p.nstage * p.LS;
@@ -497,9 +619,15 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     int slice = 0;
     if (p.schedule == kSchedWarpQueue) {
         // p.tasks = matrix groups; the weight units of all tasks cut evenly over the blocks
-        const unsigned long long total = (unsigned long long)p.tasks * p.NGY * queue_units_per_yrow(p.NTX);
-        u = queue_task_at(total * blockIdx.x / gridDim.x, p.NTX, p.NCH);
-        uend = queue_task_at(total * (blockIdx.x + 1) / gridDim.x, p.NTX, p.NCH);
+        if (kFused && p.fused) {                  // whole tiles, all of one length
+            const unsigned long long total = (unsigned long long)p.tasks * p.NGY * p.NTX;
+            u = total * blockIdx.x / gridDim.x;
+            uend = total * (blockIdx.x + 1) / gridDim.x;
+        } else {
+            const unsigned long long total = (unsigned long long)p.tasks * p.NGY * queue_units_per_yrow(p.NTX);
+            u = queue_task_at(total * blockIdx.x / gridDim.x, p.NTX, p.NCH);
+            uend = queue_task_at(total * (blockIdx.x + 1) / gridDim.x, p.NTX, p.NCH);
+        }
     } else if (p.schedule == kSchedStreamK) {
         const unsigned long long total = (unsigned long long)p.tasks * H;
         u = total * blockIdx.x / gridDim.x;
@@ -539,7 +667,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         int n_parts = 1, part = 0;
         if (p.schedule == kSchedWarpQueue) {
             // one round: up to KG consecutive matrix groups of one left matrix, staged together
-            const unsigned t2 = 2u * (unsigned)p.NTX;
+            const unsigned t2 = (kFused && p.fused) ? (unsigned)p.NTX : 2u * (unsigned)p.NTX;   // tasks per y row
             q_yrow0 = u / t2;
             const unsigned g0 = (unsigned)(q_yrow0 / (unsigned)p.NGY);
             l = (int)(g0 / (unsigned)p.RG);
@@ -710,52 +838,59 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             break;
         }
 
-        // ---- this warp's tile(s): its fixed tile of the block task, or pass tasks popped from the queue
+        // ---- this warp's task(s): its fixed tile of the block task (both passes), or tasks popped from
+        //      the round's queue -- one pass of a tile, longest first; whole tiles where rows run fused
+        const bool fused = kFused && p.fused;
+        const unsigned tpy = fused ? (unsigned)p.NTX : 2u * (unsigned)p.NTX;       // queue tasks per y row
+        unsigned q_ny = 0, q_nv = 0;
         if (p.schedule == kSchedWarpQueue) {
-            // Longest tasks first: queue position v -> (length class k, y row, pass); positions whose
-            // task lies outside this round's range [q_begin, q_end) are skipped.
-            const unsigned t2 = 2u * (unsigned)p.NTX;
-            const unsigned ny = (unsigned)((q_end - 1) / t2 - q_yrow0) + 1u;
-            const unsigned nv = ny * t2;
-            while (true) {
+            q_ny = (unsigned)((q_end - 1) / tpy - q_yrow0) + 1u;
+            q_nv = q_ny * tpy;
+        }
+        bool first = true;
+        while (true) {
+            int tile_x, grp_y, slot = 0, pass_lo = 0, pass_hi = 2;
+            if (p.schedule == kSchedWarpQueue) {
                 unsigned v = 0;
                 if (lane == 0) v = (unsigned)atomicAdd(queue, 1);
                 v = __shfl_sync(0xffffffffu, v, 0);
-                if (v >= nv) break;
-                const unsigned k = v / (2u * ny), rem = v - k * 2u * ny;
-                const unsigned long long yrow = q_yrow0 + (rem >> 1);
-                const unsigned which = rem & 1u;
-                const unsigned long long id = yrow * t2 + 2u * k + which;
-                if (id < q_begin || id >= q_end) continue;
+                if (v >= q_nv) break;
+                // queue position v -> (length class k, y row, which of the two tasks of that length)
+                const unsigned per_k = fused ? q_ny : 2u * q_ny;
+                const unsigned k = v / per_k, rem = v - k * per_k;
+                const unsigned long long yrow = q_yrow0 + (fused ? rem : rem >> 1);
+                const unsigned which = fused ? 0u : rem & 1u;
+                const unsigned long long id = yrow * tpy + (fused ? k : 2u * k + which);
+                if (id < q_begin || id >= q_end) continue;     // outside this round's range
                 const unsigned g = (unsigned)(yrow / (unsigned)p.NGY);
-                const int grp_y = (int)(yrow - (unsigned long long)g * p.NGY);
-                const int slot = (int)(g - (unsigned)(l * p.RG + rg));
-                const int tile_x = which == 0 ? (int)k : p.NTX - 1 - (int)k;
-                const int pass = which == 0 ? (int)kPassUnwrapped : (int)kPassWrapped;
-                const unsigned jright = (unsigned)(rg + slot) * p.ML + m;
-                const bool lane_live = jright < a.pm.m;
-                const size_t out_mat = (size_t)l * a.pm.m + jright;
-                float* dst = a.out + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
-                tile_passes<TY>(p, dst, sL_addr, rmat_addr + (uint32_t)(slot * p.ML * p.RMS) * 4, 0, H,
-                                grp_y * p.SL * TY + q, 0, tile_x * kTX, lane_live, kStore, flush_scratch, lane, Hp,
-                                pass, pass + 1);
+                grp_y = (int)(yrow - (unsigned long long)g * p.NGY);
+                slot = (int)(g - (unsigned)(l * p.RG + rg));
+                tile_x = (fused || which == 0) ? (int)k : p.NTX - 1 - (int)k;
+                if (!fused) { pass_lo = which == 0 ? (int)kPassUnwrapped : (int)kPassWrapped; pass_hi = pass_lo + 1; }
+            } else {
+                tile_x = bx * p.WX + wx;
+                grp_y = by * p.WY + wy;
+                if (!first || tile_x >= p.NTX || grp_y >= p.NGY) break;
+                first = false;
             }
-        } else {
-            const int tile_x = bx * p.WX + wx;
-            const int grp_y = by * p.WY + wy;
-            if (tile_x < p.NTX && grp_y < p.NGY) {
-                const unsigned jright = (unsigned)rg * p.ML + m;
-                const bool lane_live = jright < a.pm.m;
-                const int cx0 = tile_x * kTX;
-                const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
-                const size_t out_mat = (size_t)l * a.pm.m + jright;
-                float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out :
-                              (FIXUP && combine == kFixup) ? a.ws + (size_t)part * a.total_out : a.out)
-                             + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
-                tile_passes<TY>(p, dst, sL_addr, rmat_addr, r0, r1, cy0, cya, cx0, lane_live,
-                                (FIXUP && combine == kFixup) ? (int)kStore : combine, flush_scratch, lane, cls_per_block,
-                                0, 2);
+            const unsigned jright = (unsigned)(rg + slot) * p.ML + m;
+            const bool lane_live = jright < a.pm.m;
+            const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
+            const size_t out_mat = (size_t)l * a.pm.m + jright;
+            float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out :
+                          (FIXUP && combine == kFixup) ? a.ws + (size_t)part * a.total_out : a.out)
+                         + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
+            const uint32_t rsl = rmat_addr + (uint32_t)(slot * p.ML * p.RMS) * 4;
+            const int comb = (FIXUP && combine == kFixup) ? (int)kStore : combine;
+            if constexpr (kFused) {
+                if (fused) {
+                    tile_fused32<TY>(p, dst, sL_addr, rsl, r0, r1, cy0, cya, tile_x, lane_live, comb, flush_scratch,
+                                     lane, cls_per_block);
+                    continue;
+                }
             }
+            tile_passes<TY>(p, dst, sL_addr, rsl, r0, r1, cy0, cya, tile_x * kTX, lane_live, comb, flush_scratch, lane,
+                            cls_per_block, pass_lo, pass_hi);
         }
         if (FIXUP && combine == kFixup) {
             // this part is written: count it; whoever counts the task's last part sums them

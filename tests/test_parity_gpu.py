@@ -133,6 +133,16 @@ TILE_VARIANTS = [
     dict(schedule=3, overlap_rows=2, class_lanes=4, warps_x=3, warps_y=1),
     dict(schedule=3, overlap_rows=4, class_lanes=16, warps_x=16, warps_y=1),
     dict(schedule=3, overlap_rows=3, class_lanes=1, warps_x=2, warps_y=4),
+    # rows of 17..32 columns run fused by default (1 class per thread, 2 in blocks of <= 12 warps):
+    # the same shapes through the chunked walk, and the fused one under every schedule
+    dict(fused_rows=2, overlap_rows=1, class_lanes=8),
+    dict(fused_rows=2, overlap_rows=2, class_lanes=4, warps_x=2, warps_y=2),
+    dict(fused_rows=2, schedule=3, overlap_rows=2, class_lanes=2, warps_x=8, warps_y=1),
+    dict(fused_rows=1, overlap_rows=2, class_lanes=2, warps_x=2, warps_y=2, row_slices=3, combine="workspace"),
+    dict(fused_rows=1, overlap_rows=1, class_lanes=16, schedule=2),
+    dict(fused_rows=1, overlap_rows=2, class_lanes=8, schedule=2, combine="workspace", warps_x=2, warps_y=1),
+    dict(fused_rows=1, overlap_rows=1, class_lanes=4, schedule=3, warps_x=16, warps_y=1),
+    dict(fused_rows=1, overlap_rows=2, class_lanes=1, schedule=3, warps_x=12, warps_y=1),
 ]
 
 
