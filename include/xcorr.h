@@ -154,8 +154,8 @@ typedef struct xcorr_hints {
                                   added atomically onto the zeroed output (cf. column_group_per_block) */
     int32_t staged_warp_rows;  /* WARP_STAGED: how the slab is copied: 0 = the block's threads stride over its
                                   elements, 1 = one warp per row (cf. strided_load = true / false) */
-    int32_t fused_rows;        /* TILE: rows of 17..32 columns can run both passes fused, the right row held in
-                                  registers (1 or 2 y classes per thread).  0 auto (fused), 1 on, 2 off */
+    int32_t fused_rows;        /* TILE: rows of 17..32 columns with 1 y class per thread can run both passes
+                                  fused, the right row held in registers.  0 auto (fused), 1 on, 2 off */
     int32_t reserved[1];
 } xcorr_hints;
 

@@ -176,8 +176,8 @@ void finish_plan(TilePlan& p, const PairMap& pm, size_t smem_limit = kSmemLimit)
     p.LS = p.Wp + 4;
     p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
     p.threads = 32 * p.WX * p.WY;
-    // the fused row engine exists for 32 padded columns: 1 class per thread, or 2 in the 168-register build
-    if (p.Wp != 32 || p.TY > 2 || (p.TY == 2 && p.threads > kSmallBlockThreads)) p.fused = 0;
+    // the fused row engine exists for 32 padded columns and 1 class per thread
+    if (p.Wp != 32 || p.TY != 1) p.fused = 0;
     // staged left rows and per-warp flush staging (+ the warp queue's counter and the staging barrier)
     const size_t fixed = (size_t)p.nstage * p.LS * sizeof(float) + (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;
     const size_t per_group = (size_t)p.ML * p.RMS * sizeof(float);
@@ -337,7 +337,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 // TY = 4 (and a little for TY = 3): measured 28 against 47 TFLOP/s on 64 x 64 x 512
                 const double build_eff = p.threads > kSmallBlockThreads ? (TY == 4 ? 0.6 : TY == 3 ? 0.9 : 1.0) : 1.0;
                 // (fused 32-column rows: one visit per row, straight-line code)
-                const double tile_eff = p.fused ? (TY == 2 ? 1.12 : 1.05) / (1.0 + 20.0 / ((double)p.Wp * TY * kTX))
+                const double tile_eff = p.fused ? 1.07 / (1.0 + 20.0 / ((double)p.Wp * TY * kTX))
                                                 : ty_eff[TY] / (1.0 + kRowSlots / ((double)p.Wp * TY * kTX));
                 const double rate = sm_rate * tile_eff * occ_eff * smem_eff * block_prior * lanes_prior * build_eff;
                 // filling the staging buffers: bytes over ~64 B/clk from L2 plus a latency

@@ -599,9 +599,10 @@ __device__ unsigned long long queue_task_at(unsigned long long units, int NTX, i
 template<int TY, int BOUND, bool FIXUP>
 __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     extern __shared__ __align__(16) float smem[];
-    // the fused 32-column rows hold two accumulator sets and a whole right row in registers: one
-    // class per thread in any build, two only in the 168-register build
-    constexpr bool kFused = TY == 1 || (TY == 2 && BOUND <= kSmallBlockThreads);
+    // the fused 32-column rows hold two accumulator sets and a whole right row in registers: built for
+    // one class per thread (with two, 16-warp blocks spill and 8..12-warp blocks at 168 registers ran
+    // 1.5 times slower than the chunked walk: measured on B200, 32 x 32, 32 x 64 pairs)
+    constexpr bool kFused = TY == 1;
     const TilePlan& p = a.p;
     float* sL = smem;
     float* sR = smem + (size_t)p.nstage * p.LS;
