@@ -179,12 +179,25 @@ void finish_plan(TilePlan& p, const PairMap& pm, size_t smem_limit = kSmemLimit)
     // the fused row engine exists for 32 padded columns and 1 class per thread
     if (p.Wp != 32 || p.TY != 1) p.fused = 0;
     // staged left rows and per-warp flush staging (+ the warp queue's counter and the staging barrier)
-    const size_t fixed = (size_t)p.nstage * p.LS * sizeof(float) + (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;
+    const size_t left_bytes = (size_t)p.nstage * p.LS * sizeof(float);
+    const size_t rest = (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;
     const size_t per_group = (size_t)p.ML * p.RMS * sizeof(float);
-    // the warp queue stages as many matrix groups of a left together as fit (a round of its tasks)
-    p.KG = 1;
-    if (p.schedule == kSchedWarpQueue && smem_limit > fixed + per_group)
-        p.KG = (int)std::max<size_t>(1, std::min<size_t>(std::min<size_t>((size_t)p.RG, 16), (smem_limit - fixed) / per_group));
+    // The warp queue stages as many matrix groups together as fit (a round of its tasks); a round may
+    // run on into the groups of the next left matrices, each of which needs staged rows of its own.
+    p.KG = 1; p.KL = 1;
+    if (p.schedule == kSchedWarpQueue) {
+        for (int kl = std::min<int>((int)pm.n_left, 4); kl >= 1; --kl) {
+            if (smem_limit < (size_t)kl * left_bytes + rest + per_group) continue;
+            const int kg = (int)std::min<size_t>(16, (smem_limit - (size_t)kl * left_bytes - rest) / per_group);
+            // lefts that kg consecutive groups can touch
+            const int need = std::min<int>((int)pm.n_left, (kg + p.RG - 2) / p.RG + 1);
+            if (kl > need) continue;                       // fewer slots do, more room for groups
+            p.KL = kl;
+            p.KG = std::max(1, std::min(kg, pm.n_left == 1 ? p.RG : kg));
+            break;
+        }
+    }
+    const size_t fixed = (size_t)p.KL * left_bytes + rest;
     p.smem_bytes = fixed + (size_t)p.KG * per_group;
 }
 
@@ -590,9 +603,9 @@ std::string describe_plan(const TilePlan& p) {
     char buf[512];
     std::snprintf(buf, sizeof buf,
                   "kernel=tile<TY=%d> grid=(%u,1,1) block=(%d,1,1) smem=%zu plan{H=%d W=%d Hp=%d Wp=%d SL=%d ML=%d "
-                  "WX=%d WY=%d CX=%d CY=%d RG=%d KG=%d fused=%d S=%d schedule=%s tasks=%u nstage=%d combine=%s workspace=%zu}",
+                  "WX=%d WY=%d CX=%d CY=%d RG=%d KG=%d KL=%d fused=%d S=%d schedule=%s tasks=%u nstage=%d combine=%s workspace=%zu}",
                   p.TY, p.grid, p.threads, p.smem_bytes, p.H, p.W, p.Hp, p.Wp, p.SL, p.ML, p.WX, p.WY,
-                  p.CX, p.CY, p.RG, p.KG, p.fused, p.S,
+                  p.CX, p.CY, p.RG, p.KG, p.KL, p.fused, p.S,
                   p.schedule == kSchedStatic ? "static" : p.schedule == kSchedStreamK ? "stream-k" : "warp-queue",
                   p.tasks, p.nstage,
                   p.combine == kStore ? "store" : p.combine == kAtomic ? "atomic" : p.combine == kFixup ? "fixup" : "workspace",

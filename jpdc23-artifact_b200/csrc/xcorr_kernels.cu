@@ -605,7 +605,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     constexpr bool kFused = TY == 1;
     const TilePlan& p = a.p;
     float* sL = smem;
-    float* sR = smem + (size_t)p.nstage * p.LS;
+    float* sR = smem + (size_t)p.KL * p.nstage * p.LS;
     const int H = p.H, W = p.W, Hp = p.Hp, Wp = p.Wp;
     const int tid = threadIdx.x, nthr = blockDim.x;
 
@@ -662,20 +662,21 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
 
     while (u < uend) {
         bool stage_ok = true;
-        int r0, r1, bx, by, rg, l, combine, ngroups = 1;
+        int r0, r1, bx, by, rg, l, combine, ngroups = 1, nlefts = 1;
         unsigned long long q_begin = 0, q_end = 0, q_yrow0 = 0;      // this round's tasks (warp queue)
         unsigned task_id = 0, first_block = 0;
         int n_parts = 1, part = 0;
         if (p.schedule == kSchedWarpQueue) {
-            // one round: up to KG consecutive matrix groups of one left matrix, staged together
+            // one round: up to KG consecutive matrix groups (of up to KL left matrices), staged together
             const unsigned t2 = (kFused && p.fused) ? (unsigned)p.NTX : 2u * (unsigned)p.NTX;   // tasks per y row
             q_yrow0 = u / t2;
             const unsigned g0 = (unsigned)(q_yrow0 / (unsigned)p.NGY);
             l = (int)(g0 / (unsigned)p.RG);
             rg = (int)(g0 - (unsigned)l * p.RG);
             unsigned g_last = (unsigned)(((uend - 1) / t2) / (unsigned)p.NGY);
-            g_last = min(g_last, min(g0 + (unsigned)p.KG - 1u, (unsigned)(l + 1) * p.RG - 1u));
+            g_last = min(g_last, min(g0 + (unsigned)p.KG - 1u, (unsigned)(l + p.KL) * p.RG - 1u));
             ngroups = (int)(g_last - g0) + 1;
+            nlefts = (int)(g_last / (unsigned)p.RG) - l + 1;
             q_begin = u;
             q_end = min(uend, (unsigned long long)(g_last + 1) * p.NGY * t2);
             u = q_end;
@@ -710,14 +711,23 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         int rowbase = r0 + cya;
         if (rowbase >= Hp) rowbase -= Hp;
 
-        // matrices staged behind each other: the block's group, or the round's groups (warp queue),
-        // which are consecutive in memory -- matrix mm is right matrix rg * ML + mm of left l
+        // Matrices staged behind each other: the block's group, or the round's groups (warp queue).
+        // Staged matrix mm belongs to group rg + mm / ML counted from left l; a round may run on into
+        // the groups of the following left matrices, each of which has a slot of staged rows of its own.
         const int nmat = ngroups * p.ML;
-        // ---- stage the left rows: staged row i holds left row (rowbase + i) mod Hp, zeros
+        const int log_ml = 5 - p.logSL;
+        auto right_of = [&](int mm, size_t& rmat) -> bool {
+            const unsigned gg = (unsigned)rg + (unsigned)(mm >> log_ml);
+            const unsigned lt = gg / (unsigned)p.RG;
+            const unsigned j = (gg - lt * (unsigned)p.RG) * (unsigned)p.ML + (unsigned)(mm & (p.ML - 1));
+            rmat = (size_t)(l + lt) * a.pm.right_stride + j;
+            return j < a.pm.m;
+        };
+        const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);   // staged rows per left (== p.nstage in a round)
+        const int nlrows = nlefts * nstage;
+        // ---- stage the left rows: staged row i of a slot holds left row (rowbase + i) mod Hp, zeros
         //      where the padded matrix is zero.
         if (bulk) {
-            const float* gL = a.left + (size_t)l * H * W;
-            const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);
             const int rs = r1 - r0;
             const uint32_t row_bytes = (uint32_t)W * 4, mat_bytes = (uint32_t)(rs * W) * 4;
             if (warp == 0) {
@@ -725,45 +735,48 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 // left rows first, then one copy per right matrix (its rows r0..r1-1 are contiguous)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 uint32_t bytes = 0;
-                for (int i = lane; i < nstage + nmat; i += 32) {
-                    if (i < nstage) {
-                        int row = rowbase + i;
+                for (int i = lane; i < nlrows + nmat; i += 32) {
+                    if (i < nlrows) {
+                        int row = rowbase + i % nstage;
                         if (row >= Hp) row -= Hp;
                         if (row < H) bytes += row_bytes;
-                    } else if ((unsigned)rg * p.ML + (i - nstage) < a.pm.m) {
-                        bytes += mat_bytes;
+                    } else {
+                        size_t rmat;
+                        if (right_of(i - nlrows, rmat)) bytes += mat_bytes;
                     }
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
                 if (lane == 0) mbar_expect(stage_bar, bytes + a.stage_expect_surplus);
                 __syncwarp();
-                for (int i = lane; i < nstage + nmat; i += 32) {
-                    if (i < nstage) {
-                        int row = rowbase + i;
+                for (int i = lane; i < nlrows + nmat; i += 32) {
+                    if (i < nlrows) {
+                        const int ls = i / nstage;
+                        int row = rowbase + (i - ls * nstage);
                         if (row >= Hp) row -= Hp;
-                        if (row < H) bulk_copy(sL_addr + (uint32_t)(i * p.LS) * 4, gL + (size_t)row * W, row_bytes, stage_bar);
+                        if (row < H)
+                            bulk_copy(sL_addr + (uint32_t)(i * p.LS) * 4, a.left + ((size_t)(l + ls) * H + row) * W, row_bytes, stage_bar);
                     } else {
-                        const int mm = i - nstage;
-                        const unsigned j = (unsigned)rg * p.ML + mm;
-                        if (j < a.pm.m) {
-                            const size_t rmat = (size_t)l * a.pm.right_stride + j;
+                        const int mm = i - nlrows;
+                        size_t rmat;
+                        if (right_of(mm, rmat))
                             bulk_copy(sR_addr + (uint32_t)(mm * p.RMS) * 4, a.right + (rmat * H + r0) * W, mat_bytes, stage_bar);
-                        }
                     }
                 }
             }
             // rows and matrices of the zero padding: plain stores, one warp per row / matrix
             const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int i = warp; i < nstage; i += nthr >> 5) {
-                int row = rowbase + i;
+            for (int i = warp; i < nlrows; i += nthr >> 5) {
+                int row = rowbase + i % nstage;
                 if (row >= Hp) row -= Hp;
                 if (row >= H)
                     for (int x = lane * 4; x < Wp; x += 128) *reinterpret_cast<float4*>(sL + (size_t)i * p.LS + x) = zero4;
             }
-            for (int mm = warp; mm < nmat; mm += nthr >> 5)
-                if ((unsigned)rg * p.ML + mm >= a.pm.m)
+            for (int mm = warp; mm < nmat; mm += nthr >> 5) {
+                size_t rmat;
+                if (!right_of(mm, rmat))
                     for (int x = lane * 4; x < rs * Wp; x += 128) *reinterpret_cast<float4*>(sR + (size_t)mm * p.RMS + x) = zero4;
+            }
             stage_ok = mbar_wait_bounded(stage_bar, stage_parity, a.stage_wait_limit);
             if (!stage_ok) {
                 // Gave up.  Before the block leaves, its own copies must have landed (the shared
@@ -778,18 +791,17 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             stage_parity ^= 1u;
         } else {
         {
-            const float* gL = a.left + (size_t)l * H * W;
             const int units = p.LS >> 2;             // float4 per staged row (last one is padding)
-            const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);
-            const int total = nstage * units;
+            const int total = nlrows * units;
             for (int idx = tid; idx < total; idx += nthr) {
                 const int i = idx / units, c4 = idx - i * units;
-                int row = rowbase + i;
+                const int ls = i / nstage;
+                int row = rowbase + (i - ls * nstage);
                 if (row >= Hp) row -= Hp;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 const int x = c4 * 4;
                 if (row < H && x < W) {
-                    const float* g = gL + (size_t)row * W + x;
+                    const float* g = a.left + ((size_t)(l + ls) * H + row) * W + x;
                     if (a.vec_ok) {
                         stage_copy16(sL_addr + (uint32_t)(i * p.LS + x) * 4, g);
                         continue;
@@ -802,8 +814,8 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 *reinterpret_cast<float4*>(sL + (size_t)i * p.LS + x) = v;
             }
         }
-        // ---- stage rows [r0, r1) of the block's ML right matrices, zeros for the padding
-        //      columns and for matrices past the end of the left's group.
+        // ---- stage rows [r0, r1) of the staged right matrices, zeros for the padding
+        //      columns and for matrices past the end of a left's group.
         {
             const int units = Wp >> 2;
             const int rs = r1 - r0;
@@ -813,11 +825,11 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 const int mm = idx / per_mat;
                 const int rem = idx - mm * per_mat;
                 const int rr = rem / units, c4 = rem - rr * units;
-                const unsigned j = (unsigned)rg * p.ML + mm;
+                size_t rmat;
+                const bool live = right_of(mm, rmat);
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 const int x = c4 * 4;
-                if (j < a.pm.m && x < W) {
-                    const size_t rmat = (size_t)l * a.pm.right_stride + j;
+                if (live && x < W) {
                     const float* g = a.right + (rmat * H + (r0 + rr)) * W + x;
                     if (a.vec_ok) {
                         stage_copy16(sR_addr + (uint32_t)(mm * p.RMS + rr * Wp + x) * 4, g);
@@ -850,7 +862,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         }
         bool first = true;
         while (true) {
-            int tile_x, grp_y, slot = 0, pass_lo = 0, pass_hi = 2;
+            int tile_x, grp_y, slot = 0, pass_lo = 0, pass_hi = 2, task_l = l, task_rg = rg;
             if (p.schedule == kSchedWarpQueue) {
                 unsigned v = 0;
                 if (lane == 0) v = (unsigned)atomicAdd(queue, 1);
@@ -866,6 +878,8 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 const unsigned g = (unsigned)(yrow / (unsigned)p.NGY);
                 grp_y = (int)(yrow - (unsigned long long)g * p.NGY);
                 slot = (int)(g - (unsigned)(l * p.RG + rg));
+                task_l = (int)(g / (unsigned)p.RG);
+                task_rg = (int)(g - (unsigned)task_l * p.RG);
                 tile_x = (fused || which == 0) ? (int)k : p.NTX - 1 - (int)k;
                 if (!fused) { pass_lo = which == 0 ? (int)kPassUnwrapped : (int)kPassWrapped; pass_hi = pass_lo + 1; }
             } else {
@@ -874,10 +888,11 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 if (!first || tile_x >= p.NTX || grp_y >= p.NGY) break;
                 first = false;
             }
-            const unsigned jright = (unsigned)(rg + slot) * p.ML + m;
+            const unsigned jright = (unsigned)task_rg * p.ML + m;
             const bool lane_live = jright < a.pm.m;
             const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
-            const size_t out_mat = (size_t)l * a.pm.m + jright;
+            const size_t out_mat = (size_t)task_l * a.pm.m + jright;
+            const uint32_t sl_task = sL_addr + (uint32_t)((task_l - l) * p.nstage * p.LS) * 4;   // the task's left slot
             float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out :
                           (FIXUP && combine == kFixup) ? a.ws + (size_t)part * a.total_out : a.out)
                          + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
@@ -885,12 +900,12 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             const int comb = (FIXUP && combine == kFixup) ? (int)kStore : combine;
             if constexpr (kFused) {
                 if (fused) {
-                    tile_fused32<TY>(p, dst, sL_addr, rsl, r0, r1, cy0, cya, tile_x, lane_live, comb, flush_scratch,
+                    tile_fused32<TY>(p, dst, sl_task, rsl, r0, r1, cy0, cya, tile_x, lane_live, comb, flush_scratch,
                                      lane, cls_per_block);
                     continue;
                 }
             }
-            tile_passes<TY>(p, dst, sL_addr, rsl, r0, r1, cy0, cya, tile_x * kTX, lane_live, comb, flush_scratch, lane,
+            tile_passes<TY>(p, dst, sl_task, rsl, r0, r1, cy0, cya, tile_x * kTX, lane_live, comb, flush_scratch, lane,
                             cls_per_block, pass_lo, pass_hi);
         }
         if (FIXUP && combine == kFixup) {

@@ -70,7 +70,8 @@ struct TilePlan {
     int RSmax;         // rows of the longest slice
     int RG;            // right-matrix groups per left = ceil(m / ML)
     int KG;            // matrix groups staged together (1 unless the schedule is the warp queue)
-    int fused;         // 1: rows of 32 padded columns run both passes fused (TY <= 2)
+    int KL;            // left matrices with staged rows of their own (1 unless the schedule is the warp queue)
+    int fused;         // 1: rows of 32 padded columns run both passes fused (one class per thread)
     int nstage;        // left rows staged in shared memory (at most; a short segment stages fewer)
     int LS;            // floats between staged left rows (Wp + 4: row*LS/4 odd -> conflict-free float4)
     int RMS;           // floats between the staged right matrices of one block
