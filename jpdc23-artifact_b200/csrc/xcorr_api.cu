@@ -177,7 +177,7 @@ void finish_plan(TilePlan& p, const PairMap& pm, size_t smem_limit = kSmemLimit)
     p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
     p.threads = 32 * p.WX * p.WY;
     // the fused row engine exists for 32 padded columns and 1 class per thread
-    if (p.Wp != 32 || p.TY != 1) p.fused = 0;
+    if (p.Wp != 32 || p.TY != 1 || p.threads > kMaxWarps * 32) p.fused = 0;
     // staged left rows and per-warp flush staging (+ the warp queue's counter and the staging barrier)
     const size_t left_bytes = (size_t)p.nstage * p.LS * sizeof(float);
     const size_t rest = (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;
@@ -222,8 +222,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
     if (want_sl != 0 && (!is_pow2(want_sl) || want_sl > 32))
         return fail(XCORR_ERR_INVALID_HINT, "class_lanes must be 0 or a power of two <= 32");
     const int want_wx = h ? h->warps_x : 0, want_wy = h ? h->warps_y : 0;
-    if (want_wx < 0 || want_wy < 0 || (want_wx ? want_wx : 1) * (want_wy ? want_wy : 1) > kMaxWarps)
-        return fail(XCORR_ERR_INVALID_HINT, "warps_x * warps_y must be 1..16");
+    if (want_wx < 0 || want_wy < 0 || (want_wx ? want_wx : 1) * (want_wy ? want_wy : 1) > kWideBlockWarps)
+        return fail(XCORR_ERR_INVALID_HINT, "warps_x * warps_y must be 1..16 (up to 28 for schedule=3 with overlap_rows=1)");
     const int want_s = h ? h->row_slices : 0;
     if (want_s < 0 || want_s > H) return fail(XCORR_ERR_INVALID_HINT, "row_slices must be 0..rows");
     const int want_combine = h ? h->combine : 0;
@@ -312,9 +312,10 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
             if (queue_ok) {
                 if (want_wx || want_wy) {
                     const int nw = (want_wx ? want_wx : 1) * (want_wy ? want_wy : 1);
-                    cands.push_back({nw, 1, 1, kSchedWarpQueue});
+                    if (nw <= kMaxWarps || TY == 1) cands.push_back({nw, 1, 1, kSchedWarpQueue});
                 } else {
                     for (int nw : {8, 12, 16}) cands.push_back({nw, 1, 1, kSchedWarpQueue});
+                    if (TY == 1) cands.push_back({kWideBlockWarps, 1, 1, kSchedWarpQueue});
                 }
             }
 
@@ -331,7 +332,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 // resident warps per SM (1 KB of shared memory reserved per block): below ~12
                 // the FFMA pipe idles on shared-memory latency
                 const int by_smem = (int)((dev.smem_optin + 1024) / (p.smem_bytes + 1024));
-                const int regs = (p.threads <= kSmallBlockThreads && TY >= 3) ? 168 : 128;
+                if (p.threads > kMaxWarps * 32 && (c.sched != kSchedWarpQueue || TY != 1)) continue;   // no such build
+                const int regs = p.threads > kMaxWarps * 32 ? 72 : (p.threads <= kSmallBlockThreads && TY >= 3) ? 168 : 128;
                 const int by_regs = 65536 / (regs * p.threads);
                 const int blocks_sm = std::max(1, std::min(by_smem, by_regs));
                 const int resident = blocks_sm * (p.threads / 32);

@@ -416,6 +416,44 @@ __device__ __forceinline__ void fused32_flush(float (&accU)[TY][kTX], float (&ac
     }
 }
 
+// The rows [r0, r1) of one tile, TILE known at compile time: the row loop holds nothing but the
+// row itself, one compare for the next flush event and the left-row pointer updates.
+template<int TY, int TILE>
+__device__ __forceinline__ void fused32_rows(float (&accU)[TY][kTX], float (&accW)[TY][kTX], uint32_t (&lofs)[TY],
+                                             uint32_t sL_addr, uint32_t rrow, int r0, int r1, int Hp, int H, int W,
+                                             int SL, uint32_t ls_bytes, uint32_t stage_bytes, int cy0, bool lane_live,
+                                             float* __restrict__ dst, int combine, float* flush_scratch, int lane) {
+    const int OW = 2 * W - 1;
+    // the warp's classes start wrapping in y at the consecutive rows wrap_lo .. wrap_lo + SL*TY - 1:
+    // when the walk reaches such a row the class's unwrapped-in-y sums are complete and are written
+    const int wrap_lo = Hp - ((cy0 & ~(SL - 1)) + SL * TY - 1);
+    const int wrap_hi = wrap_lo + SL * TY;
+    int next_evt = max(wrap_lo, r0 + 1);
+    if (next_evt >= wrap_hi) next_evt = 0x7fffffff;
+#pragma unroll 1
+    for (int ry = r0; ry < r1; ++ry, rrow += 32 * 4) {
+        if (ry == next_evt) {
+            int tsel = -1;
+#pragma unroll
+            for (int t = 0; t < TY; ++t)
+                if (ry == Hp - (cy0 + SL * t)) tsel = t;
+            const int cyt = cy0 + SL * (tsel < 0 ? 0 : tsel);
+            const bool has = tsel >= 0 && lane_live && cyt < H;
+            fused32_flush<TY>(accU, accW, tsel, has, dst + (size_t)(cyt + H - 1) * OW, TILE * kTX, W, combine, flush_scratch, lane);
+            next_evt = ry + 1 < wrap_hi ? ry + 1 : 0x7fffffff;
+        }
+        uint32_t lp[TY];
+#pragma unroll
+        for (int t = 0; t < TY; ++t) lp[t] = sL_addr + lofs[t];
+        fused32_row<TY, TILE>(accU, accW, lp, rrow);
+#pragma unroll
+        for (int t = 0; t < TY; ++t) {
+            lofs[t] += ls_bytes;
+            if (lofs[t] == stage_bytes) lofs[t] = 0;
+        }
+    }
+}
+
 template<int TY>
 __device__ __forceinline__ void tile_fused32(const TilePlan& p, float* __restrict__ dst, uint32_t sL_addr,
                                              uint32_t rmat_addr, int r0, int r1, int cy0, int cya, int tile,
@@ -424,15 +462,15 @@ __device__ __forceinline__ void tile_fused32(const TilePlan& p, float* __restric
     const int H = p.H, W = p.W, Hp = p.Hp;
     const int OW = 2 * W - 1;
     const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);
-    const uint32_t stage_bytes = (uint32_t)(nstage * p.LS * 4);
-    const int wrap_lo = Hp - ((cy0 & ~(p.SL - 1)) + p.SL * TY - 1);
+    const uint32_t ls_bytes = (uint32_t)p.LS * 4;
+    const uint32_t stage_bytes = (uint32_t)nstage * ls_bytes;
     const int cx0 = tile * kTX;
     uint32_t lofs[TY];
 #pragma unroll
     for (int t = 0; t < TY; ++t) {
         int i = cy0 + p.SL * t - cya;
         if (i >= nstage) i -= nstage;
-        lofs[t] = (uint32_t)(i * p.LS * 4);
+        lofs[t] = (uint32_t)i * ls_bytes;
     }
     float accU[TY][kTX], accW[TY][kTX];
 #pragma unroll
@@ -440,30 +478,12 @@ __device__ __forceinline__ void tile_fused32(const TilePlan& p, float* __restric
 #pragma unroll
         for (int j = 0; j < kTX; ++j) { accU[t][j] = 0.f; accW[t][j] = 0.f; }
 
-    uint32_t rrow = rmat_addr;
-#pragma unroll 1
-    for (int ry = r0; ry < r1; ++ry, rrow += 32 * 4) {
-        // a class that starts wrapping in y at this row: its unwrapped-in-y sums are complete
-        if ((unsigned)(ry - wrap_lo) < (unsigned)(p.SL * TY) && ry > r0) {
-            int tsel = -1;
-#pragma unroll
-            for (int t = 0; t < TY; ++t)
-                if (ry == Hp - (cy0 + p.SL * t)) tsel = t;
-            const int cyt = cy0 + p.SL * (tsel < 0 ? 0 : tsel);
-            const bool has = tsel >= 0 && lane_live && cyt < H;
-            fused32_flush<TY>(accU, accW, tsel, has, dst + (size_t)(cyt + H - 1) * OW, cx0, W, combine, flush_scratch, lane);
-        }
-        uint32_t lp[TY];
-#pragma unroll
-        for (int t = 0; t < TY; ++t) lp[t] = sL_addr + lofs[t];
-        if (tile == 0) fused32_row<TY, 0>(accU, accW, lp, rrow);
-        else           fused32_row<TY, 1>(accU, accW, lp, rrow);
-#pragma unroll
-        for (int t = 0; t < TY; ++t) {
-            lofs[t] += (uint32_t)p.LS * 4;
-            if (lofs[t] == stage_bytes) lofs[t] = 0;
-        }
-    }
+    if (tile == 0)
+        fused32_rows<TY, 0>(accU, accW, lofs, sL_addr, rmat_addr, r0, r1, Hp, H, W, p.SL, ls_bytes, stage_bytes, cy0,
+                            lane_live, dst, combine, flush_scratch, lane);
+    else
+        fused32_rows<TY, 1>(accU, accW, lofs, sL_addr, rmat_addr, r0, r1, Hp, H, W, p.SL, ls_bytes, stage_bytes, cy0,
+                            lane_live, dst, combine, flush_scratch, lane);
 #pragma unroll 1
     for (int te = 0; te < TY; ++te) {
         const int cyt = cy0 + p.SL * te;
@@ -602,7 +622,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     // the fused 32-column rows hold two accumulator sets and a whole right row in registers: built for
     // one class per thread (with two, 16-warp blocks spill and 8..12-warp blocks at 168 registers ran
     // 1.5 times slower than the chunked walk: measured on B200, 32 x 32, 32 x 64 pairs)
-    constexpr bool kFused = TY == 1;
+    constexpr bool kFused = TY == 1 && BOUND <= kMaxWarps * 32;
     const TilePlan& p = a.p;
     float* sL = smem;
     float* sR = smem + (size_t)p.KL * p.nstage * p.LS;
@@ -1271,6 +1291,14 @@ static cudaError_t launch_tile_variant(const TileArgs& a, int device, cudaStream
 
 template<int TY>
 static cudaError_t launch_tile_ty(const TileArgs& a, int device, cudaStream_t stream) {
+    if (a.p.threads > kMaxWarps * 32) {
+        // the 28-warp build: one class per thread, warp queue, plain stores
+        if constexpr (TY == 1) {
+            if (a.p.schedule == kSchedWarpQueue && a.p.threads <= kWideBlockWarps * 32)
+                return launch_tile_instance<1, kWideBlockWarps * 32, false>(a, device, stream);
+        }
+        return cudaErrorInvalidConfiguration;
+    }
     return a.p.threads <= kSmallBlockThreads ? launch_tile_variant<TY, kSmallBlockThreads>(a, device, stream)
                                              : launch_tile_variant<TY, kMaxWarps * 32>(a, device, stream);
 }
