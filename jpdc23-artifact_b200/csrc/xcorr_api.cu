@@ -177,7 +177,7 @@ void finish_plan(TilePlan& p, const PairMap& pm, size_t smem_limit = kSmemLimit)
     p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
     p.threads = 32 * p.WX * p.WY;
     // the fused row engine exists for 32 padded columns and 1 class per thread
-    if (p.Wp != 32 || p.TY != 1 || p.threads > kMaxWarps * 32) p.fused = 0;
+    if (p.Wp != 32 || p.TY != 1) p.fused = 0;
     // staged left rows and per-warp flush staging (+ the warp queue's counter and the staging barrier)
     const size_t left_bytes = (size_t)p.nstage * p.LS * sizeof(float);
     const size_t rest = (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;
@@ -214,16 +214,16 @@ size_t fixup_counters_offset(int pieces, unsigned long long total_out) {
 // Every candidate gets an estimated time; the smallest wins.
 xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints* h, const DeviceInfo& dev,
                               TilePlan* out, size_t max_workspace_bytes) {
-    TilePlan best{};
-    double best_time = -1.0;
+    TilePlan best{}, best_queue{};                 // best_queue: the warp queue as a candidate of the automatic choice
+    double best_time = -1.0, best_queue_time = -1.0;
     const int want_ty = h ? h->overlap_rows : 0;
     const int want_sl = h ? h->class_lanes : 0;
     if (want_ty < 0 || want_ty > kMaxTY) return fail(XCORR_ERR_INVALID_HINT, "overlap_rows must be 0..4");
     if (want_sl != 0 && (!is_pow2(want_sl) || want_sl > 32))
         return fail(XCORR_ERR_INVALID_HINT, "class_lanes must be 0 or a power of two <= 32");
     const int want_wx = h ? h->warps_x : 0, want_wy = h ? h->warps_y : 0;
-    if (want_wx < 0 || want_wy < 0 || (want_wx ? want_wx : 1) * (want_wy ? want_wy : 1) > kWideBlockWarps)
-        return fail(XCORR_ERR_INVALID_HINT, "warps_x * warps_y must be 1..16 (up to 28 for schedule=3 with overlap_rows=1)");
+    if (want_wx < 0 || want_wy < 0 || (want_wx ? want_wx : 1) * (want_wy ? want_wy : 1) > kMaxWarps)
+        return fail(XCORR_ERR_INVALID_HINT, "warps_x * warps_y must be 1..16");
     const int want_s = h ? h->row_slices : 0;
     if (want_s < 0 || want_s > H) return fail(XCORR_ERR_INVALID_HINT, "row_slices must be 0..rows");
     const int want_combine = h ? h->combine : 0;
@@ -280,11 +280,15 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
             const bool streamk_ok = (want_sched == 0 || want_sched == kSchedStreamK) && want_s <= 1 &&
                                     want_combine != XCORR_COMBINE_STORE &&
                                     !(want_sched == 0 && want_combine == XCORR_COMBINE_WORKSPACE);
-            // The warp queue is only taken on request: measured on B200 it loses to the static
-            // schedule on every benchmark shape, because a warp task cannot be shared and a warp
-            // is bound to one of the SM's four schedulers, so its balance is no finer than the
-            // static one's while its blocks keep fewer warps busy.
-            const bool queue_ok = want_sched == kSchedWarpQueue && want_s <= 1 &&
+            // The warp queue (pass tasks of unequal length taken longest first by the warps of one
+            // resident wave of blocks; plain stores, bit-reproducible) is a candidate of the automatic
+            // choice too: it removes the wave quantisation of a few hundred equal block tasks on 148
+            // SMs.  Measured on B200 it wins where every warp gets two or more tasks (64 x 64 x 512:
+            // 351 against 371 us; 48 x 48 4 x 128: 131 against 148 us) and loses where a warp gets
+            // about one (64 x 64 x 128: 120 against 108 us of stream-K), so those are left out.
+            const bool queue_auto = want_sched == 0 && want_s <= 1 && want_combine == XCORR_COMBINE_AUTO &&
+                                    !want_wx && !want_wy;
+            const bool queue_ok = (want_sched == kSchedWarpQueue || queue_auto) && want_s <= 1 &&
                                   want_combine != XCORR_COMBINE_ATOMIC && want_combine != XCORR_COMBINE_WORKSPACE;
             std::vector<std::pair<int, int>> shapes;
             if (want_wx && want_wy) {
@@ -312,10 +316,10 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
             if (queue_ok) {
                 if (want_wx || want_wy) {
                     const int nw = (want_wx ? want_wx : 1) * (want_wy ? want_wy : 1);
-                    if (nw <= kMaxWarps || TY == 1) cands.push_back({nw, 1, 1, kSchedWarpQueue});
+                    cands.push_back({nw, 1, 1, kSchedWarpQueue});
                 } else {
-                    for (int nw : {8, 12, 16}) cands.push_back({nw, 1, 1, kSchedWarpQueue});
-                    if (TY == 1) cands.push_back({kWideBlockWarps, 1, 1, kSchedWarpQueue});
+                    for (int nw : {8, 12, 16})
+                        if (!queue_auto || nw >= 12) cands.push_back({nw, 1, 1, kSchedWarpQueue});
                 }
             }
 
@@ -332,8 +336,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 // resident warps per SM (1 KB of shared memory reserved per block): below ~12
                 // the FFMA pipe idles on shared-memory latency
                 const int by_smem = (int)((dev.smem_optin + 1024) / (p.smem_bytes + 1024));
-                if (p.threads > kMaxWarps * 32 && (c.sched != kSchedWarpQueue || TY != 1)) continue;   // no such build
-                const int regs = p.threads > kMaxWarps * 32 ? 72 : (p.threads <= kSmallBlockThreads && TY >= 3) ? 168 : 128;
+                const int regs = (p.threads <= kSmallBlockThreads && TY >= 3) ? 168 : 128;
                 const int by_regs = 65536 / (regs * p.threads);
                 const int blocks_sm = std::max(1, std::min(by_smem, by_regs));
                 const int resident = blocks_sm * (p.threads / 32);
@@ -352,7 +355,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 // TY = 4 (and a little for TY = 3): measured 28 against 47 TFLOP/s on 64 x 64 x 512
                 const double build_eff = p.threads > kSmallBlockThreads ? (TY == 4 ? 0.6 : TY == 3 ? 0.9 : 1.0) : 1.0;
                 // (fused 32-column rows: one visit per row, straight-line code)
-                const double tile_eff = p.fused ? 1.07 / (1.0 + 20.0 / ((double)p.Wp * TY * kTX))
+                const double tile_eff = p.fused ? 0.96 / (1.0 + 20.0 / ((double)p.Wp * TY * kTX))
                                                 : ty_eff[TY] / (1.0 + kRowSlots / ((double)p.Wp * TY * kTX));
                 const double rate = sm_rate * tile_eff * occ_eff * smem_eff * block_prior * lanes_prior * build_eff;
                 // filling the staging buffers: bytes over ~64 B/clk from L2 plus a latency
@@ -370,15 +373,21 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     double G = (double)dev.sm_count * blocks_sm;
                     if (G > ptasks) G = ptasks;
                     grid = (unsigned)G;
-                    const double units_block = units / G;
-                    const double macs_per_unit = 32.0 * H * 2.0 * TY * kTX;          // a quarter chunk of every row
-                    // the busiest scheduler ends at most about one longest task after the average
-                    const double longest = p.fused ? (double)queue_units_per_yrow(p.NTX) / p.NTX : 4.0 * (p.NCH - 2) + kQueueTriangleWeight;
-                    const double per_sched = units_block / 4.0 + 0.5 * longest / std::max(1.0, units_block / 4.0 / longest);
-                    const double rounds = std::max(1.0, std::ceil(groups / G / p.KG)) + (groups / G < p.KG ? 0.5 : 0.0);
-                    const double t_rate = std::ceil(G / dev.sm_count) * (4.0 * per_sched * macs_per_unit / rate + rounds * t_stage);
+                    // multiply-adds of a block's share (as the other schedules count them) and of its
+                    // longest task; every round ends with the schedulers waiting for the last of its tasks:
+                    // a fraction of a longest task each (fitted to 16 timed plans of the benchmark shapes
+                    // and their shards)
+                    (void)units;
+                    const double macs_block = groups * p.NGY * p.NTX * 32.0 * H * p.Wp * TY * kTX / G;
+                    const double longest = 32.0 * H * TY * kTX * (p.fused ? (double)p.Wp : 8.0 * (p.NCH - 1));
+                    const double rounds = std::ceil((groups / G + 1.0) / p.KG);
+                    // (the tile's own two chunks run as triangles with reloaded windows: dearer on narrow rows)
+                    const double narrow = p.fused ? 1.05 : 1.0 + 0.5 / ((double)p.NTX * p.NTX);
+                    const double t_rate = std::ceil(G / dev.sm_count) *
+                                          ((macs_block * narrow + rounds * 4.0 * 0.4 * longest) / rate + rounds * t_stage);
                     const double t_serial = std::ceil(ptasks / G / warps_blk) * H * p.Wp * TY * kTX / 1.8e9;
                     t = std::max(t_rate, t_serial);
+                    if (queue_auto && ptasks / G < 2.0 * warps_blk) continue;   // about one task per warp: the tail decides
                     comb = kStore;
                 } else if (c.sched == kSchedStreamK) {
                     const double units = tasks * H;
@@ -475,16 +484,32 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 if (plan_debug)
                     std::fprintf(stderr, "plan TY=%d SL=%d WX=%d WY=%d S=%d sched=%d comb=%d grid=%u t=%.2f us\n", TY, SL, c.WX,
                                  c.WY, c.S, c.sched, comb, grid, t * 1e6);
-                if (best_time < 0.0 || t < best_time * 0.9999) {
-                    best_time = t;
-                    best = p;
-                    best.combine = comb;
-                    best.pieces = sk_parts;
-                    best.grid = grid;
-                    best.tasks = (unsigned)tasks;
+                const bool auto_queue_cand = queue_auto && c.sched == kSchedWarpQueue;
+                TilePlan& slot = auto_queue_cand ? best_queue : best;
+                double& slot_time = auto_queue_cand ? best_queue_time : best_time;
+                if (slot_time < 0.0 || t < slot_time * 0.9999) {
+                    slot_time = t;
+                    slot = p;
+                    slot.combine = comb;
+                    slot.pieces = sk_parts;
+                    slot.grid = grid;
+                    slot.tasks = (unsigned)tasks;
                 }
             }
         }
+    }
+    // The automatic choice takes the warp queue only against a static plan that leaves a good part of
+    // its last wave of blocks empty (128 equal blocks on 148 SMs): that is the loss the queue removes.
+    // Against stream-K, which is balanced by construction, it measured slower on the dominant benchmark
+    // shape (48 x 48 16 x 128: 460 against 447 us) although the estimates are level.
+    if (best_queue_time >= 0.0) {
+        bool take = best_time < 0.0;
+        if (!take && best.schedule == kSchedStatic) {
+            const double blocks = (double)best.tasks * best.S;
+            const double wave_fill = blocks / (std::ceil(blocks / dev.sm_count) * dev.sm_count);
+            take = wave_fill < 0.9 && best_queue_time < best_time;
+        }
+        if (take) { best = best_queue; best_time = best_queue_time; }
     }
     if (best_time < 0.0)
         return fail(XCORR_ERR_UNSUPPORTED, "no tile plan fits in shared memory for this shape / these hints");

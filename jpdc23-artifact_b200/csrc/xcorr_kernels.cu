@@ -622,7 +622,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     // the fused 32-column rows hold two accumulator sets and a whole right row in registers: built for
     // one class per thread (with two, 16-warp blocks spill and 8..12-warp blocks at 168 registers ran
     // 1.5 times slower than the chunked walk: measured on B200, 32 x 32, 32 x 64 pairs)
-    constexpr bool kFused = TY == 1 && BOUND <= kMaxWarps * 32;
+    constexpr bool kFused = TY == 1;
     const TilePlan& p = a.p;
     float* sL = smem;
     float* sR = smem + (size_t)p.KL * p.nstage * p.LS;
@@ -1291,14 +1291,6 @@ static cudaError_t launch_tile_variant(const TileArgs& a, int device, cudaStream
 
 template<int TY>
 static cudaError_t launch_tile_ty(const TileArgs& a, int device, cudaStream_t stream) {
-    if (a.p.threads > kMaxWarps * 32) {
-        // the 28-warp build: one class per thread, warp queue, plain stores
-        if constexpr (TY == 1) {
-            if (a.p.schedule == kSchedWarpQueue && a.p.threads <= kWideBlockWarps * 32)
-                return launch_tile_instance<1, kWideBlockWarps * 32, false>(a, device, stream);
-        }
-        return cudaErrorInvalidConfiguration;
-    }
     return a.p.threads <= kSmallBlockThreads ? launch_tile_variant<TY, kSmallBlockThreads>(a, device, stream)
                                              : launch_tile_variant<TY, kMaxWarps * 32>(a, device, stream);
 }

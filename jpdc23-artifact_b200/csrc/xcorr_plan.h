@@ -23,10 +23,6 @@ constexpr int kTX = 16;           // x classes per thread (one 16-wide tile)
 constexpr int kMaxTY = 4;         // y classes per thread
 constexpr int kMaxWarps = 16;     // warps per block
 constexpr int kSmallBlockThreads = 384;  // blocks up to this size run the 168-register build of the kernel
-// Warp-queue plans of one class per thread may use one block of 28 warps per SM (a 72-register
-// build): 7 warps per scheduler, one task each, where 148 SMs x 4 schedulers meet a number of
-// equal tasks that 4 warps per scheduler would take in two unequal waves.
-constexpr int kWideBlockWarps = 28;
 constexpr int kSmemLimit = 227 * 1024;
 // per-warp staging area of the output flush: 32 rows of kTX + 1 floats and 32 row addresses
 constexpr int kFlushBytesPerWarp = 32 * (kTX + 1) * 4 + 32 * 8;
