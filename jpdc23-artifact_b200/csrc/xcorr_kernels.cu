@@ -738,7 +738,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         const int log_ml = 5 - p.logSL;
         auto right_of = [&](int mm, size_t& rmat) -> bool {
             const unsigned gg = (unsigned)rg + (unsigned)(mm >> log_ml);
-            const unsigned lt = gg / (unsigned)p.RG;
+            const unsigned lt = ngroups == 1 ? 0u : gg / (unsigned)p.RG;      // one group: no division in the copy loops
             const unsigned j = (gg - lt * (unsigned)p.RG) * (unsigned)p.ML + (unsigned)(mm & (p.ML - 1));
             rmat = (size_t)(l + lt) * a.pm.right_stride + j;
             return j < a.pm.m;

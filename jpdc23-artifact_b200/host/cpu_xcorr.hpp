@@ -16,8 +16,8 @@
 namespace cross {
 
 // One pair, all shifts: out[(sy+H-1)*(2W-1) + (sx+W-1)] = sum left[y+sy][x+sx]*right[y][x].
-template<typename T>
-void cpu_cross_corr_pair(const float* left, const float* right, T* out, int H, int W) {
+template<typename T, typename IN = float>
+void cpu_cross_corr_pair(const IN* left, const IN* right, T* out, int H, int W) {
     const int OW = 2 * W - 1;
     for (int sy = -(H - 1); sy <= H - 1; ++sy) {
         const int y0 = std::max(sy, 0), y1 = std::min(H + sy, H);
@@ -25,8 +25,8 @@ void cpu_cross_corr_pair(const float* left, const float* right, T* out, int H, i
             const int x0 = std::max(sx, 0), x1 = std::min(W + sx, W);
             T sum = T{};
             for (int yl = y0; yl < y1; ++yl) {
-                const float* lrow = left + static_cast<std::size_t>(yl) * W;
-                const float* rrow = right + static_cast<std::size_t>(yl - sy) * W - sx;
+                const IN* lrow = left + static_cast<std::size_t>(yl) * W;
+                const IN* rrow = right + static_cast<std::size_t>(yl - sy) * W - sx;
                 for (int xl = x0; xl < x1; ++xl) sum += static_cast<T>(rrow[xl]) * static_cast<T>(lrow[xl]);
             }
             out[static_cast<std::size_t>(sy + H - 1) * OW + (sx + W - 1)] = sum;

@@ -17,6 +17,7 @@
 
 #include <cstdlib>
 #include <fstream>
+#include <functional>
 #include <iostream>
 #include <map>
 #include <optional>
@@ -225,6 +226,215 @@ int run_computation_steps(algorithm& alg, const logger& log) {
     return 0;
 }
 
+// ---- `run --data_type double` -------------------------------------------------------------------
+// The reference parses the option and refuses it (main.cpp:431-438: the <double> dispatch is
+// commented out).  Here every direct algorithm name runs its mode in double through the library's
+// double-precision kernel (xcorr_run_f64; the name selects the mode, not a kernel family), the
+// cpu_* names through the CPU loop in double; same files, steps, timing labels and exit codes as
+// the float path.  The FFT names stay single precision.
+struct double_run_options {
+    const algorithm_spec* spec;
+    std::filesystem::path ref_path, target_path, times_path;
+    std::optional<std::filesystem::path> out_path;
+    std::optional<std::string> validate;       // empty string: recompute on the CPU
+    benchmark_type bench;
+    std::size_t outer_loops;
+    double min_time_ns;
+    bool append, progress;
+};
+
+void cpu_run_double(int mode, const basic_matrix_array<double>& left, const basic_matrix_array<double>& right,
+                    basic_matrix_array<double>& out, bool grouped) {
+    const int H = static_cast<int>(left.rows()), W = static_cast<int>(left.cols());
+    const uint32_t nl = left.num_matrices(), nr = right.num_matrices();
+    switch (mode) {
+    case XCORR_ONE_TO_ONE:
+        cpu_cross_corr_pair<double, double>(left.matrix(0), right.matrix(0), out.matrix(0), H, W);
+        break;
+    case XCORR_ONE_TO_MANY:
+        for (uint32_t t = 0; t < nr; ++t) cpu_cross_corr_pair<double, double>(left.matrix(0), right.matrix(t), out.matrix(t), H, W);
+        break;
+    case XCORR_N_TO_MN: {
+        const uint32_t m = nr / nl;
+        for (uint32_t r = 0; r < nl; ++r)
+            for (uint32_t t = 0; t < m; ++t) {
+                const uint32_t idx = grouped ? r * m + t : t * nl + r;
+                cpu_cross_corr_pair<double, double>(left.matrix(r), right.matrix(idx), out.matrix(idx), H, W);
+            }
+        break;
+    }
+    default:
+        for (uint32_t r = 0; r < nl; ++r)
+            for (uint32_t t = 0; t < nr; ++t)
+                cpu_cross_corr_pair<double, double>(left.matrix(r), right.matrix(t), out.matrix(r * nr + t), H, W);
+    }
+}
+
+int run_double(const double_run_options& o) {
+    using darray = basic_matrix_array<double>;
+    const algorithm_spec& spec = *o.spec;
+    if (spec.fam == family::fft) {
+        std::cerr << "Data type double is not available for the FFT algorithms (cuFFT path is single precision)\n";
+        return 1;
+    }
+    const bool gpu = spec.fam != family::cpu;
+    const bool compute_bench = o.bench == benchmark_type::Compute, common = o.bench == benchmark_type::CommonSteps;
+    const bool alg_bench = o.bench == benchmark_type::Algorithm;
+    logger log{o.progress && !compute_bench, o.append};
+    if (gpu) {
+        int have = 0;
+        if (cudaGetDeviceCount(&have) != cudaSuccess || have == 0)
+            throw std::runtime_error("no CUDA device is available; only the cpu_* algorithms run without one");
+    }
+    std::vector<measurement_result> steps(7);
+    auto timed = [&](std::size_t label, auto&& fn) {
+        auto t0 = wall_clock::now();
+        fn();
+        if (gpu) cudaDeviceSynchronize();
+        steps[label] = measurement_result{elapsed_ns(t0), 1};
+    };
+    darray left, right, result;
+    const bool grouped = spec.mode == XCORR_N_TO_MN && gpu;     // the library's order for n_to_mn
+    try {
+        log.log("Loading inputs");
+        timed(0, [&] {
+            left = darray::load_csv(o.ref_path, gpu);
+            right = darray::load_csv(o.target_path, gpu, grouped ? left.num_matrices() : 0);
+            if (left.rows() != right.rows() || left.cols() != right.cols())
+                throw std::runtime_error("Invalid input matrix sizes, expected ref and target to be the same size");
+            if (!xcorr_validate_input_size(spec.mode, left.rows(), left.cols(), left.num_matrices(), right.num_matrices()))
+                throw std::runtime_error("Invalid input matrix counts for " + spec.name + ": " +
+                                         std::to_string(left.num_matrices()) + " left, " +
+                                         std::to_string(right.num_matrices()) + " right");
+        });
+    } catch (std::exception& e) {
+        std::cerr << "Exception occured durign data loading step: " << e.what() << std::endl;
+        return 3;
+    }
+    const uint32_t rows = left.rows(), cols = left.cols(), nl = left.num_matrices(), nr = right.num_matrices();
+    const uint64_t n_out = xcorr_num_results(spec.mode, nl, nr);
+    const std::size_t out_elems = static_cast<std::size_t>(2 * rows - 1) * (2 * cols - 1);
+    double *d_left = nullptr, *d_right = nullptr, *d_out = nullptr;
+    measurement_result kernel_result;
+    auto check = [](cudaError_t e, const char* what) {
+        if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+    };
+    auto xcheck = [](int st) {
+        if (st != XCORR_OK)
+            throw std::runtime_error(std::string("xcorr: ") + xcorr_status_string(st) + ": " + xcorr_last_error_string());
+    };
+    auto computation = [&]() -> int {
+        struct step { const char* message; const char* name; std::size_t label; std::function<void()> fn; };
+        const std::vector<step> seq = {
+            {"Allocating", "allocation", 1, [&] {
+                 result = darray(2 * rows - 1, 2 * cols - 1, static_cast<dsize_t>(n_out), gpu);
+                 if (!gpu) return;
+                 check(cudaMalloc(&d_left, left.size() * sizeof(double)), "cudaMalloc");
+                 check(cudaMalloc(&d_right, right.size() * sizeof(double)), "cudaMalloc");
+                 check(cudaMalloc(&d_out, n_out * out_elems * sizeof(double)), "cudaMalloc");
+             }},
+            {"Transfering data", "data transfer", 2, [&] {
+                 if (!gpu) return;
+                 check(cudaMemcpy(d_left, left.data(), left.size() * sizeof(double), cudaMemcpyHostToDevice), "cudaMemcpy");
+                 check(cudaMemcpy(d_right, right.data(), right.size() * sizeof(double), cudaMemcpyHostToDevice), "cudaMemcpy");
+             }},
+            {"Running test alg", "computation", 3, [&] {
+                 if (!gpu) { cpu_run_double(spec.mode, left, right, result, false); return; }
+                 if (!alg_bench) { xcheck(xcorr_run_f64(spec.mode, d_left, d_right, d_out, rows, cols, nl, nr, nullptr)); return; }
+                 // CUDA_ADAPTIVE_MEASURE (stopwatch.hpp:125-141): events around a growing number of launches
+                 cudaEvent_t e0, e1;
+                 check(cudaEventCreate(&e0), "cudaEventCreate");
+                 check(cudaEventCreate(&e1), "cudaEventCreate");
+                 std::size_t iterations = 1;
+                 do {
+                     check(cudaEventRecord(e0, nullptr), "cudaEventRecord");
+                     for (std::size_t i = 0; i < iterations; ++i)
+                         xcheck(xcorr_run_f64(spec.mode, d_left, d_right, d_out, rows, cols, nl, nr, nullptr));
+                     check(cudaEventRecord(e1, nullptr), "cudaEventRecord");
+                     check(cudaEventSynchronize(e1), "cudaEventSynchronize");
+                     float ms = 0.f;
+                     check(cudaEventElapsedTime(&ms, e0, e1), "cudaEventElapsedTime");
+                     kernel_result = measurement_result{static_cast<double>(ms) * 1e6, iterations};
+                     iterations = next_iteration_count(o.min_time_ns, kernel_result);
+                 } while (iterations != 0);
+                 cudaEventDestroy(e0);
+                 cudaEventDestroy(e1);
+             }},
+            {"Copying output data to host", "finalization", 4, [&] {
+                 if (!gpu) return;
+                 check(cudaMemcpy(result.data(), d_out, n_out * out_elems * sizeof(double), cudaMemcpyDeviceToHost), "cudaMemcpy");
+             }},
+            {"Free resources", "free", 5, [&] {
+                 cudaFree(d_left); cudaFree(d_right); cudaFree(d_out);
+                 d_left = d_right = d_out = nullptr;
+             }},
+        };
+        for (const auto& s : seq) {
+            try {
+                log.log(s.message);
+                if (common) timed(s.label, s.fn); else s.fn();
+            } catch (std::exception& e) {
+                std::cerr << "Exception occured durign " << s.name << " step: " << e.what()
+                          << "\nLast kernel launch arguments:\n" << xcorr_last_launch_string() << std::endl;
+                return 3;
+            }
+        }
+        return 0;
+    };
+    for (std::size_t loop = 0; loop < o.outer_loops; ++loop) {
+        measurement_result compute_result;
+        if (compute_bench) {
+            std::size_t iterations = 1;
+            do {
+                auto t0 = wall_clock::now();
+                for (std::size_t i = 0; i < iterations; ++i) {
+                    if (int ret = computation()) return ret;
+                    if (gpu) cudaDeviceSynchronize();
+                }
+                compute_result = measurement_result{elapsed_ns(t0), iterations};
+                iterations = next_iteration_count(o.min_time_ns, compute_result);
+            } while (iterations != 0);
+        } else if (int ret = computation()) {
+            return ret;
+        }
+        if (gpu && xcorr_check_device() != XCORR_OK) {
+            std::cerr << "Exception somewhere in CUDA code: " << xcorr_last_error_string()
+                      << "\nLast kernel launch arguments:\n" << xcorr_last_launch_string() << std::endl;
+            return 3;
+        }
+        if (o.out_path.has_value()) {
+            log.log("Storing results");
+            const auto path = o.outer_loops > 1 ? loop_out_path(*o.out_path, loop) : *o.out_path;
+            timed(6, [&] { result.store_csv(path, grouped ? nr / nl : 0); });
+        }
+        if (o.bench != benchmark_type::None) {
+            std::vector<std::string> labels;
+            std::vector<measurement_result> results;
+            if (compute_bench) { labels = {"Computation"}; results = {compute_result}; }
+            else if (common) { labels = {"Load", "Prepare", "Transfer", "Run", "Finalize", "Free", "Store"}; results = steps; }
+            else if (gpu) { labels = {"Kernel"}; results = {kernel_result}; }
+            output_measurements(o.times_path, labels, results, {}, o.append || loop > 0);
+        }
+        if (!o.validate.has_value()) {
+            log.log("No validation");
+        } else {
+            darray valid;
+            if (!o.validate->empty()) {
+                log.log("Validating results against " + *o.validate);
+                valid = darray::load_csv(*o.validate, false, grouped ? nl : 0);
+                if (valid.rows() != result.rows() || valid.cols() != result.cols() || valid.num_matrices() != result.num_matrices())
+                    throw std::runtime_error("Cannot validate matrices of different sizes");
+            } else {
+                log.log("Computing valid results and validating");
+                valid = darray(result.rows(), result.cols(), result.num_matrices(), false);
+                cpu_run_double(spec.mode, left, right, valid, grouped);
+            }
+            log.result_stats(validate_result<double>(result.data(), valid.data(), result.size()), !o.append && loop == 0);
+        }
+    }
+    return 0;
+}
+
 int command_run(const std::vector<std::string>& tokens, const std::string& prog) {
     parsed_args a = parse_options(tokens, kRunOptions);
     if (a.has("help")) { print_help(std::cout, prog); return 0; }
@@ -263,10 +473,16 @@ int command_run(const std::vector<std::string>& tokens, const std::string& prog)
         print_help(std::cerr, prog);
         return 1;
     }
-    if (data_type != "single") {   // main.cpp:431-438
+    if (data_type != "single" && data_type != "double") {   // main.cpp:431-438
         std::cerr << "Unknown data type " << data_type << "\n";
         print_help(std::cerr, prog);
         return 1;
+    }
+    if (data_type == "double") {
+        double_run_options o{spec, ref_path, target_path, times_path, out_path, std::nullopt, bench, outer_loops,
+                             min_time_s * 1e9, append, progress};
+        if (a.has("validate")) o.validate = a.values["validate"];
+        return run_double(o);
     }
     if (n_devices < 1) throw option_error("--devices must be at least 1");
     std::vector<int> devices;

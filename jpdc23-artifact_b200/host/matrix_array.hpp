@@ -1,4 +1,5 @@
-// Stack of equally sized float matrices plus the reference's text format.
+// Stack of equally sized matrices (float, or double for --data_type double) plus the reference's
+// text format.
 //
 // Counterpart of data_array<T, ALLOC> and impl::csv (repo/cross-corr/src/matrix.hpp:93-187,
 // :410-619) with the pinned host allocation of allocator.cuh:16-48.
@@ -27,14 +28,15 @@ namespace cross {
 using dsize_t = std::uint32_t;
 
 // Host buffer: page-locked when a CUDA device is there (fast H2D/D2H), plain otherwise.
-class host_buffer {
+template<typename T>
+class basic_host_buffer {
 public:
-    host_buffer() = default;
-    explicit host_buffer(std::size_t count, bool pinned) { allocate(count, pinned); }
-    host_buffer(const host_buffer&) = delete;
-    host_buffer& operator=(const host_buffer&) = delete;
-    host_buffer(host_buffer&& o) noexcept { *this = std::move(o); }
-    host_buffer& operator=(host_buffer&& o) noexcept {
+    basic_host_buffer() = default;
+    explicit basic_host_buffer(std::size_t count, bool pinned) { allocate(count, pinned); }
+    basic_host_buffer(const basic_host_buffer&) = delete;
+    basic_host_buffer& operator=(const basic_host_buffer&) = delete;
+    basic_host_buffer(basic_host_buffer&& o) noexcept { *this = std::move(o); }
+    basic_host_buffer& operator=(basic_host_buffer&& o) noexcept {
         if (this != &o) {
             release();
             data_ = o.data_; count_ = o.count_; pinned_ = o.pinned_;
@@ -42,14 +44,14 @@ public:
         }
         return *this;
     }
-    ~host_buffer() { release(); }
+    ~basic_host_buffer() { release(); }
 
-    float* data() { return data_; }
-    const float* data() const { return data_; }
+    T* data() { return data_; }
+    const T* data() const { return data_; }
     std::size_t size() const { return count_; }
 
 private:
-    float* data_ = nullptr;
+    T* data_ = nullptr;
     std::size_t count_ = 0;
     bool pinned_ = false;
 
@@ -58,15 +60,15 @@ private:
         if (count == 0) return;
         if (pinned) {
             void* p = nullptr;
-            if (cudaHostAlloc(&p, count * sizeof(float), cudaHostAllocDefault) == cudaSuccess) {
-                data_ = static_cast<float*>(p);
+            if (cudaHostAlloc(&p, count * sizeof(T), cudaHostAllocDefault) == cudaSuccess) {
+                data_ = static_cast<T*>(p);
                 pinned_ = true;
-                std::memset(data_, 0, count * sizeof(float));
+                std::memset(data_, 0, count * sizeof(T));
                 return;
             }
             (void)cudaGetLastError();  // no device / no pinned memory: fall through to malloc
         }
-        data_ = static_cast<float*>(std::calloc(count, sizeof(float)));
+        data_ = static_cast<T*>(std::calloc(count, sizeof(T)));
         if (!data_) throw std::bad_alloc();
     }
 
@@ -76,11 +78,13 @@ private:
         data_ = nullptr;
     }
 };
+using host_buffer = basic_host_buffer<float>;
 
-class matrix_array {
+template<typename T>
+class basic_matrix_array {
 public:
-    matrix_array() = default;
-    matrix_array(dsize_t rows, dsize_t cols, dsize_t count, bool pinned)
+    basic_matrix_array() = default;
+    basic_matrix_array(dsize_t rows, dsize_t cols, dsize_t count, bool pinned)
         : rows_(rows), cols_(cols), count_(count),
           data_(static_cast<std::size_t>(rows) * cols * count, pinned) {}
 
@@ -89,10 +93,10 @@ public:
     dsize_t num_matrices() const { return count_; }
     std::size_t matrix_elems() const { return static_cast<std::size_t>(rows_) * cols_; }
     std::size_t size() const { return data_.size(); }
-    float* data() { return data_.data(); }
-    const float* data() const { return data_.data(); }
-    float* matrix(dsize_t i) { return data_.data() + matrix_elems() * i; }
-    const float* matrix(dsize_t i) const { return data_.data() + matrix_elems() * i; }
+    T* data() { return data_.data(); }
+    const T* data() const { return data_.data(); }
+    T* matrix(dsize_t i) { return data_.data() + matrix_elems() * i; }
+    const T* matrix(dsize_t i) const { return data_.data() + matrix_elems() * i; }
 
     // matrix.hpp:614-618: file index i of a file holding num_groups groups of group_size
     // matrices goes to slot (i % group_size) * num_groups + i / group_size.
@@ -108,7 +112,8 @@ public:
     // inputs; this format loads at memory speed.
     static bool is_binary_path(const std::filesystem::path& path) { return path.extension() == ".bin"; }
 
-    static matrix_array load_binary(const std::filesystem::path& path, bool pinned, dsize_t group_size) {
+    static basic_matrix_array load_binary(const std::filesystem::path& path, bool pinned, dsize_t group_size) {
+        if constexpr (sizeof(T) != sizeof(float)) throw std::runtime_error("binary matrix files hold float32; use text files with --data_type double");
         std::ifstream in(path, std::ios::binary);
         if (!in) throw std::runtime_error("Could not open file " + path.string());
         char magic[8];
@@ -120,11 +125,11 @@ public:
         if (rows == 0 || cols == 0 || count == 0) throw std::runtime_error("Invalid input file format");
         if (group_size != 0 && count % group_size != 0)
             throw std::runtime_error("Data array cannot be interleaved, as number of matrices is not divisible by group size");
-        matrix_array a(rows, cols, count, pinned);
+        basic_matrix_array a(rows, cols, count, pinned);
         const dsize_t num_groups = group_size ? count / group_size : 0;
         const std::size_t mat_bytes = a.matrix_elems() * sizeof(float);
         for (dsize_t i = 0; i < count; ++i) {
-            float* dst = a.matrix(group_size ? interleaved_index(i, group_size, num_groups) : i);
+            T* dst = a.matrix(group_size ? interleaved_index(i, group_size, num_groups) : i);
             if (!in.read(reinterpret_cast<char*>(dst), static_cast<std::streamsize>(mat_bytes)))
                 throw std::runtime_error("Invalid input file format: file ends inside matrix " + std::to_string(i));
             if (!little_endian())
@@ -139,6 +144,7 @@ public:
     }
 
     void store_binary(const std::filesystem::path& path, dsize_t num_groups) const {
+        if constexpr (sizeof(T) != sizeof(float)) throw std::runtime_error("binary matrix files hold float32; use text files with --data_type double");
         std::ofstream out(path, std::ios::binary);
         if (!out) throw std::runtime_error("Could not open file " + path.string() + " for writing");
         if (num_groups != 0 && count_ % num_groups != 0)
@@ -150,7 +156,7 @@ public:
         const dsize_t group_size = num_groups ? count_ / num_groups : 0;
         std::vector<uint32_t> swapped;
         for (dsize_t i = 0; i < count_; ++i) {
-            const float* src = matrix(num_groups ? interleaved_index(i, group_size, num_groups) : i);
+            const T* src = matrix(num_groups ? interleaved_index(i, group_size, num_groups) : i);
             if (little_endian()) {
                 out.write(reinterpret_cast<const char*>(src), static_cast<std::streamsize>(matrix_elems() * sizeof(float)));
             } else {
@@ -166,7 +172,7 @@ public:
     // group_size == 0: file order (load_from_csv, matrix.hpp:437-450); otherwise the
     // grouped order of load_interleaved_from_csv (matrix.hpp:471-503).  A path ending in .bin
     // is read as a binary matrix file.
-    static matrix_array load_csv(const std::filesystem::path& path, bool pinned, dsize_t group_size = 0) {
+    static basic_matrix_array load_csv(const std::filesystem::path& path, bool pinned, dsize_t group_size = 0) {
         if (is_binary_path(path)) return load_binary(path, pinned, group_size);
         std::ifstream in(path);
         if (!in) throw std::runtime_error("Could not open file " + path.string());
@@ -174,11 +180,11 @@ public:
         read_header(in, rows, cols, count);
         if (group_size != 0 && count % group_size != 0)
             throw std::runtime_error("Data array cannot be interleaved, as number of matrices is not divisible by group size");
-        matrix_array a(rows, cols, count, pinned);
+        basic_matrix_array a(rows, cols, count, pinned);
         const dsize_t num_groups = group_size ? count / group_size : 0;
         std::string line;
         for (dsize_t i = 0; i < count; ++i) {
-            float* dst = a.matrix(group_size ? interleaved_index(i, group_size, num_groups) : i);
+            T* dst = a.matrix(group_size ? interleaved_index(i, group_size, num_groups) : i);
             for (dsize_t y = 0; y < rows; ++y) {
                 if (!std::getline(in, line))
                     throw std::runtime_error("Failed to read line " + std::to_string(y) + " from csv file");
@@ -201,7 +207,7 @@ public:
         out << std::fixed;
         const dsize_t group_size = num_groups ? count_ / num_groups : 0;
         for (dsize_t i = 0; i < count_; ++i) {
-            const float* src = matrix(num_groups ? interleaved_index(i, group_size, num_groups) : i);
+            const T* src = matrix(num_groups ? interleaved_index(i, group_size, num_groups) : i);
             for (dsize_t y = 0; y < rows_; ++y) {
                 const char* sep = "";
                 for (dsize_t x = 0; x < cols_; ++x) {
@@ -215,7 +221,7 @@ public:
 
 private:
     dsize_t rows_ = 0, cols_ = 0, count_ = 0;
-    host_buffer data_;
+    basic_host_buffer<T> data_;
 
     static bool little_endian() {
         const uint32_t one = 1;
@@ -255,14 +261,14 @@ private:
     }
 
     // One text row -> `cols` floats; too long / too short rows throw (matrix.hpp:146-153).
-    static void parse_row(const std::string& line, dsize_t y, dsize_t cols, float* dst) {
+    static void parse_row(const std::string& line, dsize_t y, dsize_t cols, T* dst) {
         const char* p = line.c_str();
         dsize_t x = 0;
         while (*p != '\0' && *p != '\r') {
             if (x == cols)
                 throw std::runtime_error("Line " + std::to_string(y) + " is too long, expected " + std::to_string(cols) + " values");
             char* end = nullptr;
-            dst[x] = std::strtof(p, &end);
+            if constexpr (sizeof(T) == sizeof(double)) dst[x] = std::strtod(p, &end); else dst[x] = std::strtof(p, &end);
             if (end == p) throw std::invalid_argument("stof");
             ++x;
             p = end;
@@ -274,5 +280,6 @@ private:
                                      ", got " + std::to_string(x) + " values");
     }
 };
+using matrix_array = basic_matrix_array<float>;
 
 }  // namespace cross

@@ -248,7 +248,7 @@ def test_exit_codes(cross, tmp_path):
     assert run(cross, "run", "--bogus", "cpu_one_to_one", l, rr).returncode == 1
     assert run(cross, "run", "cpu_one_to_one", l).returncode == 1
     assert run(cross, "run", "-b", "Sometimes", "cpu_one_to_one", l, rr).returncode == 1
-    assert run(cross, "run", "-d", "double", "cpu_one_to_one", l, rr).returncode == 1
+    assert run(cross, "run", "-d", "quad", "cpu_one_to_one", l, rr).returncode == 1      # double is accepted here
     r = run(cross, "run", "cpu_one_to_one", l, tmp_path / "missing.csv")
     assert r.returncode == 3 and "data loading step" in r.stderr
     (tmp_path / "badfft.json").write_text(json.dumps({"hadamard_threads_per_block": 0}))
@@ -277,6 +277,64 @@ def test_exit_codes(cross, tmp_path):
                l, rr).returncode == 1
     (tmp_path / "broken.json").write_text("{ \"warps_per_thread_block\": ")
     assert run(cross, "run", "--args_path", tmp_path / "broken.json", "nai_shuffle_one_to_one", l, rr).returncode == 2
+
+
+def test_double_data_type_on_the_cpu(cross, oracle, tmp_path):
+    """`run --data_type double` (refused upstream, main.cpp:431-438): the cpu_* names compute in
+    double from the full-precision text inputs; files, statistics and timing labels as for single."""
+    rng = np.random.default_rng(5)
+    left, right = rng.random((2, 7, 9)), rng.random((6, 7, 9))          # float64 values
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    r = run(cross, "run", "--data_type", "double", "--out", tmp_path / "o.csv", "--validate", "--no_progress",
+            "-b", "Compute", "-m", "0.001", "-t", tmp_path / "t.csv", "cpu_n_to_mn", tmp_path / "l.csv", tmp_path / "r.csv",
+            cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    import scipy.signal
+    got = read_matrices(tmp_path / "o.csv")
+    for t in range(3):
+        for l in range(2):                       # file order: right / result t*n + l belongs to left l
+            want = scipy.signal.correlate2d(left[l], right[t * 2 + l], mode="full")
+            assert np.abs(got[t * 2 + l] - want).max() <= 5.1e-7
+    assert r.stdout.splitlines()[0] == "Max,Mean,Stddev" and float(r.stdout.splitlines()[1].split(",")[0]) < 1e-12
+    assert open(tmp_path / "t.csv").read().splitlines()[0] == "Computation,Computation_iterations"
+    assert run(cross, "run", "--data_type", "half", "cpu_one_to_one", tmp_path / "l.csv", tmp_path / "r.csv").returncode == 1
+    assert run(cross, "run", "--data_type", "double", "fft_orig_one_to_one", tmp_path / "l.csv", tmp_path / "r.csv").returncode == 1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("alg,mode,rows,cols,nl,nr,bench", [
+    ("nai_shuffle_multirow_both_one_to_one", "one_to_one", 33, 20, 1, 1, "Algorithm"),
+    ("nai_shuffle_multirow_both_multimat_right_one_to_many", "one_to_many", 16, 24, 1, 7, "CommonSteps"),
+    ("nai_shuffle_multirow_both_multimat_right_n_to_mn", "n_to_mn", 12, 12, 3, 9, "Compute"),
+    ("nai_orig_n_to_m", "n_to_m", 9, 17, 2, 5, "None"),
+])
+def test_double_data_type_on_the_gpu(cross, tmp_path, alg, mode, rows, cols, nl, nr, bench):
+    """Every direct algorithm name runs its mode in double with --data_type double: result files in
+    the reference's file order equal scipy's float64 correlation, the timing file carries the
+    benchmark type's labels."""
+    import scipy.signal
+    rng = np.random.default_rng(11)
+    left, right = rng.random((nl, rows, cols)), rng.random((nr, rows, cols))
+    write_matrices(tmp_path / "l.csv", left)
+    write_matrices(tmp_path / "r.csv", right)
+    r = run(cross, "run", "-d", "double", "-o", tmp_path / "o.csv", "-v", "-n", "-b", bench, "-m", "0.002",
+            "-t", tmp_path / "t.csv", alg, tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
+    assert r.returncode == 0, r.stderr
+    got = read_matrices(tmp_path / "o.csv")
+    pairs = {"one_to_one": [(0, 0)], "one_to_many": [(0, t) for t in range(nr)],
+             "n_to_mn": [(i % nl, i) for i in range(nr)], "n_to_m": [(l, t) for l in range(nl) for t in range(nr)]}[mode]
+    assert got.shape[0] == len(pairs)
+    for k, (l, t) in enumerate(pairs):
+        want = scipy.signal.correlate2d(left[l], right[t], mode="full")
+        assert np.abs(got[k] - want).max() <= 5.1e-7, (alg, k)
+    assert float(r.stdout.splitlines()[1].split(",")[0]) < 1e-12          # --validate: CPU double recompute
+    if bench != "None":
+        head = open(tmp_path / "t.csv").read().splitlines()[0]
+        assert head == {"Algorithm": "Kernel,Kernel_iterations", "Compute": "Computation,Computation_iterations",
+                        "CommonSteps": "Load,Load_iterations,Prepare,Prepare_iterations,Transfer,Transfer_iterations,"
+                                       "Run,Run_iterations,Finalize,Finalize_iterations,Free,Free_iterations,"
+                                       "Store,Store_iterations"}[bench]
 
 
 # ---- GPU --------------------------------------------------------------------------------------------
