@@ -177,7 +177,9 @@ void finish_plan(TilePlan& p, const PairMap& pm, size_t smem_limit = kSmemLimit)
     p.RMS = round_up(p.RSmax * p.Wp, 32) + 4;
     p.threads = 32 * p.WX * p.WY;
     // the fused row engine exists for 32 padded columns and 1 class per thread
-    if (p.Wp != 32 || p.TY != 1) p.fused = 0;
+    // ... and not for stream-K, whose segments of a few rows do not repay fetching its long straight-line
+    // code (32 x 32 8 x 8: 16.8 against 14.4 us)
+    if (p.Wp != 32 || p.TY != 1 || p.schedule == kSchedStreamK) p.fused = 0;
     // staged left rows and per-warp flush staging (+ the warp queue's counter and the staging barrier)
     const size_t left_bytes = (size_t)p.nstage * p.LS * sizeof(float);
     const size_t rest = (size_t)(p.threads / 32) * kFlushBytesPerWarp + 16;

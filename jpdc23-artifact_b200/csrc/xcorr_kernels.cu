@@ -1,7 +1,7 @@
 // Device code of the direct 2-D cross-correlation library (sm_100a).
 //
 // Three kernel families:
-//   tile_kernel<TY, BOUND, FIXUP>
+//   tile_kernel<TY, BOUND, VARIANT>
 //                          register-tiled circular-class kernel; the fast path for every
 //                          mode.  Stands in for the reference's warp-shuffle families
 //                          (naive_shuffle*.cu): grouped-overlap, multi-matrix-right/both
@@ -49,6 +49,7 @@ namespace xcorr {
 // unwrapped) one at the end of the slice.
 
 enum Pass : int { kPassWrapped = 0, kPassUnwrapped = 1 };
+enum Build : int { kBuildPlain = 0, kBuildFixup = 1, kBuildQueue = 2 };
 
 // 16-byte shared-memory load through a 32-bit shared-window address (one register per
 // address instead of the two a generic pointer takes).
@@ -244,13 +245,13 @@ __device__ __forceinline__ void warp_flush(float* scratch, const float (&vals)[k
     __syncwarp();
 }
 
-// The passes [pass_lo, pass_hi) over the slice's rows for one thread (both, or one of them as a
-// task of its own in the warp-queue schedule).
-template<int TY>
+// Both passes over the slice's rows for one thread, or (ONEPASS, the warp-queue build) the one pass
+// `only_pass` as a task of its own.
+template<int TY, bool ONEPASS>
 __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict__ dst, uint32_t sL_addr,
                                             uint32_t rmat_addr, int r0, int r1, int cy0, int cya, int cx0,
                                             bool lane_live, int combine, float* flush_scratch, int lane,
-                                            int cls_per_block, int pass_lo, int pass_hi) {
+                                            int cls_per_block, int only_pass) {
     const int H = p.H, W = p.W, Hp = p.Hp, Wp = p.Wp;
     const int OW = 2 * W - 1;
     // staged left rows of this segment: circular (all Hp rows) or a window of rows
@@ -261,7 +262,7 @@ __device__ __forceinline__ void tile_passes(const TilePlan& p, float* __restrict
     const int wrap_lo = Hp - ((cy0 & ~(p.SL - 1)) + p.SL * TY - 1);
 
 #pragma unroll 1
-    for (int pass = pass_lo; pass < pass_hi; ++pass) {
+    for (int pass = ONEPASS ? only_pass : 0; pass < (ONEPASS ? only_pass + 1 : 2); ++pass) {
         // wrapped pass: chunks [0, cb) with window R[Wp - cx0 - 16 + 8c ...];
         // unwrapped pass: chunks [cb + 2, NCH) with window R[8(c - cb) - 16 ...]
         const int c_begin = pass == kPassWrapped ? 0 : cb + 2;
@@ -616,13 +617,18 @@ __device__ unsigned long long queue_task_at(unsigned long long units, int NTX, i
 // FIXUP: the build that can write parts of a cut stream-K task to partial images and sum them
 // (combine = kFixup); kept apart because its extra code cost the other plans 1-2 % when it sat
 // in the same kernel.
-template<int TY, int BOUND, bool FIXUP>
+template<int TY, int BOUND, int VARIANT>
 __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
+    // Three builds of the kernel: plain (static and stream-K plans), with the fix-up of cut stream-K
+    // tasks, and the warp queue.  Code of a schedule that sits in the same kernel costs the others a
+    // few percent (instruction fetch, registers held across the row loop): measured on B200.
+    constexpr bool FIXUP = VARIANT == kBuildFixup;
+    constexpr bool QUEUE = VARIANT == kBuildQueue;
     extern __shared__ __align__(16) float smem[];
     // the fused 32-column rows hold two accumulator sets and a whole right row in registers: built for
     // one class per thread (with two, 16-warp blocks spill and 8..12-warp blocks at 168 registers ran
     // 1.5 times slower than the chunked walk: measured on B200, 32 x 32, 32 x 64 pairs)
-    constexpr bool kFused = TY == 1;
+    constexpr bool kFused = TY == 1 && !FIXUP;
     const TilePlan& p = a.p;
     float* sL = smem;
     float* sR = smem + (size_t)p.KL * p.nstage * p.LS;
@@ -638,7 +644,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
     //      tasks of one matrix group, which the block's warps take from a shared counter.
     unsigned long long u, uend;
     int slice = 0;
-    if (p.schedule == kSchedWarpQueue) {
+    if (QUEUE) {
         // p.tasks = matrix groups; the weight units of all tasks cut evenly over the blocks
         if (kFused && p.fused) {                  // whole tiles, all of one length
             const unsigned long long total = (unsigned long long)p.tasks * p.NGY * p.NTX;
@@ -682,11 +688,11 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
 
     while (u < uend) {
         bool stage_ok = true;
-        int r0, r1, bx, by, rg, l, combine, ngroups = 1, nlefts = 1;
+        int r0, r1, bx, by, rg, l, combine, ngroups = 1, nlefts = 1;      // (both stay 1 outside the queue build)
         unsigned long long q_begin = 0, q_end = 0, q_yrow0 = 0;      // this round's tasks (warp queue)
         unsigned task_id = 0, first_block = 0;
         int n_parts = 1, part = 0;
-        if (p.schedule == kSchedWarpQueue) {
+        if (QUEUE) {
             // one round: up to KG consecutive matrix groups (of up to KL left matrices), staged together
             const unsigned t2 = (kFused && p.fused) ? (unsigned)p.NTX : 2u * (unsigned)p.NTX;   // tasks per y row
             q_yrow0 = u / t2;
@@ -726,7 +732,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         }
 
         // y classes the staged left rows must serve: the block's groups, or all in queue mode
-        const int cls_per_block = p.schedule == kSchedWarpQueue ? Hp : p.WY * p.SL * TY;
+        const int cls_per_block = QUEUE ? Hp : p.WY * p.SL * TY;
         const int cya = by * cls_per_block;          // first y class of the block
         int rowbase = r0 + cya;
         if (rowbase >= Hp) rowbase -= Hp;
@@ -738,13 +744,13 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         const int log_ml = 5 - p.logSL;
         auto right_of = [&](int mm, size_t& rmat) -> bool {
             const unsigned gg = (unsigned)rg + (unsigned)(mm >> log_ml);
-            const unsigned lt = ngroups == 1 ? 0u : gg / (unsigned)p.RG;      // one group: no division in the copy loops
+            const unsigned lt = QUEUE ? gg / (unsigned)p.RG : 0u;              // one group outside the queue build
             const unsigned j = (gg - lt * (unsigned)p.RG) * (unsigned)p.ML + (unsigned)(mm & (p.ML - 1));
             rmat = (size_t)(l + lt) * a.pm.right_stride + j;
             return j < a.pm.m;
         };
         const int nstage = min(r1 - r0 + cls_per_block - 1, Hp);   // staged rows per left (== p.nstage in a round)
-        const int nlrows = nlefts * nstage;
+        const int nlrows = QUEUE ? nlefts * nstage : nstage;
         // ---- stage the left rows: staged row i of a slot holds left row (rowbase + i) mod Hp, zeros
         //      where the padded matrix is zero.
         if (bulk) {
@@ -757,7 +763,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 uint32_t bytes = 0;
                 for (int i = lane; i < nlrows + nmat; i += 32) {
                     if (i < nlrows) {
-                        int row = rowbase + i % nstage;
+                        int row = rowbase + (QUEUE ? i % nstage : i);
                         if (row >= Hp) row -= Hp;
                         if (row < H) bytes += row_bytes;
                     } else {
@@ -771,7 +777,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 __syncwarp();
                 for (int i = lane; i < nlrows + nmat; i += 32) {
                     if (i < nlrows) {
-                        const int ls = i / nstage;
+                        const int ls = QUEUE ? i / nstage : 0;
                         int row = rowbase + (i - ls * nstage);
                         if (row >= Hp) row -= Hp;
                         if (row < H)
@@ -787,7 +793,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             // rows and matrices of the zero padding: plain stores, one warp per row / matrix
             const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int i = warp; i < nlrows; i += nthr >> 5) {
-                int row = rowbase + i % nstage;
+                int row = rowbase + (QUEUE ? i % nstage : i);
                 if (row >= Hp) row -= Hp;
                 if (row >= H)
                     for (int x = lane * 4; x < Wp; x += 128) *reinterpret_cast<float4*>(sL + (size_t)i * p.LS + x) = zero4;
@@ -815,7 +821,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             const int total = nlrows * units;
             for (int idx = tid; idx < total; idx += nthr) {
                 const int i = idx / units, c4 = idx - i * units;
-                const int ls = i / nstage;
+                const int ls = QUEUE ? i / nstage : 0;
                 int row = rowbase + (i - ls * nstage);
                 if (row >= Hp) row -= Hp;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -865,7 +871,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         }
         stage_wait();
         }
-        if (p.schedule == kSchedWarpQueue && tid == 0) *queue = 0;
+        if (QUEUE && tid == 0) *queue = 0;
         if (__syncthreads_or(!stage_ok)) {
             if (tid == 0) atomicAdd(&g_stage_timeouts, 1u);
             break;
@@ -876,14 +882,14 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
         const bool fused = kFused && p.fused;
         const unsigned tpy = fused ? (unsigned)p.NTX : 2u * (unsigned)p.NTX;       // queue tasks per y row
         unsigned q_ny = 0, q_nv = 0;
-        if (p.schedule == kSchedWarpQueue) {
+        if (QUEUE) {
             q_ny = (unsigned)((q_end - 1) / tpy - q_yrow0) + 1u;
             q_nv = q_ny * tpy;
         }
         bool first = true;
         while (true) {
-            int tile_x, grp_y, slot = 0, pass_lo = 0, pass_hi = 2, task_l = l, task_rg = rg;
-            if (p.schedule == kSchedWarpQueue) {
+            int tile_x, grp_y, slot = 0, only_pass = 0, task_l = l, task_rg = rg;
+            if (QUEUE) {
                 unsigned v = 0;
                 if (lane == 0) v = (unsigned)atomicAdd(queue, 1);
                 v = __shfl_sync(0xffffffffu, v, 0);
@@ -901,7 +907,7 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                 task_l = (int)(g / (unsigned)p.RG);
                 task_rg = (int)(g - (unsigned)task_l * p.RG);
                 tile_x = (fused || which == 0) ? (int)k : p.NTX - 1 - (int)k;
-                if (!fused) { pass_lo = which == 0 ? (int)kPassUnwrapped : (int)kPassWrapped; pass_hi = pass_lo + 1; }
+                if (!fused) only_pass = which == 0 ? (int)kPassUnwrapped : (int)kPassWrapped;
             } else {
                 tile_x = bx * p.WX + wx;
                 grp_y = by * p.WY + wy;
@@ -912,11 +918,11 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
             const bool lane_live = jright < a.pm.m;
             const int cy0 = grp_y * p.SL * TY + q;   // class t of this lane: cy0 + SL*t
             const size_t out_mat = (size_t)task_l * a.pm.m + jright;
-            const uint32_t sl_task = sL_addr + (uint32_t)((task_l - l) * p.nstage * p.LS) * 4;   // the task's left slot
+            const uint32_t sl_task = QUEUE ? sL_addr + (uint32_t)((task_l - l) * p.nstage * p.LS) * 4 : sL_addr;   // the task's left slot
             float* dst = (combine == kWorkspace ? a.ws + (size_t)slice * a.total_out :
                           (FIXUP && combine == kFixup) ? a.ws + (size_t)part * a.total_out : a.out)
                          + out_mat * (size_t)(2 * W - 1) * (2 * H - 1);
-            const uint32_t rsl = rmat_addr + (uint32_t)(slot * p.ML * p.RMS) * 4;
+            const uint32_t rsl = QUEUE ? rmat_addr + (uint32_t)(slot * p.ML * p.RMS) * 4 : rmat_addr;
             const int comb = (FIXUP && combine == kFixup) ? (int)kStore : combine;
             if constexpr (kFused) {
                 if (fused) {
@@ -925,8 +931,8 @@ __global__ void __launch_bounds__(BOUND, 1) tile_kernel(const TileArgs a) {
                     continue;
                 }
             }
-            tile_passes<TY>(p, dst, sl_task, rsl, r0, r1, cy0, cya, tile_x * kTX, lane_live, comb, flush_scratch, lane,
-                            cls_per_block, pass_lo, pass_hi);
+            tile_passes<TY, QUEUE>(p, dst, sl_task, rsl, r0, r1, cy0, cya, tile_x * kTX, lane_live, comb, flush_scratch, lane,
+                                   cls_per_block, only_pass);
         }
         if (FIXUP && combine == kFixup) {
             // this part is written: count it; whoever counts the task's last part sums them
@@ -1274,19 +1280,20 @@ static cudaError_t allow_smem(K kernel, std::atomic<size_t>* raised, int device,
     return e;
 }
 
-template<int TY, int BOUND, bool FIXUP>
+template<int TY, int BOUND, int VARIANT>
 static cudaError_t launch_tile_instance(const TileArgs& a, int device, cudaStream_t stream) {
     static std::atomic<size_t> raised[kAttrDevices];
-    cudaError_t e = allow_smem(tile_kernel<TY, BOUND, FIXUP>, raised, device, a.p.smem_bytes);
+    cudaError_t e = allow_smem(tile_kernel<TY, BOUND, VARIANT>, raised, device, a.p.smem_bytes);
     if (e != cudaSuccess) return e;
-    tile_kernel<TY, BOUND, FIXUP><<<a.p.grid, a.p.threads, a.p.smem_bytes, stream>>>(a);
+    tile_kernel<TY, BOUND, VARIANT><<<a.p.grid, a.p.threads, a.p.smem_bytes, stream>>>(a);
     return cudaGetLastError();
 }
 
 template<int TY, int BOUND>
 static cudaError_t launch_tile_variant(const TileArgs& a, int device, cudaStream_t stream) {
-    return a.p.combine == kFixup ? launch_tile_instance<TY, BOUND, true>(a, device, stream)
-                                 : launch_tile_instance<TY, BOUND, false>(a, device, stream);
+    if (a.p.schedule == kSchedWarpQueue) return launch_tile_instance<TY, BOUND, kBuildQueue>(a, device, stream);
+    return a.p.combine == kFixup ? launch_tile_instance<TY, BOUND, kBuildFixup>(a, device, stream)
+                                 : launch_tile_instance<TY, BOUND, kBuildPlain>(a, device, stream);
 }
 
 template<int TY>
