@@ -643,7 +643,7 @@ def main():
     ap.add_argument("--grid-max-tflop", type=float, default=40.0)
     ap.add_argument("--only", default="", help="comma-separated subset of C1..C5 (profiling runs; "
                     "the default line always covers all five)")
-    ap.add_argument("--hints", default="", help='JSON {"C3": {"overlap_rows": 4, ...}}: force plan hints of '
+    ap.add_argument("--hints", default="", help='JSON {"C3": {"overlap_rows": 4, ...}} or {"C1": {"kernel": "warp_per_overlap"}}: force plan hints of '
                     "a configuration (profiling and tuning runs; the default line uses automatic plans)")
     args = ap.parse_args()
     if args.only:
@@ -677,7 +677,7 @@ def main():
     warmup = max(3, args.warmup)
     stream = torch.cuda.current_stream().cuda_stream
 
-    forced = {k: xc.make_hints(kernel="tile", **v) for k, v in (json.loads(args.hints) if args.hints else {}).items()}
+    forced = {k: xc.make_hints(**{"kernel": "tile", **v}) for k, v in (json.loads(args.hints) if args.hints else {}).items()}
 
     # ---- resident inputs, outputs, workspaces
     dev = {}
