@@ -1263,7 +1263,32 @@ xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_r
         xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
         if (st != XCORR_OK) return st;
         DeviceInfo dev;
-        if ((st = current_device_info(&dev)) != XCORR_OK) return st;
+        int device = 0;
+        if ((st = current_device_info(&dev, &device)) != XCORR_OK) return st;
+        // The register-tiled kernel wherever a plan fits; XCORR_F64_STRIP=1 keeps the column-strip
+        // kernel (a cross-check with another summation order).
+        const char* strip_env = std::getenv("XCORR_F64_STRIP");        // read per call: tests switch it
+        const bool force_strip = strip_env && strip_env[0] == '1';
+        TilePlan64 tp{};
+        if (!force_strip && plan_tile_f64(pm, (int)rows, (int)cols, dev.sm_count, dev.smem_optin, &tp)) {
+            TileArgs64 ta{};
+            ta.left = d_left; ta.right = d_right; ta.out = d_out; ta.p = tp; ta.pm = pm;
+            ta.vec_ok = cols % 2 == 0 && reinterpret_cast<uintptr_t>(d_left) % 16 == 0 &&
+                        reinterpret_cast<uintptr_t>(d_right) % 16 == 0;
+            cudaStream_t s64 = static_cast<cudaStream_t>(stream);
+            if (tp.S > 1) {
+                const size_t out_bytes = (size_t)pm.n_left * pm.m * (2 * (size_t)rows - 1) * (2 * (size_t)cols - 1) * sizeof(double);
+                XC_CUDA(cudaMemsetAsync(d_out, 0, out_bytes, s64));
+            }
+            XC_CUDA(launch_tile_f64(ta, device, s64));
+            char tbuf[256];
+            std::snprintf(tbuf, sizeof tbuf, "kernel=tile_f64 grid=(%u,1,1) block=(%d,1,1) smem=%zu plan{Hp=%d Wp=%d SL=%d ML=%d "
+                          "WX=%d WY=%d CX=%d CY=%d RG=%d S=%d nstage=%d combine=%s}", tp.grid, tp.threads, tp.smem_bytes, tp.Hp,
+                          tp.Wp, tp.SL, tp.ML, tp.WX, tp.WY, tp.CX, tp.CY, tp.RG, tp.S, tp.nstage, tp.S > 1 ? "atomic" : "store");
+            set_launch_text(tbuf);
+            ++t_launch_count;
+            return XCORR_OK;
+        }
         dim3 g, b;
         XC_CUDA(launch_strip_f64(d_left, d_right, d_out, (int)rows, (int)cols, pm,
                                  (unsigned long long)pm.n_left * pm.m, dev.sm_count, &g, &b,

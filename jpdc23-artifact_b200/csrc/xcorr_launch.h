@@ -30,6 +30,10 @@ cudaError_t tile_stage_timeouts(unsigned* count);
 cudaError_t launch_strip_f64(const double* left, const double* right, double* out, int H, int W, PairMap pm,
                              unsigned long long npairs, int sm_count, dim3* grid_out, dim3* block_out,
                              cudaStream_t stream);
+// Double precision, register-tiled (xcorr_f64_tile.cu).  plan_tile_f64 returns false when no plan fits
+// one SM's shared memory; a plan with S > 1 needs the output zeroed before the launch.
+bool plan_tile_f64(const PairMap& pm, int H, int W, int sm_count, size_t smem_limit, TilePlan64* out);
+cudaError_t launch_tile_f64(const TileArgs64& a, int device, cudaStream_t stream);
 cudaError_t launch_dfma_probe(double* sink, int iters, int blocks, cudaStream_t stream);
 cudaError_t launch_ffma_probe(float* sink, int iters, int blocks, cudaStream_t stream);
 

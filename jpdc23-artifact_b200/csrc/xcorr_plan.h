@@ -101,6 +101,28 @@ struct TileArgs {
 // Default bound of the staging wait: ~4 million polls, a second or so; healthy copies land in microseconds.
 constexpr unsigned kStageWaitLimit = 1u << 22;
 
+// Plan and arguments of the double-precision tile kernel (xcorr_f64_tile.cu): the float plan's
+// fields where they mean the same; 8 x classes and one y class per thread, static blocks, S row slices.
+struct TilePlan64 {
+    int H, W, Hp, Wp;
+    int SL, ML, logSL;
+    int NTX, NCH, NGY;
+    int WX, WY, CX, CY, RG;
+    int S;             // row slices (S > 1: sums added atomically onto the zeroed output)
+    int nstage, LS, RMS;
+    int threads;
+    unsigned grid;
+    size_t smem_bytes;
+};
+struct TileArgs64 {
+    const double* left;
+    const double* right;
+    double* out;
+    TilePlan64 p;
+    PairMap pm;
+    int vec_ok;        // rows may be fetched two doubles at a time
+};
+
 // Arguments of the staged warp-per-overlap kernel: a block owns one x shift, `shifts` consecutive
 // y shifts (one per warp) and up to `rights` right matrices of one left; operands go through
 // shared memory in slabs of `srows` right rows x `scols` columns, two slabs in flight.

@@ -439,6 +439,25 @@ def test_double_precision_against_the_oracle(xc, oracle, mode, rows, cols, nl, n
     assert np.abs(got - want).max() <= F64_TOL * max(np.abs(want).max(), 1e-300)
 
 
+def test_double_precision_kernels_agree(xc, oracle, monkeypatch):
+    """The two double-precision kernels -- register-tiled (the default) and column-strip (kept as the
+    fallback for rows too wide to stage, selectable with XCORR_F64_STRIP=1) -- against the oracle and
+    each other: different summation orders, same definition.  A single larger pair takes the tiled
+    kernel's row slices (sums added atomically)."""
+    for mode, rows, cols, nl, nr in (("one_to_many", 33, 20, 1, 7), ("n_to_m", 16, 24, 3, 5), ("one_to_one", 96, 72, 1, 1)):
+        left, right = seeded_inputs(rows, cols, nl, nr, 909)
+        want = oracle_grouped(oracle, mode, left, right)
+        monkeypatch.delenv("XCORR_F64_STRIP", raising=False)
+        tiled = xc.run_host_f64(mode, left.astype(np.float64), right.astype(np.float64))
+        assert "kernel=tile_f64" in xc.last_launch()
+        monkeypatch.setenv("XCORR_F64_STRIP", "1")
+        strip = xc.run_host_f64(mode, left.astype(np.float64), right.astype(np.float64))
+        assert "kernel=strip_f64" in xc.last_launch()
+        monkeypatch.delenv("XCORR_F64_STRIP", raising=False)
+        for got in (tiled, strip):
+            assert np.abs(got - want).max() <= 1e-13 * np.abs(want).max()
+
+
 def test_double_precision_inputs_against_float64_correlation(xc):
     """Inputs that need all 53 bits, against scipy's float64 correlation (an independent
     statement of the definition); on device pointers, twice: bit-identical (fixed summation order)."""
