@@ -216,8 +216,8 @@ size_t fixup_counters_offset(int pieces, unsigned long long total_out) {
 // Every candidate gets an estimated time; the smallest wins.
 xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints* h, const DeviceInfo& dev,
                               TilePlan* out, size_t max_workspace_bytes) {
-    TilePlan best{}, best_queue{};                 // best_queue: the warp queue as a candidate of the automatic choice
-    double best_time = -1.0, best_queue_time = -1.0;
+    TilePlan best{}, best_queue{}, best_queue_few{};   // best_queue*: the warp queue as a candidate of the automatic choice
+    double best_time = -1.0, best_queue_time = -1.0, best_queue_few_time = -1.0;
     const int want_ty = h ? h->overlap_rows : 0;
     const int want_sl = h ? h->class_lanes : 0;
     if (want_ty < 0 || want_ty > kMaxTY) return fail(XCORR_ERR_INVALID_HINT, "overlap_rows must be 0..4");
@@ -328,6 +328,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
             const double sm_rate = 128.0 * 1.8e9 * 0.8;
             for (const Cand& c : cands) {
                 p.WX = c.WX; p.WY = c.WY; p.S = c.S; p.schedule = c.sched;
+                p.fused = want_fused != 2;                 // (finish_plan clears it where the fused rows do not apply)
                 finish_plan(p, pm, dev.smem_optin);
                 if (p.smem_bytes > dev.smem_optin) continue;
                 if (c.sched == kSchedStatic && want_combine == XCORR_COMBINE_WORKSPACE &&
@@ -367,6 +368,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 int comb;
                 int sk_parts = 0;
                 unsigned grid;
+                bool queue_few_tasks = false;
                 if (c.sched == kSchedWarpQueue) {
                     // pass tasks (one pass of one warp tile, all rows) of unequal lengths, cut evenly by
                     // weight over one resident wave of blocks and taken longest first by the warps
@@ -389,7 +391,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                                           ((macs_block * narrow + rounds * 4.0 * 0.4 * longest) / rate + rounds * t_stage);
                     const double t_serial = std::ceil(ptasks / G / warps_blk) * H * p.Wp * TY * kTX / 1.8e9;
                     t = std::max(t_rate, t_serial);
-                    if (queue_auto && ptasks / G < 2.0 * warps_blk) continue;   // about one task per warp: the tail decides
+                    if (queue_auto && ptasks / G < 1.25 * warps_blk) continue;  // about one task per warp: the tail decides
+                    queue_few_tasks = ptasks / G < 2.0 * warps_blk;
                     comb = kStore;
                 } else if (c.sched == kSchedStreamK) {
                     const double units = tasks * H;
@@ -487,8 +490,10 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     std::fprintf(stderr, "plan TY=%d SL=%d WX=%d WY=%d S=%d sched=%d comb=%d grid=%u t=%.2f us\n", TY, SL, c.WX,
                                  c.WY, c.S, c.sched, comb, grid, t * 1e6);
                 const bool auto_queue_cand = queue_auto && c.sched == kSchedWarpQueue;
-                TilePlan& slot = auto_queue_cand ? best_queue : best;
-                double& slot_time = auto_queue_cand ? best_queue_time : best_time;
+                // (queue candidates with fewer than two tasks per warp only compete against stream-K)
+                const bool few = auto_queue_cand && queue_few_tasks;
+                TilePlan& slot = few ? best_queue_few : auto_queue_cand ? best_queue : best;
+                double& slot_time = few ? best_queue_few_time : auto_queue_cand ? best_queue_time : best_time;
                 if (slot_time < 0.0 || t < slot_time * 0.9999) {
                     slot_time = t;
                     slot = p;
@@ -504,7 +509,15 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
     // its last wave of blocks empty (128 equal blocks on 148 SMs): that is the loss the queue removes.
     // Against stream-K, which is balanced by construction, it measured slower on the dominant benchmark
     // shape (48 x 48 16 x 128: 460 against 447 us) although the estimates are level.
-    if (best_queue_time >= 0.0) {
+    if (best_time >= 0.0 && best.schedule == kSchedStreamK) {
+        // ... except where stream-K's ranges are a few rows each (a block re-stages and flushes for every
+        // one): the queue is taken if its estimate is 8 % better (48 x 48 2 x 128: 74 against 84 us,
+        // 4 x 128: 131 against 148 us), also with between one and two tasks per warp
+        if (best_queue_few_time >= 0.0 && (best_queue_time < 0.0 || best_queue_few_time < best_queue_time)) {
+            best_queue = best_queue_few; best_queue_time = best_queue_few_time;
+        }
+        if (best_queue_time >= 0.0 && best_queue_time < 0.92 * best_time) { best = best_queue; best_time = best_queue_time; }
+    } else if (best_queue_time >= 0.0) {
         bool take = best_time < 0.0;
         if (!take && best.schedule == kSchedStatic) {
             const double blocks = (double)best.tasks * best.S;
@@ -512,6 +525,8 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
             take = wave_fill < 0.9 && best_queue_time < best_time;
         }
         if (take) { best = best_queue; best_time = best_queue_time; }
+    } else if (best_time < 0.0 && best_queue_few_time >= 0.0) {
+        best = best_queue_few; best_time = best_queue_few_time;
     }
     if (best_time < 0.0)
         return fail(XCORR_ERR_UNSUPPORTED, "no tile plan fits in shared memory for this shape / these hints");

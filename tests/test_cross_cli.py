@@ -318,7 +318,7 @@ def test_double_data_type_on_the_gpu(cross, tmp_path, alg, mode, rows, cols, nl,
     left, right = rng.random((nl, rows, cols)), rng.random((nr, rows, cols))
     write_matrices(tmp_path / "l.csv", left)
     write_matrices(tmp_path / "r.csv", right)
-    r = run(cross, "run", "-d", "double", "-o", tmp_path / "o.csv", "-v", "-n", "-b", bench, "-m", "0.002",
+    r = run(cross, "run", "-d", "double", "-o", tmp_path / "o.csv", "-v", "-p", "-b", bench, "-m", "0.002",
             "-t", tmp_path / "t.csv", alg, tmp_path / "l.csv", tmp_path / "r.csv", cwd=tmp_path)
     assert r.returncode == 0, r.stderr
     got = read_matrices(tmp_path / "o.csv")
