@@ -310,8 +310,15 @@ XCORR_API xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, con
  * The reference parses `--data_type double` and refuses it (main.cpp:433-434); its <double>
  * kernel instantiations are commented out (e.g. naive_shuffle.cu:545-552).  Same modes,
  * layouts (n_to_mn GROUPED) and definition as the float entry points; no workspace, no
- * hints: one kernel (a warp per 8 x 32 block of one result matrix, double accumulation in
- * a fixed order: results are bit-reproducible).  Asynchronous on `stream`. */
+ * hints.  The kernel is register-tiled like the float one (circular classes in both directions,
+ * operands staged in shared memory; 8 x classes of one y class per thread, double accumulation).
+ * Plans that keep every result in one block write with plain stores in a fixed order:
+ * bit-reproducible.  Where rows are cut into slices (few pairs, e.g. one 256 x 256 pair: every
+ * SM gets a slice) the library zeroes `d_out` and the slices add atomically: two slices commute,
+ * more make the last bits vary from run to run.  xcorr_last_launch_string() names the plan.
+ * Rows too wide to stage take a second kernel (a warp per 8 x 32 block of a result, operands
+ * through L1), which the environment variable XCORR_F64_STRIP=1 selects for every call.
+ * Asynchronous on `stream`. */
 XCORR_API xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_right, double* d_out,
                                      uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
                                      void* stream);
