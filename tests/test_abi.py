@@ -160,6 +160,35 @@ def test_plans_exist_and_fit_for_a_sweep_of_shapes(xc):
             assert (ws > 0) == (comb in ("workspace", "fixup")), text
 
 
+def test_planner_choices_for_the_benchmark_shapes(xc):
+    """The per-shape choices the measurements led to, checked without a device (a B200 is assumed):
+    the warp queue against a static plan whose last wave of blocks is under-filled (64x64 1x512:
+    128 equal blocks on 148 SMs), stream-K kept where it is balanced already (48x48 16x128), fused
+    rows only for 17..32 columns with one class per thread and never under stream-K, the staged
+    warp-per-overlap kernel for a handful of overlaps, hints that override all of it."""
+    c3 = xc.describe_plan("one_to_many", 64, 64, 1, 512)
+    assert "schedule=warp-queue" in c3 and "grid=(148,1,1)" in c3 and "combine=store" in c3 and "fused=0" in c3
+    c5 = xc.describe_plan("n_to_mn", 48, 48, 16, 2048)
+    assert "schedule=stream-k" in c5 and "fused=0" in c5
+    small = xc.describe_plan("n_to_m", 32, 32, 4, 64)
+    assert "schedule=static" in small and "fused=1" in small and "tile<TY=1>" in small
+    assert "fused=0" in xc.describe_plan("n_to_m", 32, 32, 4, 64, xc.make_hints(kernel="tile", fused_rows=2))
+    assert "fused=0" in xc.describe_plan("n_to_m", 32, 32, 4, 64, xc.make_hints(kernel="tile", schedule=2, overlap_rows=1))
+    assert "fused=0" in xc.describe_plan("n_to_m", 32, 32, 4, 64, xc.make_hints(kernel="tile", overlap_rows=2))
+    assert "fused=0" in xc.describe_plan("n_to_m", 48, 48, 4, 64, xc.make_hints(kernel="tile", overlap_rows=1))
+    assert xc.describe_plan("one_to_one", 16, 16, 1, 1) == "kernel=warp_staged"
+    assert "kernel=tile" in xc.describe_plan("one_to_one", 16, 16, 1, 1, xc.make_hints(reproducible=1, kernel="tile"))
+    forced = xc.describe_plan("n_to_mn", 48, 48, 16, 2048, xc.make_hints(kernel="tile", schedule=3))
+    assert "schedule=warp-queue" in forced and "KG=" in forced and "KL=" in forced
+    # a queue round stages several matrix groups, and the rows of several left matrices where the groups
+    # of one left are few
+    import re
+    q = xc.describe_plan("n_to_m", 32, 32, 32, 64, xc.make_hints(kernel="tile", schedule=3, overlap_rows=1, class_lanes=2,
+                                                                 warps_x=12, warps_y=1))
+    kg, kl = (int(v) for v in re.search(r"KG=(\d+) KL=(\d+)", q).groups())
+    assert kg >= 2 and kl == 2 and "fused=1" in q
+
+
 def test_header_is_plain_c(xc, tmp_path):
     """include/xcorr.h compiles as C99 with warnings on, and a C program links against the
     library and calls a host-only entry point: the boundary is a C ABI, not a C++ one."""
