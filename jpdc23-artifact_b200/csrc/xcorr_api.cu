@@ -386,7 +386,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const double longest = 32.0 * H * TY * kTX * (p.fused ? (double)p.Wp : 8.0 * (p.NCH - 1));
                     const double rounds = std::ceil((groups / G + 1.0) / p.KG);
                     // (the tile's own two chunks run as triangles with reloaded windows: dearer on narrow rows)
-                    const double narrow = p.fused ? 1.05 : 1.0 + 0.5 / ((double)p.NTX * p.NTX);
+                    const double narrow = p.fused ? 1.15 : 1.0 + 0.5 / ((double)p.NTX * p.NTX);
                     const double t_rate = std::ceil(G / dev.sm_count) *
                                           ((macs_block * narrow + rounds * 4.0 * 0.4 * longest) / rate + rounds * t_stage);
                     const double t_serial = std::ceil(ptasks / G / warps_blk) * H * p.Wp * TY * kTX / 1.8e9;

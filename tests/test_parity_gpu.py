@@ -435,7 +435,7 @@ def test_double_precision_against_the_oracle(xc, oracle, mode, rows, cols, nl, n
     want = oracle_grouped(oracle, mode, left, right)
     got = xc.run_host_f64(mode, left.astype(np.float64), right.astype(np.float64))
     assert got.dtype == np.float64 and got.shape == want.shape
-    assert xc.last_launch().startswith("kernel=strip_f64")
+    assert xc.last_launch().startswith("kernel=tile_f64")
     assert np.abs(got - want).max() <= F64_TOL * max(np.abs(want).max(), 1e-300)
 
 
