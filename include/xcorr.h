@@ -315,7 +315,9 @@ XCORR_API xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, con
  * Plans that keep every result in one block write with plain stores in a fixed order:
  * bit-reproducible.  Where rows are cut into slices (few pairs, e.g. one 256 x 256 pair: every
  * SM gets a slice) the library zeroes `d_out` and the slices add atomically: two slices commute,
- * more make the last bits vary from run to run.  xcorr_last_launch_string() names the plan.
+ * more make the last bits vary from run to run; the environment variable XCORR_REPRODUCIBLE=1
+ * keeps to at most two slices (and to the second kernel where that does not fit), at the price
+ * of idle SMs on single large pairs.  xcorr_last_launch_string() names the plan.
  * Rows too wide to stage take a second kernel (a warp per 8 x 32 block of a result, operands
  * through L1), which the environment variable XCORR_F64_STRIP=1 selects for every call.
  * Asynchronous on `stream`. */

@@ -1285,7 +1285,9 @@ xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_r
         const char* strip_env = std::getenv("XCORR_F64_STRIP");        // read per call: tests switch it
         const bool force_strip = strip_env && strip_env[0] == '1';
         TilePlan64 tp{};
-        if (!force_strip && plan_tile_f64(pm, (int)rows, (int)cols, dev.sm_count, dev.smem_optin, &tp)) {
+        const char* rep_env = std::getenv("XCORR_REPRODUCIBLE");
+        const bool reproducible = rep_env && rep_env[0] == '1';
+        if (!force_strip && plan_tile_f64(pm, (int)rows, (int)cols, dev.sm_count, dev.smem_optin, reproducible, &tp)) {
             TileArgs64 ta{};
             ta.left = d_left; ta.right = d_right; ta.out = d_out; ta.p = tp; ta.pm = pm;
             ta.vec_ok = cols % 2 == 0 && reinterpret_cast<uintptr_t>(d_left) % 16 == 0 &&

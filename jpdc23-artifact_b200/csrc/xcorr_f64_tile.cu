@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(512, 1) tile_f64_kernel(const TileArgs64 a) {
 // Plan: lanes over y classes so that the padding of the rows stays small and the group of right
 // matrices is not larger than the matrices there are; blocks of up to 16 warps; as many row slices
 // as it takes to fit one SM's shared memory and to give every SM a block.
-bool plan_tile_f64(const PairMap& pm, int H, int W, int sm_count, size_t smem_limit, TilePlan64* out) {
+bool plan_tile_f64(const PairMap& pm, int H, int W, int sm_count, size_t smem_limit, bool reproducible, TilePlan64* out) {
     TilePlan64 best{};
     double best_cost = -1.0;
     for (int SL = 1; SL <= 32; SL *= 2) {
@@ -230,8 +230,8 @@ bool plan_tile_f64(const PairMap& pm, int H, int W, int sm_count, size_t smem_li
             const double tasks = (double)pm.n_left * p.RG * p.CX * p.CY;
             if (tasks > 2.0e9) continue;
             p.LS = p.Wp + 2;
-            for (int S = 1; S <= H; S = S < 8 ? S + 1 : S + S / 4) {
-                p.S = S;
+            for (int S = 1; S <= (reproducible ? std::min(H, 2) : H); S = S < 8 ? S + 1 : S + S / 4) {
+                p.S = S;                 // (two slices commute: still bit-reproducible; more do not)
                 const int RS = (H + S - 1) / S;
                 p.nstage = std::min(RS + WY * SL - 1, p.Hp);
                 p.RMS = RS * p.Wp + 2;

@@ -1012,7 +1012,7 @@ __global__ void overlap_wise_kernel(const float* __restrict__ left, const float*
 }
 
 // ------------------------------------------------------------------------------------------
-// warp-per-overlap: lanes stride the columns of the overlap, rows in sequence, butterfly sum
+// warp-per-overlap: lanes over columns x rows of the overlap, butterfly sum
 // ------------------------------------------------------------------------------------------
 // Row split (naive_warp_per_shift.cu:100-189 with row_distribution.cuh): with rows_per_warp > 0
 // the rows of an overlap are shared by several warps ("workers"), each taking
@@ -1081,11 +1081,29 @@ __global__ void warp_per_overlap_kernel(const float* __restrict__ left, const fl
         const unsigned long long l = pair / pm.m, j = pair % pm.m;
         const float* L = left + l * (size_t)H * W;
         const float* R = right + (l * pm.right_stride + j) * (size_t)H * W;
+        // Lanes as lc columns x 32 / lc rows of the overlap, lc the power of two that covers its width:
+        // narrow overlaps keep every lane busy (the reference spreads the overlap's elements over the
+        // lanes with a division per element, naive_warp_per_shift.cu:69-70).  Four rows per trip with
+        // all eight loads issued before the first multiply-add: for a pair of 16 x 16 the whole sum
+        // is two round trips to L2.
+        int lc = 32;
+        while (lc > 1 && (lc >> 1) >= x1 - x0) lc >>= 1;
+        const int lrn = 32 / lc;
+        const int c0 = x0 + (lane & (lc - 1));
+        const float* lbase = L + (size_t)(y0 + lane / lc) * W;
+        const float* rbase = R + (size_t)(y0 + lane / lc - sy) * W - sx;
+        const size_t rstep = (size_t)lrn * W;
         float sum = 0.f;
-        for (int yl = y0; yl < y1; ++yl) {
-            const float* lrow = L + (size_t)yl * W;
-            const float* rrow = R + (size_t)(yl - sy) * W - sx;
-            for (int xl = x0 + lane; xl < x1; xl += 32) sum = fmaf(__ldg(rrow + xl), __ldg(lrow + xl), sum);
+        for (int xl = c0; xl < x1; xl += lc) {
+            const float* lp = lbase + xl;
+            const float* rp = rbase + xl;
+            int yl = y0 + lane / lc;
+            for (; yl + 3 * lrn < y1; yl += 4 * lrn, lp += 4 * rstep, rp += 4 * rstep) {
+                const float l0 = __ldg(lp), l1 = __ldg(lp + rstep), l2 = __ldg(lp + 2 * rstep), l3 = __ldg(lp + 3 * rstep);
+                const float r0 = __ldg(rp), r1 = __ldg(rp + rstep), r2 = __ldg(rp + 2 * rstep), r3 = __ldg(rp + 3 * rstep);
+                sum = fmaf(r0, l0, sum); sum = fmaf(r1, l1, sum); sum = fmaf(r2, l2, sum); sum = fmaf(r3, l3, sum);
+            }
+            for (; yl < y1; yl += lrn, lp += rstep, rp += rstep) sum = fmaf(__ldg(rp), __ldg(lp), sum);
         }
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);

@@ -31,8 +31,9 @@ cudaError_t launch_strip_f64(const double* left, const double* right, double* ou
                              unsigned long long npairs, int sm_count, dim3* grid_out, dim3* block_out,
                              cudaStream_t stream);
 // Double precision, register-tiled (xcorr_f64_tile.cu).  plan_tile_f64 returns false when no plan fits
-// one SM's shared memory; a plan with S > 1 needs the output zeroed before the launch.
-bool plan_tile_f64(const PairMap& pm, int H, int W, int sm_count, size_t smem_limit, TilePlan64* out);
+// one SM's shared memory; a plan with S > 1 needs the output zeroed before the launch.  `reproducible`
+// keeps to plans whose results are bit-identical from run to run (at most two row slices).
+bool plan_tile_f64(const PairMap& pm, int H, int W, int sm_count, size_t smem_limit, bool reproducible, TilePlan64* out);
 cudaError_t launch_tile_f64(const TileArgs64& a, int device, cudaStream_t stream);
 cudaError_t launch_dfma_probe(double* sink, int iters, int blocks, cudaStream_t stream);
 cudaError_t launch_ffma_probe(float* sink, int iters, int blocks, cudaStream_t stream);
