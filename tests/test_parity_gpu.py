@@ -828,7 +828,7 @@ def test_reproducible_hint_gives_bit_identical_runs(xc, oracle, mode, rows, cols
     a = gpu_run(xc, mode, left, right, h)
     plan = xc.last_launch()
     assert ("combine=store" in plan or "combine=workspace" in plan or "combine=fixup" in plan or
-            "schedule=stream-k" in plan or "warp_staged" in plan)
+            "schedule=stream-k" in plan or "warp_per_overlap" in plan)
     for _ in range(3):
         assert np.array_equal(a, gpu_run(xc, mode, left, right, h)), plan
     assert rel_err(a, oracle_grouped(oracle, mode, left, right)) <= REL_TOL
