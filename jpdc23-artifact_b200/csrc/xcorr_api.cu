@@ -27,11 +27,12 @@ using namespace xcorr;
 // the plan); the text is made when somebody asks for it -- formatting a plan costs about as much
 // host time as enqueuing the kernel of a small input.
 struct LaunchNote {
-    enum Kind { kText, kTile, kStaged } kind = kText;
+    enum Kind { kText, kTile, kStaged, kWarp } kind = kText;
     TilePlan plan{};
     StagedArgs staged{};
     dim3 grid;
     size_t smem = 0;
+    int block = 0, split = 0, rows_per_warp = 0;   // kWarp
 };
 thread_local LaunchNote t_note;
 thread_local std::string t_last_launch = "no kernel launched yet";
@@ -591,16 +592,20 @@ int pick_kernel(const xcorr_hints* h) {
     return k == XCORR_KERNEL_AUTO ? XCORR_KERNEL_TILE : k;
 }
 
-// The automatic choice for a handful of overlaps (one 16 x 16 pair has 961, one 24 x 24 pair
-// 2209): one warp per overlap straight from global memory, lanes over columns x rows with four
-// rows of loads in flight -- the latency kernel.  Measured as CUDA-graph replays it takes 3.0 us
-// at 16 x 16 and 4.4 us at 24 x 24, where the staged variant takes 3.3 us and the tile kernel
-// 6.2 us.  Not for callers who asked for specific plans.
+// The automatic choice for a handful of small overlaps (one 16 x 16 pair has 961, one 32 x 32
+// pair 3969): one warp per overlap straight from global memory, lanes over columns x rows with
+// eight rows of loads in flight -- the latency kernel.  As CUDA-graph replays it takes 2.2 us at
+// 16 x 16, 3.1 us at 24 x 24 and 3.7 us at 32 x 32 (the tile kernel: 10.2, 6.2 and 7.2 us), 4.8 us
+// for eight 16 x 16 pairs (tile: 7.8 us); past 32 rows or columns an overlap takes several
+// dependent trips to L2 and the tile kernel wins (40 x 40: 6.9 against 7.2 us, 48 x 48: 11.6
+// against 8.0 us).  Not for callers who asked for specific plans.
+constexpr double kTinyOverlaps = 8000.0;
 bool tiny_auto(const xcorr_hints* h, const PairMap& pm, uint32_t rows, uint32_t cols) {
     if (h && (h->kernel != XCORR_KERNEL_AUTO || h->combine || h->overlap_rows || h->class_lanes || h->warps_x ||
               h->warps_y || h->row_slices || h->schedule || h->block_threads))
         return false;
-    return (double)pm.n_left * pm.m * (2.0 * rows - 1) * (2.0 * cols - 1) <= 2500.0;
+    if (rows > 32 || cols > 32) return false;
+    return (double)pm.n_left * pm.m * (2.0 * rows - 1) * (2.0 * cols - 1) <= kTinyOverlaps;
 }
 
 xcorr_status check_sizes(int32_t mode, uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,
@@ -669,6 +674,12 @@ const std::string& last_launch_text() {
                       "column_groups=%d loads=%s", t_note.grid.x, t_note.grid.y, t_note.grid.z, sa.shifts * 32, t_note.smem,
                       sa.shifts, sa.srows, sa.scols, sa.rights, sa.col_groups, sa.warp_rows ? "warp-per-row" : "strided");
         t_last_launch = buf;
+    } else if (t_note.kind == LaunchNote::kWarp) {
+        char buf[200];
+        std::snprintf(buf, sizeof buf, "kernel=warp_per_overlap grid=(%u,1,1) block=(%d,1,1) smem=0 split=%s rows_per_warp=%d",
+                      t_note.grid.x, t_note.block, t_note.split == XCORR_SPLIT_NONE ? "none" :
+                      t_note.split == XCORR_SPLIT_RECTANGLE ? "rectangle" : "triangle", t_note.rows_per_warp);
+        t_last_launch = buf;
     }
     t_note.kind = LaunchNote::kText;
     return t_last_launch;
@@ -692,7 +703,8 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
 
     const bool tiny = tiny_auto(hints, pm, rows, cols);
     const int kernel = tiny ? (int)XCORR_KERNEL_WARP_PER_OVERLAP : pick_kernel(hints);
-    const int bt = hints && hints->block_threads ? hints->block_threads : 256;
+    // four-warp blocks once the tiny path has more than a wave of eight-warp ones' worth of overlaps
+    const int bt = hints && hints->block_threads ? hints->block_threads : tiny && total_out > 2000 ? 128 : 256;
     if (bt < 32 || bt > 1024 || bt % 32 != 0)
         return fail(XCORR_ERR_INVALID_HINT, "block_threads must be a multiple of 32 in 32..1024");
     char buf[320];
@@ -714,9 +726,7 @@ xcorr_status run_device(int32_t mode, const float* d_left, const float* d_right,
         // parts of an overlap are added atomically: the output starts at zero (one_to_one.hpp:503)
         if (split != XCORR_SPLIT_NONE) XC_CUDA(cudaMemsetAsync(d_out, 0, total_out * sizeof(float), stream));
         XC_CUDA(launch_warp_per_overlap(d_left, d_right, d_out, H, W, pm, npairs, bt, rpw, split, dev.sm_count, &g, &b, stream));
-        std::snprintf(buf, sizeof buf, "kernel=warp_per_overlap grid=(%u,1,1) block=(%u,1,1) smem=0 split=%s rows_per_warp=%d",
-                      g.x, b.x, split == XCORR_SPLIT_NONE ? "none" : split == XCORR_SPLIT_RECTANGLE ? "rectangle" : "triangle", rpw);
-        set_launch_text(buf);
+        t_note.kind = LaunchNote::kWarp; t_note.grid = g; t_note.block = (int)b.x; t_note.split = split; t_note.rows_per_warp = rpw;
         ++t_launch_count;
         return XCORR_OK;
     }

@@ -1035,6 +1035,69 @@ __device__ __forceinline__ unsigned long long split_workers_before(unsigned y, u
     return split_workers_upper(H, r) + split_workers_upper(H - 1, r) - split_workers_upper(2 * H - 1 - y, r);
 }
 
+// The sum of one overlap (columns [x0, x1), rows [y0, y1) of the left matrix against the right
+// one shifted by (sx, sy)) by one warp, returned in every lane.  Lanes as lc columns x 32 / lc
+// rows, lc the power of two that covers the overlap's width: narrow overlaps keep every lane
+// busy (the reference spreads the overlap's elements over the lanes with a division per
+// element, naive_warp_per_shift.cu:69-70).  Eight rows per trip, rows past the end predicated
+// off, with all sixteen loads issued before the first multiply-add: for a pair of 16 x 16 the
+// whole sum is one round trip to L2.
+__device__ __forceinline__ float warp_overlap_sum(const float* __restrict__ L, const float* __restrict__ R, int W,
+                                                  int sx, int sy, int x0, int x1, int y0, int y1, int lane) {
+    int lc = 32;
+    while (lc > 1 && (lc >> 1) >= x1 - x0) lc >>= 1;
+    const int lrn = 32 / lc;
+    const int c0 = x0 + (lane & (lc - 1));
+    const int yfirst = y0 + lane / lc;
+    const float* lbase = L + (size_t)yfirst * W;
+    const float* rbase = R + (ptrdiff_t)(yfirst - sy) * W - sx;
+    const size_t rstep = (size_t)lrn * W;
+    float sum = 0.f;
+    for (int xl = c0; xl < x1; xl += lc) {
+        const float* lp = lbase + xl;
+        const float* rp = rbase + xl;
+        for (int yl = yfirst; yl < y1; yl += 8 * lrn, lp += 8 * rstep, rp += 8 * rstep) {
+            float lv[8], rv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const bool live = yl + i * lrn < y1;
+                lv[i] = live ? __ldg(lp + i * rstep) : 0.f;
+                rv[i] = live ? __ldg(rp + i * rstep) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum = fmaf(rv[i], lv[i], sum);
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    return sum;
+}
+
+// The unsplit form with 32-bit task arithmetic: what a handful of overlaps runs on, where the
+// 64-bit divisions of the general kernel below are a visible part of the few microseconds.
+__global__ void __launch_bounds__(1024) warp_per_overlap_direct_kernel(const float* __restrict__ left,
+                                                                       const float* __restrict__ right,
+                                                                       float* __restrict__ out, int H, int W,
+                                                                       PairMap pm, unsigned ntasks) {
+    const unsigned OW = 2u * W - 1, OH = 2u * H - 1, OE = OW * OH;
+    const int lane = threadIdx.x & 31;
+    const unsigned warps_per_grid = gridDim.x * (blockDim.x >> 5);
+    for (unsigned task = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); task < ntasks; task += warps_per_grid) {
+        const unsigned pair = ntasks == OE ? 0u : task / OE;
+        const unsigned oi = task - pair * OE;
+        const unsigned oyu = oi / OW;
+        const int oy = (int)oyu, ox = (int)(oi - oyu * OW);
+        const int sx = ox - (W - 1), sy = oy - (H - 1);
+        const int x0 = max(sx, 0), x1 = min(W + sx, W);
+        const int y0 = max(sy, 0), y1 = min(H + sy, H);
+        const unsigned l = pm.m == 1 ? pair : pair / pm.m, j = pair - l * pm.m;
+        const float* L = left + (size_t)l * H * W;
+        const float* R = right + ((size_t)l * pm.right_stride + j) * (size_t)H * W;
+        const float sum = warp_overlap_sum(L, R, W, sx, sy, x0, x1, y0, y1, lane);
+        if (lane == 0) out[(size_t)pair * OE + oi] = sum;
+    }
+}
+
 __global__ void warp_per_overlap_kernel(const float* __restrict__ left, const float* __restrict__ right,
                                         float* __restrict__ out, int H, int W, PairMap pm,
                                         unsigned long long ntasks, int rows_per_warp, int split) {
@@ -1081,32 +1144,7 @@ __global__ void warp_per_overlap_kernel(const float* __restrict__ left, const fl
         const unsigned long long l = pair / pm.m, j = pair % pm.m;
         const float* L = left + l * (size_t)H * W;
         const float* R = right + (l * pm.right_stride + j) * (size_t)H * W;
-        // Lanes as lc columns x 32 / lc rows of the overlap, lc the power of two that covers its width:
-        // narrow overlaps keep every lane busy (the reference spreads the overlap's elements over the
-        // lanes with a division per element, naive_warp_per_shift.cu:69-70).  Four rows per trip with
-        // all eight loads issued before the first multiply-add: for a pair of 16 x 16 the whole sum
-        // is two round trips to L2.
-        int lc = 32;
-        while (lc > 1 && (lc >> 1) >= x1 - x0) lc >>= 1;
-        const int lrn = 32 / lc;
-        const int c0 = x0 + (lane & (lc - 1));
-        const float* lbase = L + (size_t)(y0 + lane / lc) * W;
-        const float* rbase = R + (size_t)(y0 + lane / lc - sy) * W - sx;
-        const size_t rstep = (size_t)lrn * W;
-        float sum = 0.f;
-        for (int xl = c0; xl < x1; xl += lc) {
-            const float* lp = lbase + xl;
-            const float* rp = rbase + xl;
-            int yl = y0 + lane / lc;
-            for (; yl + 3 * lrn < y1; yl += 4 * lrn, lp += 4 * rstep, rp += 4 * rstep) {
-                const float l0 = __ldg(lp), l1 = __ldg(lp + rstep), l2 = __ldg(lp + 2 * rstep), l3 = __ldg(lp + 3 * rstep);
-                const float r0 = __ldg(rp), r1 = __ldg(rp + rstep), r2 = __ldg(rp + 2 * rstep), r3 = __ldg(rp + 3 * rstep);
-                sum = fmaf(r0, l0, sum); sum = fmaf(r1, l1, sum); sum = fmaf(r2, l2, sum); sum = fmaf(r3, l3, sum);
-            }
-            for (; yl < y1; yl += lrn, lp += rstep, rp += rstep) sum = fmaf(__ldg(rp), __ldg(lp), sum);
-        }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+        const float sum = warp_overlap_sum(L, R, W, sx, sy, x0, x1, y0, y1, lane);
         if (lane == 0) {
             float* dst = out + pair * OE + (size_t)oy * OW + ox;
             if (split != kSplitNone) atomicAdd(dst, sum); else *dst = sum;
@@ -1380,7 +1418,10 @@ cudaError_t launch_warp_per_overlap(const float* left, const float* right, float
     const unsigned long long cap = (unsigned long long)sm_count * 64;
     if (blocks > cap) blocks = cap;
     dim3 grid((unsigned)blocks), block(wpb * 32);
-    warp_per_overlap_kernel<<<grid, block, 0, stream>>>(left, right, out, H, W, pm, ntasks, rows_per_warp, split);
+    if (split == kSplitNone && ntasks < (1ull << 31) && npairs * pm.right_stride < (1ull << 31))
+        warp_per_overlap_direct_kernel<<<grid, block, 0, stream>>>(left, right, out, H, W, pm, (unsigned)ntasks);
+    else
+        warp_per_overlap_kernel<<<grid, block, 0, stream>>>(left, right, out, H, W, pm, ntasks, rows_per_warp, split);
     *grid_out = grid;
     *block_out = block;
     return cudaGetLastError();

@@ -296,6 +296,8 @@ class ReferenceWarpPerShift:
         u32, vp, i = C.c_uint32, C.c_void_p, C.c_int
         self.lib.refcuda_warp_per_shift.argtypes = [vp, vp, vp, u32, u32, u32]
         self.lib.refcuda_warp_per_shift.restype = i
+        self.lib.refcuda_warp_per_shift_graph_us.argtypes = [vp, vp, vp, u32, u32, u32, u32, u32]
+        self.lib.refcuda_warp_per_shift_graph_us.restype = C.c_double
 
     @staticmethod
     def available(path: str = REFCUDA_WPS_SO) -> bool:
@@ -305,3 +307,10 @@ class ReferenceWarpPerShift:
         rc = self.lib.refcuda_warp_per_shift(d_left, d_right, d_out, rows, cols, shifts_per_block)
         if rc != 0:
             raise RuntimeError(f"reference launcher warp_per_shift rejected its arguments (code {rc})")
+
+    def graph_us(self, d_left, d_right, d_out, rows, cols, shifts_per_block=16, launches=20, replays=10):
+        """Microseconds of device time per launch of the reference kernel: ``launches`` calls
+        recorded into a CUDA graph on the calling thread's default stream, replayed ``replays``
+        times between two events.  Negative when the capture failed."""
+        return float(self.lib.refcuda_warp_per_shift_graph_us(d_left, d_right, d_out, rows, cols, shifts_per_block,
+                                                              launches, replays))
