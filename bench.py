@@ -556,6 +556,8 @@ def run_grid(args):
                              reference_vs_direct=float((out - direct).abs().max() / direct.abs().max()))
                 if mode == "one_to_one" and wps is not None and r * c <= 32 * 32:
                     entry["reference_graph_us"] = wps.graph_us(L, R, O, r, c, 16)
+                    if entry.get("direct_graph_us") and entry["reference_graph_us"] > 0:
+                        entry["speedup_graph"] = entry["reference_graph_us"] / entry["direct_graph_us"]
             rows_out.append(entry)
             del left, right, out, direct, ws
             torch.cuda.empty_cache()
