@@ -74,13 +74,14 @@ typedef enum xcorr_kernel {
     XCORR_KERNEL_AUTO = 0,          /* per-shape selection */
     XCORR_KERNEL_TILE = 1,          /* register-tiled circular-class kernel (the fast path) */
     XCORR_KERNEL_OVERLAP_WISE = 2,  /* one thread per overlap -- run_cross_corr_naive_original, naive_original.cu:131-161 */
-    XCORR_KERNEL_WARP_PER_OVERLAP = 3, /* one warp per overlap -- run_ccn_warp_per_shift, naive_warp_per_shift.cu:308-335 */
+    XCORR_KERNEL_WARP_PER_OVERLAP = 3, /* one warp per overlap -- run_ccn_warp_per_shift, naive_warp_per_shift.cu:308-335.
+                                       The automatic choice for a handful of small overlaps (at most 8000 in the
+                                       call, rows and columns up to 32: a 16 x 16 or 32 x 32 pair) */
     XCORR_KERNEL_FFT = 4,           /* the cuFFT path (xcorr_fft_f32 with the normalized layout); needs the
                                        workspace xcorr_workspace_bytes() reports for this hint.  Never chosen
                                        automatically: its rounding differs from the direct path's */
     XCORR_KERNEL_WARP_STAGED = 5    /* one warp per overlap, operands staged through shared memory --
-                                       run_ccn_warp_per_shift_shared_mem, naive_warp_per_shift_shared_mem.cu:392-496.
-                                       The automatic choice for a handful of overlaps (a 16 x 16 pair) */
+                                       run_ccn_warp_per_shift_shared_mem, naive_warp_per_shift_shared_mem.cu:392-496 */
 } xcorr_kernel;
 
 /* How the rows of one overlap are shared by several warps of the plain warp-per-overlap kernel
