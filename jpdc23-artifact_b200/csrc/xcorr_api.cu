@@ -524,6 +524,10 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
             const double blocks = (double)best.tasks * best.S;
             const double wave_fill = blocks / (std::ceil(blocks / dev.sm_count) * dev.sm_count);
             take = wave_fill < 0.9 && best_queue_time < best_time;
+            // ... or, with rows of 32 padded columns and more, where the estimates of the two schedules
+            // track their measured ratio within 2 %, a queue estimated 6 % faster (32 x 32 1 x 4000:
+            // estimated 195 against 210 us, measured 194 against 210 us)
+            if (!take && best.Wp >= 32) take = best_queue_time < 0.94 * best_time;
         }
         if (take) { best = best_queue; best_time = best_queue_time; }
     } else if (best_time < 0.0 && best_queue_few_time >= 0.0) {
