@@ -344,11 +344,15 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 const int by_regs = 65536 / (regs * p.threads);
                 const int blocks_sm = std::max(1, std::min(by_smem, by_regs));
                 const int resident = blocks_sm * (p.threads / 32);
-                const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident);
+                // (the warp queue with one class per thread, half the independent FFMA of two: with 12 resident warps it ran
+                // 3 % behind 16 on 64 x 64 1 x 512 -- 365 against 354 us, three runs each)
+                const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident) *
+                                       (c.sched == kSchedWarpQueue && TY == 1 && resident < 16 ? 0.97 : 1.0);
                 // shared-memory wavefronts per 8-step chunk against its FFMA issue slots
                 const double wavefronts = 2.0 * TY * std::max(1, p.SL / 8) + 6.0 * std::max(1, p.ML / 8);
                 const double smem_util = 4.0 * wavefronts / (8.0 * TY * kTX);
-                const double smem_eff = 1.0 / (1.0 + std::max(0.0, smem_util - 0.4));
+                // (fused rows load a right row once per row and 8 left values: a few wavefronts per 512 FFMA)
+                const double smem_eff = p.fused ? 1.0 : 1.0 / (1.0 + std::max(0.0, smem_util - 0.4));
                 // measured on B200 over the plan space of the benchmark shapes: large blocks
                 // (12..16 warps sharing one staging) and many right matrices per warp run
                 // up to ~15 % faster than small blocks / few matrices per warp
@@ -387,13 +391,14 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const double longest = 32.0 * H * TY * kTX * (p.fused ? (double)p.Wp : 8.0 * (p.NCH - 1));
                     const double rounds = std::ceil((groups / G + 1.0) / p.KG);
                     // (the tile's own two chunks run as triangles with reloaded windows: dearer on narrow rows)
-                    const double narrow = p.fused ? 1.15 : 1.0 + 0.5 / ((double)p.NTX * p.NTX);
+                    // (fused rows: 1.07 from seven timed shapes of 20..32 columns, 31 us .. 190 us)
+                    const double narrow = p.fused ? 1.07 : 1.0 + 0.5 / ((double)p.NTX * p.NTX);
                     const double t_rate = std::ceil(G / dev.sm_count) *
                                           ((macs_block * narrow + rounds * 4.0 * 0.4 * longest) / rate + rounds * t_stage);
                     const double t_serial = std::ceil(ptasks / G / warps_blk) * H * p.Wp * TY * kTX / 1.8e9;
                     t = std::max(t_rate, t_serial);
                     if (queue_auto && ptasks / G < 1.25 * warps_blk) continue;  // about one task per warp: the tail decides
-                    queue_few_tasks = ptasks / G < 2.0 * warps_blk;
+                    queue_few_tasks = ptasks / G < 24.0;      // fewer than six per scheduler
                     comb = kStore;
                 } else if (c.sched == kSchedStreamK) {
                     const double units = tasks * H;
@@ -491,7 +496,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     std::fprintf(stderr, "plan TY=%d SL=%d WX=%d WY=%d S=%d sched=%d comb=%d grid=%u t=%.2f us\n", TY, SL, c.WX,
                                  c.WY, c.S, c.sched, comb, grid, t * 1e6);
                 const bool auto_queue_cand = queue_auto && c.sched == kSchedWarpQueue;
-                // (queue candidates with fewer than two tasks per warp only compete against stream-K)
+                // (queue candidates with fewer than six tasks per scheduler only compete against stream-K)
                 const bool few = auto_queue_cand && queue_few_tasks;
                 TilePlan& slot = few ? best_queue_few : auto_queue_cand ? best_queue : best;
                 double& slot_time = few ? best_queue_few_time : auto_queue_cand ? best_queue_time : best_time;

@@ -164,10 +164,17 @@ def test_planner_choices_for_the_benchmark_shapes(xc):
     """The per-shape choices the measurements led to, checked without a device (a B200 is assumed):
     the warp queue against a static plan whose last wave of blocks is under-filled (64x64 1x512:
     128 equal blocks on 148 SMs), stream-K kept where it is balanced already (48x48 16x128), fused
-    rows only for 17..32 columns with one class per thread and never under stream-K, the staged
-    warp-per-overlap kernel for a handful of overlaps, hints that override all of it."""
+    rows only for 17..32 columns with one class per thread and never under stream-K (under the
+    queue for 32x32 32x64, in static blocks for its shards), 16-warp blocks for the queue with one
+    class per thread, the warp-per-overlap kernel for a handful of overlaps, hints that override
+    all of it."""
     c3 = xc.describe_plan("one_to_many", 64, 64, 1, 512)
     assert "schedule=warp-queue" in c3 and "grid=(148,1,1)" in c3 and "combine=store" in c3 and "fused=0" in c3
+    assert "tile<TY=1>" in c3 and "block=(512,1,1)" in c3
+    c4 = xc.describe_plan("n_to_m", 32, 32, 32, 64)
+    assert "schedule=warp-queue" in c4 and "fused=1" in c4 and "tile<TY=1>" in c4 and "combine=store" in c4
+    sat = xc.describe_plan("one_to_many", 32, 32, 1, 4000)        # a full static plan, yet the queue is estimated 6 % faster
+    assert "schedule=warp-queue" in sat
     c5 = xc.describe_plan("n_to_mn", 48, 48, 16, 2048)
     assert "schedule=stream-k" in c5 and "fused=0" in c5
     small = xc.describe_plan("n_to_m", 32, 32, 4, 64)
