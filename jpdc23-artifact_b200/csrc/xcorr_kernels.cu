@@ -968,17 +968,26 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __res
         const int orow = (int)(grow % (unsigned long long)OH);
         const int sy = orow - (H - 1);
         const int wrap_row = sy >= 0 ? Hp - sy : -sy;
-        // slices with r0 < wrap_row (sy >= 0) or r1 > wrap_row (sy < 0)
-        int s_first = 0, s_last = S;              // [s_first, s_last)
-        if (sy >= 0) {
-            while (s_last > 0 && (int)(((long long)(s_last - 1) * H) / S) >= wrap_row) --s_last;
-        } else {
-            while (s_first < S && (int)(((long long)(s_first + 1) * H) / S) <= wrap_row) ++s_first;
-        }
+        // Slice s holds the right rows [s*H/S, (s+1)*H/S).  It wrote this output row iff it starts
+        // before the wrap row (sy >= 0: s*H < wrap_row*S) or ends after it (sy < 0:
+        // (s+1)*H >= (wrap_row+1)*S): the contributing slices are [s_first, s_last).
+        int s_first = 0, s_last = S;
+        if (sy >= 0) s_last = (int)min((long long)S, ((long long)wrap_row * S + H - 1) / H);
+        else s_first = (int)min((long long)S, max(0ll, ((long long)(wrap_row + 1) * S + H - 1) / H - 1));
         const unsigned long long base = grow * (unsigned long long)OW;
+        const float* first = ws + (unsigned long long)s_first * total_out + base;
         for (int x = threadIdx.x; x < OW; x += blockDim.x) {
+            // eight loads in flight, added in slice order (skipped slots add 0): the sum is the same
+            // sequential one whatever the batch size, and latency is paid once per eight slices
             float sum = 0.f;
-            for (int s = s_first; s < s_last; ++s) sum += ws[(unsigned long long)s * total_out + base + x];
+            const float* p = first + x;
+            for (int s = s_first; s < s_last; s += 8, p += 8 * total_out) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = s + i < s_last ? __ldcg(p + (unsigned long long)i * total_out) : 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum += v[i];
+            }
             out[base + x] = sum;
         }
     }
