@@ -344,10 +344,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 const int by_regs = 65536 / (regs * p.threads);
                 const int blocks_sm = std::max(1, std::min(by_smem, by_regs));
                 const int resident = blocks_sm * (p.threads / 32);
-                // (the warp queue with one class per thread, half the independent FFMA of two: with 12 resident warps it ran
-                // 3 % behind 16 on 64 x 64 1 x 512 -- 365 against 354 us, three runs each)
-                const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident) *
-                                       (c.sched == kSchedWarpQueue && TY == 1 && resident < 16 ? 0.97 : 1.0);
+                const double occ_eff = std::min(1.0, 0.4 + 0.05 * resident);
                 // shared-memory wavefronts per 8-step chunk against its FFMA issue slots
                 const double wavefronts = 2.0 * TY * std::max(1, p.SL / 8) + 6.0 * std::max(1, p.ML / 8);
                 const double smem_util = 4.0 * wavefronts / (8.0 * TY * kTX);
@@ -393,8 +390,16 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     // (the tile's own two chunks run as triangles with reloaded windows: dearer on narrow rows)
                     // (fused rows: 1.07 from seven timed shapes of 20..32 columns, 31 us .. 190 us)
                     const double narrow = p.fused ? 1.07 : 1.0 + 0.5 / ((double)p.NTX * p.NTX);
+                    // One class per thread has half the independent FFMA of two: with 12 resident warps it ran
+                    // 2-3 % behind 16 (64 x 64 1 x 512: 360 against 352 us; 32 x 32 32 x 64 fused: 103 against
+                    // 101 us; 16 x 16 100 x 4000: 33 against 29 us) -- where the tasks are of one length or a block
+                    // has 30 and more of them (48 x 48 4 x 128, 31 per block: 133 against 131 us).  With fewer
+                    // tasks of unequal length 16 warps leave the longest ones nothing to pair with (64 x 64
+                    // 1 x 256, 28 per block: 194 us with 12 warps, 201 with 16).
+                    const bool level_tasks = p.fused || p.NTX == 1 || ptasks / G >= 30.0;
+                    const double rate_q = rate * (TY == 1 && resident < 16 && level_tasks ? 0.97 : 1.0);
                     const double t_rate = std::ceil(G / dev.sm_count) *
-                                          ((macs_block * narrow + rounds * 4.0 * 0.4 * longest) / rate + rounds * t_stage);
+                                          ((macs_block * narrow + rounds * 4.0 * 0.4 * longest) / rate_q + rounds * t_stage);
                     const double t_serial = std::ceil(ptasks / G / warps_blk) * H * p.Wp * TY * kTX / 1.8e9;
                     t = std::max(t_rate, t_serial);
                     if (queue_auto && ptasks / G < 1.25 * warps_blk) continue;  // about one task per warp: the tail decides
