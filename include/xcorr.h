@@ -321,6 +321,8 @@ XCORR_API xcorr_status xcorr_run_host_f32(int32_t mode, const float* h_left, con
  * of idle SMs on single large pairs.  xcorr_last_launch_string() names the plan.
  * Rows too wide to stage take a second kernel (a warp per 8 x 32 block of a result, operands
  * through L1), which the environment variable XCORR_F64_STRIP=1 selects for every call.
+ * A handful of small overlaps (at most 8000, rows and columns up to 32) runs on the
+ * warp-per-overlap latency kernel, as in single precision.
  * Asynchronous on `stream`. */
 XCORR_API xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_right, double* d_out,
                                      uint32_t rows, uint32_t cols, uint32_t n_left, uint32_t n_right,

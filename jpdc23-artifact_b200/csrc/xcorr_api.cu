@@ -1315,6 +1315,20 @@ xcorr_status xcorr_run_f64(int32_t mode, const double* d_left, const double* d_r
         TilePlan64 tp{};
         const char* rep_env = std::getenv("XCORR_REPRODUCIBLE");
         const bool reproducible = rep_env && rep_env[0] == '1';
+        // a handful of small overlaps: the warp-per-overlap latency kernel, as in single precision
+        const double overlaps = (double)pm.n_left * pm.m * (2.0 * rows - 1) * (2.0 * cols - 1);
+        if (!force_strip && !std::getenv("XCORR_F64_PLAN") && rows <= 32 && cols <= 32 && overlaps <= kTinyOverlaps) {
+            dim3 g;
+            const int bt = overlaps > 2000.0 ? 128 : 256;
+            XC_CUDA(launch_warp_per_overlap_f64(d_left, d_right, d_out, (int)rows, (int)cols, pm,
+                                                (unsigned long long)pm.n_left * pm.m, bt, &g,
+                                                static_cast<cudaStream_t>(stream)));
+            char wbuf[128];
+            std::snprintf(wbuf, sizeof wbuf, "kernel=warp_per_overlap_f64 grid=(%u,1,1) block=(%d,1,1) smem=0", g.x, bt);
+            set_launch_text(wbuf);
+            ++t_launch_count;
+            return XCORR_OK;
+        }
         if (!force_strip && plan_tile_f64(pm, (int)rows, (int)cols, dev.sm_count, dev.smem_optin, reproducible, &tp)) {
             TileArgs64 ta{};
             ta.left = d_left; ta.right = d_right; ta.out = d_out; ta.p = tp; ta.pm = pm;

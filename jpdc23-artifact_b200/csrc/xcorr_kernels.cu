@@ -1051,30 +1051,31 @@ __device__ __forceinline__ unsigned long long split_workers_before(unsigned y, u
 // element, naive_warp_per_shift.cu:69-70).  Eight rows per trip, rows past the end predicated
 // off, with all sixteen loads issued before the first multiply-add: for a pair of 16 x 16 the
 // whole sum is one round trip to L2.
-__device__ __forceinline__ float warp_overlap_sum(const float* __restrict__ L, const float* __restrict__ R, int W,
-                                                  int sx, int sy, int x0, int x1, int y0, int y1, int lane) {
+template<typename T>
+__device__ __forceinline__ T warp_overlap_sum(const T* __restrict__ L, const T* __restrict__ R, int W,
+                                              int sx, int sy, int x0, int x1, int y0, int y1, int lane) {
     int lc = 32;
     while (lc > 1 && (lc >> 1) >= x1 - x0) lc >>= 1;
     const int lrn = 32 / lc;
     const int c0 = x0 + (lane & (lc - 1));
     const int yfirst = y0 + lane / lc;
-    const float* lbase = L + (size_t)yfirst * W;
-    const float* rbase = R + (ptrdiff_t)(yfirst - sy) * W - sx;
+    const T* lbase = L + (size_t)yfirst * W;
+    const T* rbase = R + (ptrdiff_t)(yfirst - sy) * W - sx;
     const size_t rstep = (size_t)lrn * W;
-    float sum = 0.f;
+    T sum = T(0);
     for (int xl = c0; xl < x1; xl += lc) {
-        const float* lp = lbase + xl;
-        const float* rp = rbase + xl;
+        const T* lp = lbase + xl;
+        const T* rp = rbase + xl;
         for (int yl = yfirst; yl < y1; yl += 8 * lrn, lp += 8 * rstep, rp += 8 * rstep) {
-            float lv[8], rv[8];
+            T lv[8], rv[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const bool live = yl + i * lrn < y1;
-                lv[i] = live ? __ldg(lp + i * rstep) : 0.f;
-                rv[i] = live ? __ldg(rp + i * rstep) : 0.f;
+                lv[i] = live ? __ldg(lp + i * rstep) : T(0);
+                rv[i] = live ? __ldg(rp + i * rstep) : T(0);
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) sum = fmaf(rv[i], lv[i], sum);
+            for (int i = 0; i < 8; ++i) sum = fma(rv[i], lv[i], sum);
         }
     }
 #pragma unroll
@@ -1084,9 +1085,11 @@ __device__ __forceinline__ float warp_overlap_sum(const float* __restrict__ L, c
 
 // The unsplit form with 32-bit task arithmetic: what a handful of overlaps runs on, where the
 // 64-bit divisions of the general kernel below are a visible part of the few microseconds.
-__global__ void __launch_bounds__(1024) warp_per_overlap_direct_kernel(const float* __restrict__ left,
-                                                                       const float* __restrict__ right,
-                                                                       float* __restrict__ out, int H, int W,
+// Also instantiated for double (the same latency kernel for xcorr_run_f64).
+template<typename T>
+__global__ void __launch_bounds__(1024) warp_per_overlap_direct_kernel(const T* __restrict__ left,
+                                                                       const T* __restrict__ right,
+                                                                       T* __restrict__ out, int H, int W,
                                                                        PairMap pm, unsigned ntasks) {
     const unsigned OW = 2u * W - 1, OH = 2u * H - 1, OE = OW * OH;
     const int lane = threadIdx.x & 31;
@@ -1100,9 +1103,9 @@ __global__ void __launch_bounds__(1024) warp_per_overlap_direct_kernel(const flo
         const int x0 = max(sx, 0), x1 = min(W + sx, W);
         const int y0 = max(sy, 0), y1 = min(H + sy, H);
         const unsigned l = pm.m == 1 ? pair : pair / pm.m, j = pair - l * pm.m;
-        const float* L = left + (size_t)l * H * W;
-        const float* R = right + ((size_t)l * pm.right_stride + j) * (size_t)H * W;
-        const float sum = warp_overlap_sum(L, R, W, sx, sy, x0, x1, y0, y1, lane);
+        const T* L = left + (size_t)l * H * W;
+        const T* R = right + ((size_t)l * pm.right_stride + j) * (size_t)H * W;
+        const T sum = warp_overlap_sum<T>(L, R, W, sx, sy, x0, x1, y0, y1, lane);
         if (lane == 0) out[(size_t)pair * OE + oi] = sum;
     }
 }
@@ -1153,7 +1156,7 @@ __global__ void warp_per_overlap_kernel(const float* __restrict__ left, const fl
         const unsigned long long l = pair / pm.m, j = pair % pm.m;
         const float* L = left + l * (size_t)H * W;
         const float* R = right + (l * pm.right_stride + j) * (size_t)H * W;
-        const float sum = warp_overlap_sum(L, R, W, sx, sy, x0, x1, y0, y1, lane);
+        const float sum = warp_overlap_sum<float>(L, R, W, sx, sy, x0, x1, y0, y1, lane);
         if (lane == 0) {
             float* dst = out + pair * OE + (size_t)oy * OW + ox;
             if (split != kSplitNone) atomicAdd(dst, sum); else *dst = sum;
@@ -1428,11 +1431,23 @@ cudaError_t launch_warp_per_overlap(const float* left, const float* right, float
     if (blocks > cap) blocks = cap;
     dim3 grid((unsigned)blocks), block(wpb * 32);
     if (split == kSplitNone && ntasks < (1ull << 31) && npairs * pm.right_stride < (1ull << 31))
-        warp_per_overlap_direct_kernel<<<grid, block, 0, stream>>>(left, right, out, H, W, pm, (unsigned)ntasks);
+        warp_per_overlap_direct_kernel<float><<<grid, block, 0, stream>>>(left, right, out, H, W, pm, (unsigned)ntasks);
     else
         warp_per_overlap_kernel<<<grid, block, 0, stream>>>(left, right, out, H, W, pm, ntasks, rows_per_warp, split);
     *grid_out = grid;
     *block_out = block;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_warp_per_overlap_f64(const double* left, const double* right, double* out, int H, int W,
+                                        PairMap pm, unsigned long long npairs, int block_threads, dim3* grid_out,
+                                        cudaStream_t stream) {
+    const unsigned long long ntasks = (2ull * W - 1) * (2ull * H - 1) * npairs;
+    if (ntasks >= (1ull << 31)) return cudaErrorInvalidValue;
+    const int wpb = block_threads / 32 > 0 ? block_threads / 32 : 1;
+    dim3 grid((unsigned)((ntasks + wpb - 1) / wpb)), block(wpb * 32);
+    warp_per_overlap_direct_kernel<double><<<grid, block, 0, stream>>>(left, right, out, H, W, pm, (unsigned)ntasks);
+    *grid_out = grid;
     return cudaGetLastError();
 }
 

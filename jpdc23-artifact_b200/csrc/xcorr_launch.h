@@ -30,6 +30,10 @@ cudaError_t tile_stage_timeouts(unsigned* count);
 cudaError_t launch_strip_f64(const double* left, const double* right, double* out, int H, int W, PairMap pm,
                              unsigned long long npairs, int sm_count, dim3* grid_out, dim3* block_out,
                              cudaStream_t stream);
+// The warp-per-overlap latency kernel in double (a handful of small overlaps; below 2^31 of them).
+cudaError_t launch_warp_per_overlap_f64(const double* left, const double* right, double* out, int H, int W,
+                                        PairMap pm, unsigned long long npairs, int block_threads, dim3* grid_out,
+                                        cudaStream_t stream);
 // Double precision, register-tiled (xcorr_f64_tile.cu).  plan_tile_f64 returns false when no plan fits
 // one SM's shared memory; a plan with S > 1 needs the output zeroed before the launch.  `reproducible`
 // keeps to plans whose results are bit-identical from run to run (at most two row slices).
