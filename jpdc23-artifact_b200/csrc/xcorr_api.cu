@@ -354,7 +354,9 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 // (12..16 warps sharing one staging) and many right matrices per warp run
                 // up to ~15 % faster than small blocks / few matrices per warp
                 const int warps_blk = p.threads / 32;
-                const double block_prior = warps_blk >= 12 ? 1.0 : warps_blk >= 8 ? 0.93 : warps_blk >= 4 ? 0.87 : 0.8;
+                // (fused rows lose less in four-warp blocks: 28 x 28 1 x 1000 runs 43 us in 441 blocks of four
+                // warps, 50 us in 128 blocks of fourteen)
+                const double block_prior = warps_blk >= 12 ? 1.0 : warps_blk >= 8 ? 0.93 : warps_blk >= 4 ? (p.fused ? 0.92 : 0.87) : 0.8;
                 const double lanes_prior = p.ML >= 8 ? 1.0 : p.ML == 4 ? 0.96 : p.ML == 2 ? 0.92 : 0.9;
                 // blocks of more than 384 threads run the 128-register build, which spills for
                 // TY = 4 (and a little for TY = 3): measured 28 against 47 TFLOP/s on 64 x 64 x 512
@@ -365,7 +367,12 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                 const double rate = sm_rate * tile_eff * occ_eff * smem_eff * block_prior * lanes_prior * build_eff;
                 // filling the staging buffers: bytes over ~64 B/clk from L2 plus a latency
                 // chain, paid once per block (per segment / phase)
-                const double t_stage = ((double)p.smem_bytes / 64.0 + 2000.0) / 1.9e9;
+                // (rows whose length is no multiple of four floats are staged word by word by the block's
+                // own threads, ~120 cycles per word and thread: 17 x 30 1 x 100 in two-warp blocks that stage
+                // 70 KB each took 34 us, 14 us in blocks of ten warps)
+                const double stage_cycles = W % 4 == 0 ? (double)p.smem_bytes / 64.0 + 2000.0
+                                                       : (double)p.smem_bytes / 4.0 / p.threads * 120.0 + 2000.0;
+                const double t_stage = stage_cycles / 1.9e9;
                 double t;
                 int comb;
                 int sk_parts = 0;
@@ -423,7 +430,7 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     const double sk_flushes = 2.0 * (std::min<double>(p.SL * TY, rows_per_block) + TY) * segments;
                     const double sk_row_cycles = kRowBase + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
                     const double t_serial = (rows_per_block * sk_row_cycles + sk_flushes * 500.0 +
-                                             4000.0 * segments) / 1.9e9;
+                                             std::max(4000.0, stage_cycles) * segments) / 1.9e9;
                     // every block boundary splits one task; a split task is added atomically twice
                     // (measured on B200 with the coalesced flush: ~3.4 TB/s of atomic traffic, the
                     // memset of the output ~5 TB/s)
@@ -472,7 +479,13 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     // flushes and TY final ones per pass) relative to the FFMA of a warp's slice
                     const double flush_share = 2.0 * (std::min<double>(p.SL * TY, rs) + TY) * kFlushSlots /
                                                (rs * p.Wp * TY * kTX);
-                    const double t_rate = busiest * macs_per_block / rate * ((rs + 0.25) / rs + flush_share) +
+                    // (fewer blocks than would be resident: the SM's rate is that of the warps it really holds.
+                    // Fused rows only, where the lone-warp bound below no longer hides it: 32 x 32 4 x 64 in 128
+                    // four-warp blocks runs the same 22.9 us with 47 KB or 80 KB of shared memory per block)
+                    const double held = std::min<double>(blocks_sm, busiest) * (p.threads / 32);
+                    // (a lone fused warp per scheduler keeps 3/4 of the rate of four: 32 x 32 4 x 64 against 32 x 64)
+                    const double rate_s = p.fused ? rate / occ_eff * std::min(1.0, 0.67 + 0.0208 * held) : rate;
+                    const double t_rate = busiest * macs_per_block / rate_s * ((rs + 0.25) / rs + flush_share) +
                                           std::ceil(busiest / blocks_sm) * t_stage;
                     // A lone warp is bound by latency, not by the SM's FFMA rate: per right row its
                     // FFMAs one per clock plus ~150 cycles of row overhead per pass and ~40 per
@@ -480,8 +493,11 @@ xcorr_status plan_tile_search(const PairMap& pm, int H, int W, const xcorr_hints
                     // ones per pass), ~4000 for the staging.  This decides the plan of tiny inputs
                     // (16 x 16: many small warps tasks with few flushes beat one full warp).
                     const double flushes = 2.0 * (std::min<double>(p.SL * TY, rs) + TY);
-                    const double row_cycles = kRowBase + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
-                    const double t_serial = (rs * row_cycles + flushes * 500.0 + 4000.0) / 1.9e9;
+                    // (fused rows: one visit per row, no windows -- the row's FFMA plus ~60 cycles; timed on
+                    // 32 x 32 1 x 32 in four-warp blocks: 11.3 us in all, ~530 cycles per row)
+                    const double row_cycles = p.fused ? 60.0 + (double)p.Wp * TY * kTX
+                                                      : kRowBase + (p.NCH + 2) * 40.0 + (double)p.Wp * TY * kTX;
+                    const double t_serial = (rs * row_cycles + flushes * 500.0 + std::max(4000.0, stage_cycles)) / 1.9e9;
                     comb = want_combine;
                     if (comb == XCORR_COMBINE_AUTO) {
                         comb = S == 1 ? kStore : S == 2 ? kAtomic : kWorkspace;
