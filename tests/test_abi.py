@@ -175,6 +175,12 @@ def test_planner_choices_for_the_benchmark_shapes(xc):
     assert "schedule=warp-queue" in c4 and "fused=1" in c4 and "tile<TY=1>" in c4 and "combine=store" in c4
     sat = xc.describe_plan("one_to_many", 32, 32, 1, 4000)        # a full static plan, yet the queue is estimated 6 % faster
     assert "schedule=warp-queue" in sat
+    # small shapes of 17..32 columns: static blocks with fused rows where they fill the GPU (timed 19 against
+    # 23 us of stream-K), stream-K where they do not, or where ragged rows would be staged word by word by few threads
+    mid = xc.describe_plan("n_to_mn", 24, 24, 32, 256)
+    assert "schedule=static" in mid and "fused=1" in mid
+    assert "schedule=stream-k" in xc.describe_plan("n_to_m", 32, 32, 8, 8)
+    assert "schedule=stream-k" in xc.describe_plan("one_to_many", 17, 30, 1, 100)
     c5 = xc.describe_plan("n_to_mn", 48, 48, 16, 2048)
     assert "schedule=stream-k" in c5 and "fused=0" in c5
     small = xc.describe_plan("n_to_m", 32, 32, 4, 64)
